@@ -1,0 +1,25 @@
+// attention.cuh — host-side call block of the attention kernels.
+#pragma once
+#include "common.cuh"
+
+namespace jb {
+
+struct AttnCall {
+    __half* out = nullptr; const __half* q = nullptr;
+    const void* k = nullptr; const void* v = nullptr; const float* ks = nullptr; const float* vs = nullptr;
+    // ragged batch: device arrays of per-sequence pointers / lengths (batch entries)
+    const void* const* k_list = nullptr; const void* const* v_list = nullptr;
+    const float* const* ks_list = nullptr; const float* const* vs_list = nullptr; const int* seq_lens = nullptr;
+    int batch = 1, max_seq = 0;
+    int n_heads = 0, n_kv = 0, hd = 0, chd = 0, seq_len = 0;
+    const int* d_pos = nullptr;       // device position: seq_len = *d_pos + 1
+    float scale = 1.f; int kv_int8 = 0, window = 0, n_splits = 0;
+    int causal_start = -1;            // >= 0: prefill, `batch` = number of query tokens
+};
+
+int    attn_splits_for(int seq_len);
+float* splitk_buffer(size_t floats, bool may_alloc);
+int    launch_attention_general(const AttnCall& c, cudaStream_t st);
+int    launch_attention(const AttnCall& c, cudaStream_t st);      // picks the fast path when it applies
+
+}  // namespace jb

@@ -1,0 +1,143 @@
+// common.cuh — shared device/host helpers of the B200 kernel library.
+//
+// Block formats follow GGUF as the reference re-declares them
+// (src/kernels/gemv_q4.cu:141-164): Q4_K 144 B, Q5_K 176 B, Q6_K 210 B per 256 weights.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdio>
+
+namespace jb {
+
+constexpr int QK_K      = 256;
+constexpr int Q4K_BYTES = 144;
+constexpr int Q5K_BYTES = 176;
+constexpr int Q6K_BYTES = 210;
+constexpr int T_Q4K = 12, T_Q5K = 13, T_Q6K = 14;
+
+__host__ __device__ inline int block_bytes(int t) {
+    return t == T_Q4K ? Q4K_BYTES : t == T_Q5K ? Q5K_BYTES : t == T_Q6K ? Q6K_BYTES : 0;
+}
+
+// ── error channel (host) ────────────────────────────────────────────────
+// The reference logs and falls back to a CPU path; this library has no CPU path, so
+// every entry point records a retrievable error instead (and zero-fills its output
+// where the reference does).
+enum : int {
+    JB_OK = 0, JB_ERR_ARG = 1, JB_ERR_TYPE = 2, JB_ERR_PTR = 3, JB_ERR_CUDA = 4,
+    JB_ERR_NOMEM = 5, JB_ERR_LIMIT = 6, JB_ERR_TIMEOUT = 7, JB_ERR_STATE = 8,
+};
+int  set_error(int code, const char* fmt, ...);
+int  cuda_error(cudaError_t e, const char* what);
+#define JB_CUDA(call)                                                     \
+    do { cudaError_t e__ = (call); if (e__ != cudaSuccess) return ::jb::cuda_error(e__, #call); } while (0)
+
+// ── per-device context ──────────────────────────────────────────────────
+// Library-owned scratch is per device (the reference keeps process-global statics,
+// src/kernels/gemv_q4.cu:1309-1321, attention.cu:975-988, rope.cu:29-40).
+struct RopeTable { float theta; int half_dim; int max_seq; float* cos; float* sin; };
+struct DeviceCtx {
+    int   device = -1;
+    int   sm_count = 0;
+    int   max_smem_optin = 0;
+    int*  d_status = nullptr;           // device status word written by bounded waits
+    float* splitk = nullptr; size_t splitk_floats = 0;
+    void*  mmq_act = nullptr; size_t mmq_act_bytes = 0;
+    RopeTable rope[8]; int n_rope = 0;
+    bool gemv_attr[2] = { false, false };
+};
+DeviceCtx* ctx();                        // context of the current device (created on first use)
+
+// ── device helpers ──────────────────────────────────────────────────────
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself block for a
+// hardware-defined short interval) and reports false; callers set the status word
+// and return instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// 1-D bulk copy global -> shared through the TMA unit; both addresses 16-byte aligned,
+// size a multiple of 16 bytes; completion is signalled on `bar` by byte count.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Programmatic dependent launch: wait for the producer grid's memory / let dependents start.
+__device__ __forceinline__ void pdl_wait()   { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    int d; asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+__device__ __forceinline__ float h2f_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// 6-bit scale / min j (0..7) of a Q4_K/Q5_K block from its three packed scale words
+// (bytes 0-3, 4-7, 8-11 of scales[12]; layout per src/kernels/gemv_q4.cu:185-195).
+__device__ __forceinline__ void scale_min_k4(int j, uint32_t s0, uint32_t s1, uint32_t s2, int& sc, int& mn) {
+    const int sh = 8 * (j & 3);
+    if (j < 4) { sc = (s0 >> sh) & 63; mn = (s1 >> sh) & 63; }
+    else {
+        sc = ((s2 >> sh) & 0xF) | (((s0 >> (sh + 6)) & 3) << 4);
+        mn = ((s2 >> (sh + 4)) & 0xF) | (((s1 >> (sh + 6)) & 3) << 4);
+    }
+}
+#endif  // __CUDACC__
+
+// Launch with the programmatic-dependent-launch attribute when `pdl` is set.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+bool pdl_enabled();          // process-wide switch (default on)
+void count_launch(int n = 1);  // launch counter for the benchmark's gpu_launches claim
+
+}  // namespace jb

@@ -1,0 +1,33 @@
+// gemv.cuh — host-side argument block of the streaming K-quant GEMV.
+#pragma once
+#include "common.cuh"
+
+namespace jb {
+
+struct GemvSeg { const void* W; void* y; int M; int type; };
+
+// One launch computes up to three projections that share one activation vector
+// (the reference's gemv_quant / _pair / _triple / _add / _f32 family,
+// src/kernels/gemv_q4.cu:2633-2775).
+struct GemvArgs {
+    GemvSeg seg[3];
+    int nseg = 1;
+    const __half* x = nullptr;
+    int K = 0;
+    // 0: activations quantised to q8_1 codes, integer dots (reference dp4a path);
+    // 1: activations kept as 16-bit fixed point, integer dots (stands in for the
+    //    reference's fp16-x float path: same mathematics, no 8-bit activation rounding).
+    int xmode = 0;
+    int out_mode = 0;                 // 0 half, 1 float, 2 half(half(acc)+residual), 3 silu(seg0)*seg1 -> seg0.y
+    const __half* residual = nullptr; // out_mode 2
+    // optional fused input RMSNorm: x := half((x [+ norm_res]) * rrms * w) before quantising
+    int do_norm = 0;
+    const void* norm_w = nullptr; int norm_w_fp32 = 1; float eps = 0.f;
+    int32_t* dbg_dots = nullptr;      // optional: integer accumulators of seg 0
+};
+
+int launch_gemv(const GemvArgs& a, cudaStream_t st);
+int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const __half* residual,
+                    int M, int K, cudaStream_t st);
+
+}  // namespace jb

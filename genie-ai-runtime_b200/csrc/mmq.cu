@@ -1,0 +1,124 @@
+// mmq.cu — batched K-quant GEMM (prefill), first CUDA-core version.
+//
+// Arithmetic mirrors the reference's default prefill path: activations are quantised
+// per 32 without clamping; Q4_K keeps (half d, half sum-of-x) per group and folds the
+// weight sub-scales as half products, Q6_K keeps fp32 d (mmq_q4k_llama.cu:383-404,
+// :159-163, :321-322; mmq_q6k_llama.cu:424-438, :208, :361).
+#include "mmq.cuh"
+
+namespace jb {
+
+struct ActQ { int8_t* q; float* d; float* s; };   // [N][K] codes, [N][K/32] scale, [N][K/32] sum
+
+size_t mmq_scratch_bytes(int N, int K) { return (size_t)N * K + 2 * (size_t)N * (K / 32) * sizeof(float) + 256; }
+
+void* mmq_scratch(size_t bytes, bool may_alloc) {
+    DeviceCtx* c = ctx();
+    if (!c) return nullptr;
+    if (bytes > c->mmq_act_bytes) {
+        if (!may_alloc) return nullptr;
+        if (c->mmq_act) cudaFree(c->mmq_act);
+        c->mmq_act = nullptr; c->mmq_act_bytes = 0;
+        if (cudaMalloc(&c->mmq_act, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        c->mmq_act_bytes = bytes;
+    }
+    return c->mmq_act;
+}
+
+// one warp per 32-element group of one token
+__global__ void mmq_quantize_kernel(const __half* x, ActQ a, int N, int K, int ds4) {
+    pdl_wait();
+    const long long g = (long long)blockIdx.x * blockDim.y + threadIdx.y;
+    const int lane = threadIdx.x, G = K / 32;
+    if (g >= (long long)N * G) return;
+    const float v = __half2float(x[g * 32 + lane]);
+    const float amax = warp_max(fabsf(v));
+    float sum = v;
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    const float d = __fdiv_rn(amax, 127.0f), dinv = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+    a.q[g * 32 + lane] = (int8_t)__float2int_rn(__fmul_rn(v, dinv));
+    if (lane == 0) {
+        a.d[g] = ds4 ? __half2float(__float2half_rn(d)) : d;
+        a.s[g] = ds4 ? __half2float(__float2half_rn(sum)) : 0.f;
+    }
+}
+
+// one warp per (row, token); lanes stride over 32-groups (Q4_K) / 16-groups (Q6_K)
+__global__ void mmq_simple_kernel(__half* y, const uint8_t* W, int type, ActQ a, int M, int N, int K, int32_t* dbg) {
+    pdl_wait();
+    const int row = blockIdx.x * blockDim.y + threadIdx.y, tok = blockIdx.y, lane = threadIdx.x;
+    if (row >= M) return;
+    const int nb = K / QK_K;
+    const int8_t* q8 = a.q + (size_t)tok * K;
+    const float* d8 = a.d + (size_t)tok * (K / 32);
+    const float* s8 = a.s + (size_t)tok * (K / 32);
+    float acc = 0.f;
+    if (type == T_Q4K) {
+        for (int g = lane; g < nb * 8; g += 32) {
+            const uint8_t* blk = W + ((size_t)row * nb + (g >> 3)) * Q4K_BYTES;
+            const int j = g & 7;
+            const uint32_t* s = reinterpret_cast<const uint32_t*>(blk + 4);
+            int sc, mn; scale_min_k4(j, s[0], s[1], s[2], sc, mn);
+            const uint32_t* qs = reinterpret_cast<const uint32_t*>(blk + 16 + 32 * (j >> 1));
+            const int* xq = reinterpret_cast<const int*>(q8 + g * 32);
+            int dot = 0;
+            #pragma unroll
+            for (int w = 0; w < 8; ++w) dot = dp4a_us((j & 1) ? (qs[w] >> 4) & 0x0F0F0F0Fu : qs[w] & 0x0F0F0F0Fu, xq[w], dot);
+            if (dbg) dbg[((size_t)tok * M + row) * (nb * 8) + g] = dot;
+            const __half dh = __ushort_as_half(*reinterpret_cast<const unsigned short*>(blk));
+            const __half mh = __hneg(__ushort_as_half(*reinterpret_cast<const unsigned short*>(blk + 2)));
+            const float ax = __half2float(__hmul(dh, __float2half_rn((float)sc)));
+            const float ay = __half2float(__hmul(mh, __float2half_rn((float)mn)));
+            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(ax, d8[g]), (float)dot));
+            acc = __fadd_rn(acc, __fmul_rn(ay, s8[g]));
+        }
+    } else {
+        for (int g = lane; g < nb * 16; g += 32) {
+            const uint8_t* blk = W + ((size_t)row * nb + (g >> 4)) * Q6K_BYTES;
+            const int e0 = (g & 15) * 16;
+            int dot = 0;
+            for (int i = 0; i < 16; ++i) {
+                const int e = e0 + i, n = e >> 7, r = e & 127, quarter = r >> 5, l = r & 31;
+                int lo = (quarter & 1) ? blk[64 * n + 32 + l] : blk[64 * n + l];
+                lo = (quarter & 2) ? (lo >> 4) : (lo & 0xF);
+                const int qv = (lo | (((blk[128 + 32 * n + l] >> (2 * quarter)) & 3) << 4)) - 32;
+                dot += qv * (int)q8[(g >> 4) * 256 + e];
+            }
+            if (dbg) dbg[((size_t)tok * M + row) * (nb * 16) + g] = dot;
+            const float d = h2f_bits(blk[208] | (blk[209] << 8));
+            acc += __fmul_rn(__fmul_rn(__fmul_rn((float)dot, (float)(int8_t)blk[192 + (g & 15)]), d8[g >> 1]), d);
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)tok * M + row] = __float2half_rn(acc);
+}
+
+static bool capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) { cudaGetLastError(); return false; }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return JB_OK;
+    if (K <= 0 || K % QK_K) return set_error(JB_ERR_ARG, "batched gemm: K=%d is not a positive multiple of 256", K);
+    if (type != T_Q4K && type != T_Q6K) return set_error(JB_ERR_TYPE, "batched gemm: ggml type %d", type);
+    if (!y || !W || !x) return set_error(JB_ERR_PTR, "batched gemm: null pointer");
+    if (type == T_Q4K && ((uintptr_t)W & 3)) return set_error(JB_ERR_PTR, "batched gemm: Q4_K weights must be 4-byte aligned");
+    const size_t need = mmq_scratch_bytes(N, K);
+    uint8_t* base = (uint8_t*)mmq_scratch(need, !capturing(st));
+    if (!base) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need);
+    ActQ a;
+    a.q = (int8_t*)base;
+    a.d = (float*)(base + (((size_t)N * K + 255) & ~(size_t)255));
+    a.s = a.d + (size_t)N * (K / 32);
+    const long long groups = (long long)N * (K / 32);
+    JB_CUDA(launch_k(mmq_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, a, N, K, (int)(type == T_Q4K)));
+    count_launch();
+    JB_CUDA(launch_k(mmq_simple_kernel, dim3((M + 3) / 4, N), dim3(32, 4), 0, st, pdl_enabled(), y, (const uint8_t*)W, type, a, M, N, K, dbg));
+    count_launch();
+    return JB_OK;
+}
+
+}  // namespace jb

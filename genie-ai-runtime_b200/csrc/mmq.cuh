@@ -1,0 +1,15 @@
+// mmq.cuh — prefill / batched K-quant GEMM launchers.
+#pragma once
+#include "common.cuh"
+
+namespace jb {
+
+// y[N x M] half (token-major) = x[N x K] half . W^T, W in Q4_K / Q6_K blocks, with the
+// arithmetic of the reference's default prefill path (gemm_quant_batched,
+// src/kernels/gemv_q4.cu:2478-2495 -> mmq_q4k_llama.cu / mmq_q6k_llama.cu).
+// dbg_dots (optional): integer accumulators [N][M][K/32] (Q4_K) or [N][M][K/16] (Q6_K).
+int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg_dots, cudaStream_t st);
+size_t mmq_scratch_bytes(int N, int K);
+void*  mmq_scratch(size_t bytes, bool may_alloc);
+
+}  // namespace jb

@@ -1,0 +1,192 @@
+/* jllm_b200.h — C ABI of the B200 (sm_100a) kernel library behind genie-ai-runtime's
+ * kernel API.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream passed as
+ * `void*` (a cudaStream_t), and returns a status code (0 = ok).  The functions in the
+ * first part mirror, one for one, the C++ functions the reference engine calls
+ * (include/jllm_kernels.h in the reference; the same library also exports those C++
+ * symbols with identical mangling, see jllm_b200_api.hpp, so the engine's objects link
+ * against it unchanged).  The second part holds additive extension entry points.
+ *
+ * Differences from the reference's behaviour, by design: there is no CPU fallback.
+ * Where the reference logs and falls back (or zero-fills), these functions record an
+ * error retrievable with jllm_b200_last_error(), zero-fill the output where the
+ * reference does, and return a non-zero status.
+ *
+ * All pointers are device pointers unless stated otherwise.  `half` buffers are IEEE
+ * binary16.  ggml_type: 12 = Q4_K, 13 = Q5_K, 14 = Q6_K (GGUF block layouts unchanged).
+ */
+#ifndef JLLM_B200_H
+#define JLLM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define JLLM_B200_OK          0
+#define JLLM_B200_ERR_ARG     1   /* bad size / shape */
+#define JLLM_B200_ERR_TYPE    2   /* unsupported ggml / dense type */
+#define JLLM_B200_ERR_PTR     3   /* null, unresolvable or misaligned pointer */
+#define JLLM_B200_ERR_CUDA    4   /* CUDA runtime error (text in last_error) */
+#define JLLM_B200_ERR_NOMEM   5   /* library scratch could not be (re)allocated */
+#define JLLM_B200_ERR_LIMIT   6   /* size beyond a documented maximum */
+#define JLLM_B200_ERR_TIMEOUT 7   /* a bounded device-side wait ran out */
+#define JLLM_B200_ERR_STATE   8   /* call not valid in the current state */
+
+/* ── library state ───────────────────────────────────────────────────────── */
+/* Creates the per-device context (status word, SM count) for `device` (-1 = current).
+ * Implicit on first use; call it explicitly before CUDA-graph capture. */
+int         jllm_b200_init(int device);
+const char* jllm_b200_last_error(void);          /* thread-local text of the last error */
+int         jllm_b200_last_error_code(void);
+void        jllm_b200_clear_error(void);
+/* Synchronises `stream` and returns the device status word (0, or ERR_TIMEOUT if a
+ * bounded wait inside a kernel gave up); the word is cleared. */
+int         jllm_b200_device_status(void* stream);
+long long   jllm_b200_launch_count(void);        /* kernels launched by this library so far */
+void        jllm_b200_set_pdl(int on);           /* programmatic dependent launch on/off (default on) */
+
+/* ── mapped-weight registry — include/jllm_kernels.h:40-43, src/engine/model.cpp:39-66 ── */
+const void* jllm_b200_resolve_mapped_weight_device_ptr(const void* host_ptr);
+void        jllm_b200_register_mapped_weight_region(const void* host_base, const void* device_base, int64_t bytes);
+void        jllm_b200_clear_mapped_weight_region(const void* host_base);
+
+/* ── K-quant GEMV family (decode) ────────────────────────────────────────── */
+/* gemv_quant — include/jllm_kernels.h:64-72, src/kernels/gemv_q4.cu:2633-2688.
+ * y[M] half = W[M x K] . x[K].  Q4_K/Q6_K: x quantised to q8_1, integer dots; Q5_K: float. */
+int jllm_b200_gemv_quant(void* y, const void* W, int ggml_type, const void* x, int M, int K, void* stream);
+/* gemv_q4 — include/jllm_kernels.h:51-60 (forwards to gemv_quant with Q4_K, gemv_q4.cu:1238-1243). */
+int jllm_b200_gemv_q4(void* y, const void* W_q4, const void* scales, const void* x, int M, int K, int group_size, void* stream);
+/* gemv_quant_add — :78-87, gemv_q4.cu:2690-2718.  y = half(half(W.x) + residual); fp16-x arithmetic. */
+int jllm_b200_gemv_quant_add(void* y, const void* W, int ggml_type, const void* x, const void* residual, int M, int K, void* stream);
+/* gemv_quant_pair — :92-104, gemv_q4.cu:2720-2734.  Two projections sharing x. */
+int jllm_b200_gemv_quant_pair(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,
+                              const void* x, int K, void* stream);
+/* gemv_quant_triple — :106-122, gemv_q4.cu:2736-2753.  Three projections sharing x. */
+int jllm_b200_gemv_quant_triple(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,
+                                void* y2, const void* W2, int type2, int M2, const void* x, int K, void* stream);
+/* gemv_quant_f32 — :148-156, gemv_q4.cu:2755-2775.  fp32 output (logits). */
+int jllm_b200_gemv_quant_f32(float* y, const void* W, int ggml_type, const void* x, int M, int K, void* stream);
+/* gemm_quant_batched — :135-144, gemv_q4.cu:2478-2517.  y[N x M] = x[N x K] . W^T; N == 1 is gemv_quant. */
+int jllm_b200_gemm_quant_batched(void* y, const void* W, int ggml_type, const void* x, int M, int N, int K, void* stream);
+/* dequant_embedding_row — :160-167, gemv_q4.cu:2777-2809.  Returns 0 on success (the C++ symbol returns bool). */
+int jllm_b200_dequant_embedding_row(void* dst, const void* W, int ggml_type, int token_id, int hidden_dim, void* stream);
+/* gemv_dense / gemm_dense_batched — :220-227, gemv_q4.cu:2842-2885.  wtype 0 = F32, 1 = F16, 30 = BF16. */
+int jllm_b200_gemv_dense(void* out, const void* W, int wtype, const void* x, int M, int K, void* stream);
+int jllm_b200_gemm_dense_batched(void* out, const void* W, int wtype, const void* x, int M, int N, int K, void* stream);
+
+/* ── element-wise family ─────────────────────────────────────────────────── */
+/* fused_rmsnorm_residual — :174-184, src/kernels/fused_norm.cu:103-165. */
+int jllm_b200_fused_rmsnorm_residual(void* output, const void* x, const void* residual, const void* weight,
+                                     int rows, int hidden_dim, float eps, int weight_fp32, void* stream);
+/* fused_swiglu / fused_geglu — :191-210, src/kernels/convert.cu:106-148. */
+int jllm_b200_fused_swiglu(void* output, const void* gate, const void* up, int rows, int intermediate_dim, void* stream);
+int jllm_b200_fused_geglu(void* output, const void* gate, const void* up, int rows, int intermediate_dim, void* stream);
+/* vec_scale / logit_softcap — :213-216, convert.cu:152-181. */
+int jllm_b200_vec_scale(void* x, int n, float s, void* stream);
+int jllm_b200_logit_softcap(float* x, int n, float cap, void* stream);
+/* softmax_inplace — :406-410, src/kernels/softmax.cu:76-82. */
+int jllm_b200_softmax_inplace(float* x, int n, void* stream);
+/* fp16_to_int8 — :413-420, convert.cu:71-75.  One absmax scale per row. */
+int jllm_b200_fp16_to_int8(int8_t* dst, float* scale_out, const void* src, int rows, int cols, void* stream);
+
+/* ── RoPE — :238-316, src/kernels/rope.cu ─────────────────────────────────── */
+int jllm_b200_rope_precompute_table(int max_seq, int head_dim, float theta_base);
+int jllm_b200_rope_clear_tables(void);
+int jllm_b200_rope_inplace(void* q, void* k, int n_heads, int n_kv_heads, int head_dim, int position, float theta_base, int neox, void* stream);
+int jllm_b200_rope_inplace_store_kv_fp16(void* q, void* k, const void* v, void* k_cache_dst, void* v_cache_dst, int n_heads,
+                                         int n_kv_heads, int head_dim, int position, float theta_base, int neox, void* stream);
+int jllm_b200_rope_inplace_batched(void* q, void* k, int n_heads, int n_kv_heads, int head_dim, int start_pos, int N,
+                                   int q_stride, int k_stride, float theta_base, int neox, void* stream);
+int jllm_b200_rope_inplace_store_kv_fp16_batched(void* q, void* k, const void* v, void* k_cache_base, void* v_cache_base, int kv_slot,
+                                                 int n_heads, int n_kv_heads, int head_dim, int start_pos, int N, int q_stride,
+                                                 int kv_stride, float theta_base, int neox, void* stream);
+int jllm_b200_rope_inplace_store_kv_fp16_dyn(void* q, void* k, const void* v, void* k_cache_layer_base, void* v_cache_layer_base,
+                                             int n_heads, int n_kv_heads, int head_dim, int cache_head_dim, const int* d_pos,
+                                             float theta_base, int neox, void* stream);
+int jllm_b200_rope_inplace_dyn(void* q, void* k, int n_heads, int n_kv_heads, int head_dim, const int* d_pos, float theta_base,
+                               int neox, void* stream);
+
+/* ── attention ───────────────────────────────────────────────────────────── */
+/* flash_attention_decode — :323-342, src/kernels/attention.cu:1036-1137.  k_scales / v_scales are fp32,
+ * indexed [pos * n_kv_heads + kv_head] (null for FP16 KV). */
+int jllm_b200_flash_attention_decode(void* output, const void* q, const void* k_cache, const void* v_cache, int n_heads,
+                                     int n_kv_heads, int head_dim, int cache_head_dim, int seq_len, float scale, int kv_int8,
+                                     const float* k_scales, const float* v_scales, int window, void* stream);
+/* flash_attention_prefill_batched — :354-373, attention.cu:617-697. */
+int jllm_b200_flash_attention_prefill_batched(void* output, const void* q, const void* k_cache, const void* v_cache, int n_heads,
+                                              int n_kv_heads, int head_dim, int cache_head_dim, int N, int start_pos, float scale,
+                                              int kv_int8, const float* k_scales, const float* v_scales, int window, void* stream);
+/* flash_attention_decode_dyn — :380-396, attention.cu:1007-1034.  seq_len = *d_pos + 1. */
+int jllm_b200_flash_attention_decode_dyn(void* output, const void* q, const void* k_cache, const void* v_cache, int n_heads,
+                                         int n_kv_heads, int head_dim, int cache_head_dim, const int* d_pos, float scale, int kv_int8,
+                                         const float* kv_scales, int window, int n_splits, void* stream);
+/* decode_attn_splits / get_splitk_partials — :402-403, attention.cu:975-1005. */
+int    jllm_b200_decode_attn_splits(int seq_len);
+float* jllm_b200_get_splitk_partials(int n_heads, int n_splits, int head_dim);
+
+/* ── memory pools — include/jllm_memory.h:104-222, src/memory/kv_cache.cpp, pool.cpp ──
+ * Opaque handles over the C++ classes jllm::KVCachePool / jllm::ScratchPool (same object
+ * layout as the reference's, see jllm_b200_api.hpp). */
+typedef struct jllm_b200_kv_pool jllm_b200_kv_pool;
+typedef struct jllm_b200_scratch jllm_b200_scratch;
+jllm_b200_kv_pool* jllm_b200_kv_pool_create(int n_layers, int n_kv_heads, int head_dim, int max_context, int overflow_context, int kv_type_bytes);
+void     jllm_b200_kv_pool_destroy(jllm_b200_kv_pool* p);
+void*    jllm_b200_kv_pool_key_ptr(jllm_b200_kv_pool* p, int layer, int pos);
+void*    jllm_b200_kv_pool_val_ptr(jllm_b200_kv_pool* p, int layer, int pos);
+float*   jllm_b200_kv_pool_scale_ptr(jllm_b200_kv_pool* p, int layer, int pos, int is_value);
+int64_t  jllm_b200_kv_pool_scales_bytes(jllm_b200_kv_pool* p);
+int64_t  jllm_b200_kv_pool_capacity_bytes(jllm_b200_kv_pool* p);
+int64_t  jllm_b200_kv_pool_used_bytes(jllm_b200_kv_pool* p);
+int64_t  jllm_b200_kv_pool_packed_used_bytes(jllm_b200_kv_pool* p, int used_tokens);
+int      jllm_b200_kv_pool_gather_used_to_host(jllm_b200_kv_pool* p, void* host_dst, int used_tokens);
+int      jllm_b200_kv_pool_scatter_from_host(jllm_b200_kv_pool* p, const void* host_src, int used_tokens, int zero_remaining);
+int      jllm_b200_kv_pool_used_tokens(jllm_b200_kv_pool* p);
+void     jllm_b200_kv_pool_clear(jllm_b200_kv_pool* p);
+jllm_b200_scratch* jllm_b200_scratch_create(int64_t size_bytes);
+void     jllm_b200_scratch_destroy(jllm_b200_scratch* s);
+void*    jllm_b200_scratch_get(jllm_b200_scratch* s, int64_t size);
+void     jllm_b200_scratch_reset(jllm_b200_scratch* s);
+int64_t  jllm_b200_scratch_mark(jllm_b200_scratch* s);
+void     jllm_b200_scratch_rewind_to(jllm_b200_scratch* s, int64_t saved);
+int64_t  jllm_b200_scratch_used(jllm_b200_scratch* s);
+int64_t  jllm_b200_scratch_capacity(jllm_b200_scratch* s);
+
+/* ══ extension entry points (no counterpart in the reference API) ══════════ */
+/* Integer accumulators of the dp4a GEMV path for one matrix: dots[M][K/32] (Q4_K: Σ over a
+ * 32-element sub-block of q4*q8) or dots[M][K/16] (Q6_K: Σ over a 16-element scale group of
+ * (q6-32)*q8), written by the same kernel that produces y (used by the bit-exactness tests). */
+int jllm_b200_gemv_quant_int_dots(void* y, int32_t* dots, const void* W, int ggml_type, const void* x, int M, int K, void* stream);
+/* Same for the batched GEMM: dots[N][M][K/32] or [N][M][K/16]. */
+int jllm_b200_gemm_quant_batched_int_dots(void* y, int32_t* dots, const void* W, int ggml_type, const void* x, int M, int N, int K, void* stream);
+/* RMSNorm fused into the shared-activation GEMVs: x := half(x * rrms * w) is formed in shared
+ * memory and quantised there, equal to fused_rmsnorm_residual -> gemv_quant_pair / _triple. */
+int jllm_b200_norm_gemv_quant_pair(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,
+                                   const void* x, const void* norm_weight, int weight_fp32, float eps, int K, void* stream);
+int jllm_b200_norm_gemv_quant_triple(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,
+                                     void* y2, const void* W2, int type2, int M2, const void* x, const void* norm_weight,
+                                     int weight_fp32, float eps, int K, void* stream);
+/* gate/up pair with the SwiGLU applied in the epilogue: out[M] = silu(half(Wg.x)) * half(Wu.x). */
+int jllm_b200_norm_gemv_pair_swiglu(void* out, const void* Wgate, const void* Wup, int type, int M, const void* x,
+                                    const void* norm_weight, int weight_fp32, float eps, int K, void* stream);
+/* Per-head RMSNorm of q and k (weights fp32, may be null), RoPE, and int8 quantisation of the new
+ * K and V rows into the cache at `position` (or *d_pos) — the five launches of
+ * Engine::transformer_layer_attn_compute (src/engine/decode.cu:1443-1478) in one. */
+int jllm_b200_qkv_prep_int8(void* q, const void* k, const void* v, const float* q_norm, const float* k_norm, float eps,
+                            int8_t* k_cache_layer, int8_t* v_cache_layer, float* k_scales_layer, float* v_scales_layer,
+                            int n_heads, int n_kv_heads, int head_dim, int position, const int* d_pos, float theta_base,
+                            int neox, void* stream);
+/* Ragged batched decode attention: sequence b has its own cache bases and length (device arrays of
+ * `batch` entries); q/out are [batch][n_heads][head_dim].  Equals a loop over flash_attention_decode. */
+int jllm_b200_flash_attention_decode_batched(void* output, const void* q, const void* const* k_list, const void* const* v_list,
+                                             const float* const* ks_list, const float* const* vs_list, const int* seq_lens,
+                                             int batch, int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                             int kv_int8, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JLLM_B200_H */

@@ -1,0 +1,66 @@
+"""GPU parity of the batched K-quant GEMM (prefill) against the oracle and the reference's own
+golden vectors (tests/golden/q4k_int8.npz, q6k_int8.npz)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from gpu_util import pkg, dev, close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("t,M,N,K", [(12, 128, 16, 512), (12, 130, 7, 1024), (12, 64, 65, 2560), (14, 128, 16, 512), (14, 33, 9, 2560),
+                                      (14, 20, 3, 9728), (13, 16, 3, 512)])
+def test_gemm_quant_batched_matches_oracle(t, M, N, K):
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1003 + M + N))
+    W = orc.gen_weight(rng, t, M, K)
+    X = orc.gen_act(rng, N * K)
+    y = torch.zeros(N * M, dtype=torch.float16, device="cuda")
+    jb.gemm_quant_batched(y, dev(W), t, dev(X), M, N, K)
+    want = orc.entry_gemm_quant_batched(W, t, X, M, N, K).astype(np.float32).reshape(-1)
+    ok, md = close(y.float().cpu().numpy(), want)
+    assert ok, md
+
+
+@pytest.mark.parametrize("t,M,N,K", [(12, 40, 5, 768), (14, 24, 6, 512)])
+def test_gemm_integer_accumulators_bit_exact(t, M, N, K):
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1004 + M))
+    W = orc.gen_weight(rng, t, M, K)
+    X = orc.gen_act(rng, N * K)
+    G = K // 32 if t == 12 else K // 16
+    dots = torch.zeros((N, M, G), dtype=torch.int32, device="cuda")
+    y = torch.zeros(N * M, dtype=torch.float16, device="cuda")
+    jb.gemm_quant_batched_int_dots(y, dots, dev(W), t, dev(X), M, N, K)
+    assert np.array_equal(dots.cpu().numpy(), orc.mmq_int_dots(W, t, X, M, N, K))
+
+
+@pytest.mark.parametrize("name,t", [("q4k_int8.npz", 12), ("q6k_int8.npz", 14)])
+def test_reference_golden_vectors(golden_dir, name, t):
+    """The reference's own acceptance bar for its int8 GEMM: every |Δ| <= 0.5 against its int8 host model
+    (tests/test_mmq_q4k_int8.cu:533-541, tests/test_mmq_q6k_int8.cu:298-310)."""
+    import torch
+    jb = pkg()
+    g = np.load(os.path.join(golden_dir, name))
+    M, N, K = map(int, g["shape"])
+    y = torch.zeros(N * M, dtype=torch.float16, device="cuda")
+    jb.gemm_quant_batched(y, dev(g["W"]), t, dev(g["X"].view(np.float16)), M, N, K)
+    ref = g["Y_int8"].view(np.float16).astype(np.float32)
+    assert np.max(np.abs(y.float().cpu().numpy() - ref)) <= 0.5
+
+
+def test_n_equal_one_routes_to_gemv():
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1005))
+    M, K = 77, 1024
+    W = dev(orc.gen_weight(rng, 12, M, K)); x = dev(orc.gen_act(rng, K))
+    a = torch.zeros(M, dtype=torch.float16, device="cuda"); b = torch.zeros_like(a)
+    jb.gemm_quant_batched(a, W, 12, x, M, 1, K)
+    jb.gemv_quant(b, W, 12, x, M, K)
+    assert torch.equal(a, b)
