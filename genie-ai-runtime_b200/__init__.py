@@ -81,3 +81,4 @@ def device_status(stream=None):
 
 from .kernels import *  # noqa: E402,F401,F403
 from .pools import KVCachePool, ScratchPool  # noqa: E402,F401
+from . import decoder  # noqa: E402,F401

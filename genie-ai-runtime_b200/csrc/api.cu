@@ -319,7 +319,7 @@ int jllm_b200_norm_gemv_pair_swiglu(void* out, const void* Wg, const void* Wu, i
 }
 int jllm_b200_qkv_prep_int8(void* q, const void* k, const void* v, const float* qn, const float* kn, float eps, int8_t* kc, int8_t* vc,
                             float* ksc, float* vsc, int nh, int nkv, int hd, int pos, const int* d_pos, float th, int neox, void* s) {
-    return launch_qkv_prep(H(q), CH(k), CH(v), qn, kn, eps, kc, vc, ksc, vsc, nh, nkv, hd, pos, d_pos, th, neox != 0, ST(s));
+    return launch_qkv_prep(H(q), CH(k), CH(v), qn, kn, eps, kc, vc, ksc, vsc, nh, nkv, hd, pos, d_pos, th, neox != 0, true, ST(s));
 }
 int jllm_b200_flash_attention_decode_batched(void* o, const void* q, const void* const* kl, const void* const* vl, const float* const* ksl,
                                              const float* const* vsl, const int* seq_lens, int batch, int max_seq, int nh, int nkv, int hd,

@@ -1,0 +1,269 @@
+// decoder.cu — host-side sequencing of one decode step (and greedy generation) over the kernel
+// API, with the token and the position kept in device memory so that a single captured CUDA
+// graph serves every step.  Order of operations follows the reference engine:
+// Engine::decode_step (src/engine/decode.cu:2101-2194), transformer_layer (:1169-1246),
+// transformer_layer_attn_compute (:1437-1497), attn/ffn exits (:1499-1522).
+#include "../../include/jllm_b200.h"
+#include "../../include/jllm_b200_api.hpp"
+#include "common.cuh"
+#include "gemv.cuh"
+#include "elementwise.cuh"
+#include "attention.cuh"
+#include <cfloat>
+#include <new>
+#include <vector>
+
+namespace jb {
+
+// greedy argmax over fp32 logits; also advances the device-side step state:
+// state[0] = position, state[1] = current token, state[2] = number of tokens written to `out`.
+__global__ void argmax_advance_kernel(const float* logits, int n, int* state, int* out, int out_cap) {
+    pdl_wait();
+    __shared__ float sv[32]; __shared__ int si[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float best = -INFINITY; int bi = 0x7FFFFFFF;
+    for (int i = tid; i < n; i += blockDim.x) {
+        const float v = logits[i];
+        if (isfinite(v) && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o); const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        if (bi == 0x7FFFFFFF) bi = 0;
+        const int k = state[2];
+        if (out && k < out_cap) out[k] = bi;
+        state[2] = k + 1;
+        state[1] = bi;
+        state[0] = state[0] + 1;
+    }
+}
+
+__global__ void set_state_kernel(int* state, int pos, int token) {
+    pdl_wait();
+    if (threadIdx.x == 0) { state[0] = pos; state[1] = token; }
+}
+// prompt feeding inside a graph: token for this step comes from a device list
+__global__ void next_prompt_kernel(int* state, const int* prompt, int idx_base) {
+    pdl_wait();
+    if (threadIdx.x == 0) { const int p = state[0]; state[1] = prompt[p - idx_base]; }
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+struct jllm_b200_decoder {
+    jllm_b200_model_desc m;
+    std::vector<jllm_b200_layer_desc> layers;
+    jllm::KVCachePool kv;
+    bool fused = true, use_graph = false;
+    __half *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *gate = nullptr, *up = nullptr, *sw = nullptr;
+    float* logits = nullptr;
+    int* state = nullptr;       // [pos, token, n_out]
+    int* out_tokens = nullptr; int out_cap = 0;
+    int* prompt_dev = nullptr; int prompt_cap = 0;
+    cudaGraphExec_t graph_exec = nullptr; int graph_splits = 0;
+    cudaStream_t own_stream = nullptr;   // used when the caller passes the legacy default stream, which cannot be captured
+    int kernels_per_step = 0;
+    void* slab = nullptr;
+};
+
+static int dec_alloc(jllm_b200_decoder* d) {
+    const jllm_b200_model_desc& m = d->m;
+    const size_t H = m.hidden_dim, QD = (size_t)m.n_heads * m.head_dim, KVD = (size_t)m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
+    auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t total = 3 * al(H * 2) + 2 * al(QD * 2) + 2 * al(KVD * 2) + 3 * al(I * 2) + al((size_t)m.vocab_size * 4) + al(64) +
+                         al((size_t)(m.max_context + 8) * 4) * 2;
+    if (cudaMalloc(&d->slab, total) != cudaSuccess) { cudaGetLastError(); return set_error(JB_ERR_NOMEM, "decoder: %zu B of activations", total); }
+    cudaMemset(d->slab, 0, total);
+    char* p = (char*)d->slab;
+    auto take = [&](size_t b) { char* r = p; p += al(b); return r; };
+    d->x = (__half*)take(H * 2); d->x2 = (__half*)take(H * 2); d->normed = (__half*)take(H * 2);
+    d->q = (__half*)take(QD * 2); d->att = (__half*)take(QD * 2);
+    d->k = (__half*)take(KVD * 2); d->v = (__half*)take(KVD * 2);
+    d->gate = (__half*)take(I * 2); d->up = (__half*)take(I * 2); d->sw = (__half*)take(I * 2);
+    d->logits = (float*)take((size_t)m.vocab_size * 4);
+    d->state = (int*)take(64);
+    d->out_cap = m.max_context + 8; d->out_tokens = (int*)take((size_t)d->out_cap * 4);
+    d->prompt_cap = m.max_context + 8; d->prompt_dev = (int*)take((size_t)d->prompt_cap * 4);
+    return JB_OK;
+}
+
+#define DCHK(call) do { const int rc__ = (call); if (rc__) return rc__; } while (0)
+
+// Enqueues one decode step that reads position and token from d->state.  n_splits is fixed per
+// enqueue (a captured graph keeps the value it was captured with).
+static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
+    const jllm_b200_model_desc& m = d->m;
+    const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, KVD = m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
+    const int* d_pos = d->state; const int* d_tok = d->state + 1;
+    const float scale = 1.0f / sqrtf((float)m.head_dim);
+    const long long l0 = jllm_b200_launch_count();
+    DCHK(launch_embed_row(d->x, m.tok_embd, m.embd_type, 0, d_tok, H, st));
+    for (int l = 0; l < m.n_layers; ++l) {
+        const jllm_b200_layer_desc& w = d->layers[l];
+        int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
+        float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
+        if (d->fused) {
+            DCHK(jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD, d->k, w.wk, w.type_wk, KVD, d->v, w.wv, w.type_wv, KVD,
+                                                  d->x, w.rms_attn, 1, m.rms_eps, H, st));
+            DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, m.n_heads, m.n_kv_heads, m.head_dim,
+                                 0, d_pos, m.rope_theta, m.rope_neox != 0, true, st));
+        } else {
+            DCHK(launch_rmsnorm(d->normed, d->x, nullptr, w.rms_attn, true, 1, H, m.rms_eps, st));
+            DCHK(jllm_b200_gemv_quant_triple(d->q, w.wq, w.type_wq, QD, d->k, w.wk, w.type_wk, KVD, d->v, w.wv, w.type_wv, KVD, d->normed, H, st));
+            if (w.q_norm && w.k_norm) {
+                DCHK(launch_rmsnorm(d->q, d->q, nullptr, w.q_norm, true, m.n_heads, m.head_dim, m.rms_eps, st));
+                DCHK(launch_rmsnorm(d->k, d->k, nullptr, w.k_norm, true, m.n_kv_heads, m.head_dim, m.rms_eps, st));
+            }
+            DCHK(launch_rope(d->q, d->k, nullptr, nullptr, nullptr, m.n_heads, m.n_kv_heads, m.head_dim, m.head_dim, 0, d_pos, m.rope_theta,
+                             m.rope_neox != 0, 1, 0, 0, 0, false, st));
+            // K/V rows of this step: one absmax scale per kv head, written at *d_pos (fp16_to_int8 arithmetic;
+            // norms and rotation are already applied, so the prep kernel only quantises)
+            DCHK(launch_qkv_prep(d->q, d->k, d->v, nullptr, nullptr, m.rms_eps, kc, vc, ks, vs, 0, m.n_kv_heads, m.head_dim, 0, d_pos,
+                                 m.rope_theta, m.rope_neox != 0, false, st));
+        }
+        AttnCall c;
+        c.out = d->att; c.q = d->q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads;
+        c.hd = m.head_dim; c.chd = m.head_dim; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
+        DCHK(launch_attention(c, st));
+        DCHK(jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, d->att, d->x, H, QD, st));
+        if (d->fused) {
+            DCHK(jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, I, d->x2, w.rms_ffn, 1, m.rms_eps, H, st));
+        } else {
+            DCHK(launch_rmsnorm(d->normed, d->x2, nullptr, w.rms_ffn, true, 1, H, m.rms_eps, st));
+            DCHK(jllm_b200_gemv_quant_pair(d->gate, w.w_gate, w.type_w_gate, I, d->up, w.w_up, w.type_w_up, I, d->normed, H, st));
+            DCHK(launch_glu(d->sw, d->gate, d->up, 1, I, false, st));
+        }
+        DCHK(jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, d->sw, d->x2, H, I, st));
+    }
+    DCHK(launch_rmsnorm(d->normed, d->x, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
+    DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, m.vocab_size, H, st));
+    JB_CUDA(launch_k(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, pdl_enabled(), (const float*)d->logits, m.vocab_size, d->state,
+                     d->out_tokens, d->out_cap));
+    count_launch();
+    d->kernels_per_step = (int)(jllm_b200_launch_count() - l0);
+    return JB_OK;
+}
+
+static int splits_for_ctx(const jllm_b200_decoder* d, int upto_pos) { return attn_splits_for(upto_pos + 1); }
+
+extern "C" {
+
+jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, int flags) {
+    if (!model || !model->layers || model->n_layers <= 0) { set_error(JB_ERR_ARG, "decoder: empty model description"); return nullptr; }
+    if (model->hidden_dim % QK_K || model->intermediate_dim % QK_K || (model->n_heads * model->head_dim) % QK_K) {
+        set_error(JB_ERR_ARG, "decoder: hidden/intermediate/q dims must be multiples of 256"); return nullptr;
+    }
+    if (!ctx()) return nullptr;
+    jllm_b200_decoder* d = new (std::nothrow) jllm_b200_decoder();
+    if (!d) return nullptr;
+    d->m = *model;
+    d->layers.assign(model->layers, model->layers + model->n_layers);
+    d->m.layers = d->layers.data();
+    d->fused = (flags & 1) != 0; d->use_graph = (flags & 2) != 0;
+    jllm::KVCachePool::Config c = { model->n_layers, model->n_kv_heads, model->head_dim, model->max_context, 0, 1 };
+    if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); delete d; return nullptr; }
+    if (dec_alloc(d)) { d->kv.destroy(); delete d; return nullptr; }
+    // scratch that must exist before any graph capture
+    splitk_buffer((size_t)model->n_heads * 64 * (model->head_dim + 2), true);
+    return d;
+}
+void jllm_b200_decoder_destroy(jllm_b200_decoder* d) {
+    if (!d) return;
+    if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
+    if (d->own_stream) cudaStreamDestroy(d->own_stream);
+    if (d->slab) cudaFree(d->slab);
+    d->kv.destroy();
+    delete d;
+}
+int jllm_b200_decoder_reset(jllm_b200_decoder* d) {
+    JB_CUDA(cudaMemset(d->state, 0, 64));
+    d->kv.clear();
+    return JB_OK;
+}
+int jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (position < 0 || position >= d->m.max_context) return set_error(JB_ERR_ARG, "decoder: position %d outside the context of %d", position, d->m.max_context);
+    if (token < 0 || token >= d->m.vocab_size) return set_error(JB_ERR_ARG, "decoder: token %d outside the vocabulary", token);
+    JB_CUDA(launch_k(set_state_kernel, dim3(1), dim3(32), 0, st, false, d->state, position, token));
+    count_launch();
+    return dec_enqueue_step(d, splits_for_ctx(d, position), st);
+}
+
+// graph of one step; re-captured when the split count of the attention changes
+static int dec_graph_for(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
+    if (d->graph_exec && d->graph_splits == n_splits) return JB_OK;
+    if (d->graph_exec) { cudaGraphExecDestroy(d->graph_exec); d->graph_exec = nullptr; }
+    cudaGraph_t g = nullptr;
+    JB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    const int rc = dec_enqueue_step(d, n_splits, st);
+    const cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return cuda_error(e, "cudaStreamEndCapture");
+    const cudaError_t ie = cudaGraphInstantiate(&d->graph_exec, g, 0);
+    cudaGraphDestroy(g);
+    if (ie != cudaSuccess) { d->graph_exec = nullptr; return cuda_error(ie, "cudaGraphInstantiate"); }
+    d->graph_splits = n_splits;
+    return JB_OK;
+}
+
+int jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d->use_graph && (st == nullptr || st == cudaStreamLegacy)) {
+        if (!d->own_stream) JB_CUDA(cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking));
+        JB_CUDA(cudaStreamSynchronize(st));          // order after whatever the caller queued on the default stream
+        st = d->own_stream; stream = (void*)st;
+    }
+    if (n_prompt <= 0 || n_new < 0 || !host_prompt) return set_error(JB_ERR_ARG, "decoder: n_prompt=%d n_new=%d", n_prompt, n_new);
+    if (n_prompt + n_new > d->m.max_context) return set_error(JB_ERR_LIMIT, "decoder: %d tokens exceed the context of %d", n_prompt + n_new, d->m.max_context);
+    for (int i = 0; i < n_prompt; ++i)
+        if (host_prompt[i] < 0 || host_prompt[i] >= d->m.vocab_size) return set_error(JB_ERR_ARG, "decoder: prompt token %d outside the vocabulary", host_prompt[i]);
+    JB_CUDA(cudaMemcpyAsync(d->prompt_dev, host_prompt, (size_t)n_prompt * sizeof(int), cudaMemcpyHostToDevice, st));
+    JB_CUDA(cudaMemsetAsync(d->state, 0, 64, st));
+    d->kv.clear();
+    // steps 0 .. n_prompt-1 consume prompt tokens; every step's argmax is recorded, the first n_prompt-1 are discarded below
+    const int total_steps = n_prompt + (n_new > 0 ? n_new - 1 : 0);
+    for (int s = 0; s < total_steps; ++s) {
+        if (s < n_prompt) {
+            JB_CUDA(launch_k(next_prompt_kernel, dim3(1), dim3(32), 0, st, false, d->state, (const int*)d->prompt_dev, 0));
+            count_launch();
+        }
+        const int ns = splits_for_ctx(d, s);
+        if (d->use_graph) {
+            DCHK(dec_graph_for(d, ns, st));
+            JB_CUDA(cudaGraphLaunch(d->graph_exec, st));
+            count_launch(d->kernels_per_step);
+        } else {
+            DCHK(dec_enqueue_step(d, ns, st));
+        }
+    }
+    if (n_new > 0 && host_out)
+        JB_CUDA(cudaMemcpyAsync(host_out, d->out_tokens + (n_prompt - 1), (size_t)n_new * sizeof(int), cudaMemcpyDeviceToHost, st));
+    JB_CUDA(cudaStreamSynchronize(st));
+    return jllm_b200_device_status(stream);
+}
+const float* jllm_b200_decoder_logits(jllm_b200_decoder* d) { return d->logits; }
+int jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream) {
+    int h[3] = { 0, 0, 0 };
+    if (cudaMemcpyAsync(h, d->state, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess) return -1;
+    cudaStreamSynchronize((cudaStream_t)stream);
+    return h[1];
+}
+int jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d) { return d->kernels_per_step; }
+const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which) {
+    switch (which) {
+        case 0: return d->x;   case 1: return d->x2; case 2: return d->q;  case 3: return d->k; case 4: return d->v;
+        case 5: return d->att; case 6: return d->sw; case 7: return d->kv.key_ptr(0, 0); case 8: return d->kv.kv_scale_ptr(0, 0, false);
+        default: return nullptr;
+    }
+}
+
+}  // extern "C"

@@ -353,7 +353,7 @@ struct QkvPrepArgs {
     __half* q; const __half* k; const __half* v;
     const float* q_norm; const float* k_norm; float eps;
     int8_t* k_cache; int8_t* v_cache; float* k_scales; float* v_scales;   // layer bases, position 0
-    int n_heads, n_kv, hd, pos; const int* d_pos; int neox;
+    int n_heads, n_kv, hd, pos; const int* d_pos; int neox; int do_rope;
 };
 __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ RopeFreq fr) {
     pdl_wait();
@@ -379,7 +379,7 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
             for (int i = lane; i < hd; i += 32) buf[i] = __half2float(src[i]);
         }
         __syncwarp();
-        for (int pr = lane; pr < h2; pr += 32) {
+        for (int pr = lane; a.do_rope && pr < h2; pr += 32) {
             const float ang = __fmul_rn((float)pos, fr.f[pr]);
             const float c = cosf(ang), s = sinf(ang);
             const int i0 = a.neox ? pr : 2 * pr, i1 = a.neox ? pr + h2 : 2 * pr + 1;
@@ -406,10 +406,10 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
 }
 int launch_qkv_prep(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
                     int8_t* k_cache, int8_t* v_cache, float* k_scales, float* v_scales, int n_heads, int n_kv, int hd,
-                    int pos, const int* d_pos, float theta, bool neox, cudaStream_t st) {
+                    int pos, const int* d_pos, float theta, bool neox, bool do_rope, cudaStream_t st) {
     if (!q || !k || !v || !k_cache || !v_cache || !k_scales || !v_scales) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
     if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
-    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, pos, d_pos, (int)neox };
+    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, pos, d_pos, (int)neox, (int)do_rope };
     const int warps = n_heads + 2 * n_kv;
     JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
     count_launch();

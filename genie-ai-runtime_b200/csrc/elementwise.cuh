@@ -23,6 +23,6 @@ int launch_embed_row(__half* dst, const void* W, int type, int token, const int*
 int launch_dense(__half* out, const void* W, int wtype, const __half* x, int M, int N, int K, cudaStream_t st);
 int launch_qkv_prep(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
                     int8_t* k_cache, int8_t* v_cache, float* k_scales, float* v_scales, int n_heads, int n_kv, int hd,
-                    int pos, const int* d_pos, float theta, bool neox, cudaStream_t st);
+                    int pos, const int* d_pos, float theta, bool neox, bool do_rope, cudaStream_t st);
 
 }  // namespace jb

@@ -1,0 +1,100 @@
+"""Decoder session over the C ABI (jllm_b200_decoder_*): the reference engine's per-token kernel
+sequence (src/engine/decode.cu:1169-1246, :2101-2194) with greedy sampling on the device."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib, _stream, check, JllmError, last_error
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")] + \
+               [(n, C.c_int) for n in ("type_wq", "type_wk", "type_wv", "type_wo", "type_w_gate", "type_w_up", "type_w_down")] + \
+               [(n, C.c_void_p) for n in ("rms_attn", "rms_ffn", "q_norm", "k_norm")]
+
+
+class ModelDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_layers", "hidden_dim", "n_heads", "n_kv_heads", "head_dim", "intermediate_dim", "vocab_size",
+                                        "max_context")] + \
+               [("rope_theta", C.c_float), ("rms_eps", C.c_float), ("rope_neox", C.c_int),
+                ("tok_embd", C.c_void_p), ("embd_type", C.c_int), ("output", C.c_void_p), ("output_type", C.c_int),
+                ("output_norm", C.c_void_p), ("layers", C.POINTER(LayerDesc))]
+
+
+lib.jllm_b200_decoder_create.restype = C.c_void_p
+lib.jllm_b200_decoder_logits.restype = C.c_void_p
+
+FUSED, GRAPH = 1, 2
+
+
+class Decoder:
+    """`weights` is a dict shaped like oracle.gen_model(): per-layer (uint8 block image, ggml type) pairs
+    and float32 norm vectors, given as torch CUDA tensors (see `upload`)."""
+
+    def __init__(self, cfg, weights, max_context, flags=FUSED | GRAPH):
+        self._keep = weights
+        L = cfg["n_layers"]
+        self._layers = (LayerDesc * L)()
+        names = dict(wq="wq", wk="wk", wv="wv", wo="wo", w_gate="gate", w_up="up", w_down="down")
+        for i, lw in enumerate(weights["layers"]):
+            for f, k in names.items():
+                setattr(self._layers[i], f, lw[k][0].data_ptr())
+                setattr(self._layers[i], "type_" + f, lw[k][1])
+            for k in ("rms_attn", "rms_ffn", "q_norm", "k_norm"):
+                setattr(self._layers[i], k, lw[k].data_ptr() if lw.get(k) is not None else None)
+        m = ModelDesc()
+        m.n_layers, m.hidden_dim, m.n_heads, m.n_kv_heads = L, cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
+        m.head_dim, m.intermediate_dim, m.vocab_size, m.max_context = cfg["head_dim"], cfg["ffn"], cfg["vocab"], max_context
+        m.rope_theta, m.rms_eps, m.rope_neox = cfg["rope_theta"], cfg["eps"], 1
+        m.tok_embd, m.embd_type = weights["tok_embd"][0].data_ptr(), weights["tok_embd"][1]
+        m.output, m.output_type = weights["output"][0].data_ptr(), weights["output"][1]
+        m.output_norm = weights["out_norm"].data_ptr()
+        m.layers = self._layers
+        self.cfg, self.max_context = cfg, max_context
+        self._h = lib.jllm_b200_decoder_create(C.byref(m), C.c_int(flags))
+        if not self._h:
+            raise JllmError(-1, last_error())
+
+    def close(self):
+        if self._h:
+            lib.jllm_b200_decoder_destroy(C.c_void_p(self._h))
+            self._h = None
+
+    def step(self, token, position, stream=None):
+        check(lib.jllm_b200_decoder_step(C.c_void_p(self._h), int(token), int(position), _stream(stream)))
+        return int(lib.jllm_b200_decoder_last_token(C.c_void_p(self._h), _stream(stream)))
+
+    def logits(self):
+        import torch
+        ptr = lib.jllm_b200_decoder_logits(C.c_void_p(self._h))
+        out = torch.empty(self.cfg["vocab"], dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        C.CDLL("libcudart.so").cudaMemcpy(C.c_void_p(out.data_ptr()), C.c_void_p(ptr), C.c_size_t(out.numel() * 4), 3)
+        return out
+
+    def generate(self, prompt, n_new, stream=None):
+        """Host token ids in, host token ids out (both copies happen inside the call)."""
+        p = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(max(n_new, 1), np.int32)
+        check(lib.jllm_b200_decoder_generate(C.c_void_p(self._h), p.ctypes.data_as(C.c_void_p), C.c_int(p.size), C.c_int(n_new),
+                                             out.ctypes.data_as(C.c_void_p), _stream(stream)))
+        return out[:n_new]
+
+    def kernels_per_step(self):
+        return int(lib.jllm_b200_decoder_kernels_per_step(C.c_void_p(self._h)))
+
+
+def upload(model):
+    """oracle.gen_model()-style numpy weights -> the same structure with torch CUDA tensors."""
+    import torch
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = dict(layers=[], tok_embd=(t(model["tok_embd"][0]), model["tok_embd"][1]), output=(t(model["output"][0]), model["output"][1]),
+               out_norm=t(model["out_norm"]))
+    for lw in model["layers"]:
+        d = {}
+        for k, v in lw.items():
+            d[k] = (t(v[0]), v[1]) if isinstance(v, tuple) else t(v)
+        out["layers"].append(d)
+    return out

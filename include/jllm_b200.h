@@ -186,6 +186,46 @@ int jllm_b200_flash_attention_decode_batched(void* output, const void* q, const 
                                              int batch, int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float scale,
                                              int kv_int8, void* stream);
 
+/* ── decoder session (extension; stands where Engine::decode_step / transformer_layer sit,
+ * src/engine/decode.cu:1169-1246, :1437-1530, :2101-2194) ─────────────────────────────
+ * Host-side sequencing of the kernels above for a Qwen3/Llama-shaped decoder with INT8 KV:
+ * per layer RMSNorm -> Q/K/V GEMV -> QK-norm + RoPE + KV int8 store -> decode attention ->
+ * Wo + residual -> RMSNorm -> gate/up GEMV -> SwiGLU -> W_down + residual, then the final norm,
+ * fp32 logits and a greedy argmax on the device (lowest index among equal maxima, non-finite
+ * logits skipped, as sample_greedy does, src/engine/sample.cpp:160-170).  Position and token
+ * live in device memory, so one captured CUDA graph replays for every step. */
+typedef struct {
+    const void *wq, *wk, *wv, *wo, *w_gate, *w_up, *w_down;     /* K-quant block images (device) */
+    int type_wq, type_wk, type_wv, type_wo, type_w_gate, type_w_up, type_w_down;
+    const float *rms_attn, *rms_ffn, *q_norm, *k_norm;          /* fp32 norm weights; q_norm/k_norm may be null */
+} jllm_b200_layer_desc;
+typedef struct {
+    int n_layers, hidden_dim, n_heads, n_kv_heads, head_dim, intermediate_dim, vocab_size, max_context;
+    float rope_theta, rms_eps;
+    int rope_neox;
+    const void* tok_embd; int embd_type;
+    const void* output;   int output_type;
+    const float* output_norm;
+    const jllm_b200_layer_desc* layers;                          /* host array of n_layers entries */
+} jllm_b200_model_desc;
+typedef struct jllm_b200_decoder jllm_b200_decoder;
+/* flags: bit 0 = fused kernels (norm+GEMV, SwiGLU epilogue, one QKV-prep launch) instead of the reference's
+ * launch-for-launch sequence (both give identical bits); bit 1 = replay a captured CUDA graph per step. */
+jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, int flags);
+void   jllm_b200_decoder_destroy(jllm_b200_decoder* d);
+int    jllm_b200_decoder_reset(jllm_b200_decoder* d);
+/* Runs one step for `token` at `position`; logits stay on the device (see _logits); returns the status. */
+int    jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, void* stream);
+/* Feeds `n_prompt` host tokens (one decode step each), then generates `n_new` tokens greedily; the
+ * generated ids are copied to host_out.  Inputs and outputs cross the host/device boundary inside the call. */
+int    jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream);
+const float* jllm_b200_decoder_logits(jllm_b200_decoder* d);     /* device pointer, vocab_size floats */
+int    jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream);   /* argmax of the last step (synchronises) */
+int    jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d);
+/* Internal activation buffers of the last step, for tests: 0 x, 1 x2, 2 q, 3 k, 4 v, 5 attention out, 6 SwiGLU out,
+ * 7 layer-0 K cache, 8 layer-0 K scales. */
+const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);
+
 #ifdef __cplusplus
 }
 #endif

@@ -100,22 +100,23 @@ def pack_q6k(d, sc, q):
     return out
 
 
-def gen_q4k(rng, rows, K):
-    """Q4_K matrix with the benchmark's value distributions: d,dmin=|N(0,1)|*0.01 (fp16),
-    scales/mins U{0..63}, quants U{0..15}.  Returns [rows, K/256*144] uint8."""
+def gen_q4k(rng, rows, K, sigma=0.01, min_ratio=1.0):
+    """Q4_K matrix with the benchmark's value distributions: d=|N(0,1)|*sigma, dmin=|N(0,1)|*sigma*min_ratio (fp16;
+    sigma = 0.01 and min_ratio = 1 in the kernel-level configurations), scales/mins U{0..63}, quants U{0..15}.
+    Returns [rows, K/256*144] uint8."""
     B = rows * (K // 256)
-    d = (np.abs(rng.standard_normal(B)) * 0.01).astype(np.float16)
-    dm = (np.abs(rng.standard_normal(B)) * 0.01).astype(np.float16)
+    d = (np.abs(rng.standard_normal(B)) * sigma).astype(np.float16)
+    dm = (np.abs(rng.standard_normal(B)) * sigma * min_ratio).astype(np.float16)
     sc = rng.integers(0, 64, (B, 8))
     mn = rng.integers(0, 64, (B, 8))
     q = rng.integers(0, 16, (B, 256), dtype=np.uint8)
     return pack_q4k(d, dm, sc, mn, q).reshape(rows, -1)
 
 
-def gen_q6k(rng, rows, K):
-    """Q6_K matrix: d=|N(0,1)|*0.01 (fp16), int8 scales U{-64..63}, quants U{0..63}."""
+def gen_q6k(rng, rows, K, sigma=0.01):
+    """Q6_K matrix: d=|N(0,1)|*sigma (fp16), int8 scales U{-64..63}, quants U{0..63}."""
     B = rows * (K // 256)
-    d = (np.abs(rng.standard_normal(B)) * 0.01).astype(np.float16)
+    d = (np.abs(rng.standard_normal(B)) * sigma).astype(np.float16)
     sc = rng.integers(-64, 64, (B, 16))
     q = rng.integers(0, 64, (B, 256), dtype=np.uint8)
     return pack_q6k(d, sc, q).reshape(rows, -1)
@@ -341,23 +342,41 @@ class _Model(C.Structure):
                 ("kv", C.c_void_p), ("kv_scales", C.c_void_p)]
 
 
+# Whole-model weights.  The kernel-level generator (sigma 0.01, dmin ~ d) gives weights of RMS ~3 with a mean of
+# +1.6: a stacked decoder overflows fp16 inside its first layer (every logit NaN), and even rescaled its common-mode
+# gain makes the network amplify one fp16 ULP into percent-level logit changes.  Model weights therefore use
+# dmin = 7.5 d, which centres d*sc*q - dmin*m on zero (E[q] = 7.5, E[sc] = E[m]), and a sigma that gives W.x unit RMS:
+# Q4_K  E[w^2] = sigma^2 (E[sc^2]E[q^2] + 7.5^2 E[m^2] - 2*7.5 E|N|^2 E[sc]E[m]E[q]) ~ (327 sigma)^2,
+# Q6_K  E[w^2] = sigma^2 * 1365 * 341.5 ~ (683 sigma)^2.
+_W_RMS = {Q4_K: 327.0, Q6_K: 683.0}
+MODEL_MIN_RATIO = 7.5
+
+
+def model_sigma(ggml_type, K):
+    """sigma that makes W.x of a unit-RMS x come out with RMS ~1."""
+    return 1.0 / (_W_RMS[ggml_type] * np.sqrt(K))
+
+
 def gen_model(seed, n_layers=36, hidden=2560, n_heads=32, n_kv=8, hd=128, ffn=9728, vocab=151936):
     """Random-init Qwen3-shaped weights in the benchmark's quant mix: Q4_K everywhere except
-    Q6_K for attn_v, ffn_down and output; F32 norm weights 1+0.02*N(0,1).  Returns a dict of
-    numpy arrays (uint8 block images / float32 norms)."""
+    Q6_K for attn_v, ffn_down and output; F32 norm weights 1+0.02*N(0,1).  Blocks come from the
+    kernel-level generators with d (and dmin) scaled by model_sigma() so activations stay O(1).
+    Returns a dict of numpy arrays (uint8 block images / float32 norms)."""
     rng = np.random.Generator(np.random.PCG64(seed))
     qd, kvd = n_heads * hd, n_kv * hd
+    gen_q4k_u = lambda r, rows, K: gen_q4k(r, rows, K, model_sigma(Q4_K, K), MODEL_MIN_RATIO)
+    gen_q6k_u = lambda r, rows, K: gen_q6k(r, rows, K, model_sigma(Q6_K, K))
     m = dict(cfg=dict(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, ffn=ffn,
                       vocab=vocab, rope_theta=1e6, eps=1e-6), layers=[])
     nrm = lambda n: (1.0 + 0.02 * rng.standard_normal(n)).astype(np.float32)
     for _ in range(n_layers):
         m["layers"].append(dict(
-            wq=(gen_q4k(rng, qd, hidden), Q4_K), wk=(gen_q4k(rng, kvd, hidden), Q4_K), wv=(gen_q6k(rng, kvd, hidden), Q6_K),
-            wo=(gen_q4k(rng, hidden, qd), Q4_K), gate=(gen_q4k(rng, ffn, hidden), Q4_K), up=(gen_q4k(rng, ffn, hidden), Q4_K),
-            down=(gen_q6k(rng, hidden, ffn), Q6_K),
+            wq=(gen_q4k_u(rng, qd, hidden), Q4_K), wk=(gen_q4k_u(rng, kvd, hidden), Q4_K), wv=(gen_q6k_u(rng, kvd, hidden), Q6_K),
+            wo=(gen_q4k_u(rng, hidden, qd), Q4_K), gate=(gen_q4k_u(rng, ffn, hidden), Q4_K), up=(gen_q4k_u(rng, ffn, hidden), Q4_K),
+            down=(gen_q6k_u(rng, hidden, ffn), Q6_K),
             rms_attn=nrm(hidden), rms_ffn=nrm(hidden), q_norm=nrm(hd), k_norm=nrm(hd)))
-    m["tok_embd"] = (gen_q4k(rng, vocab, hidden), Q4_K)
-    m["output"] = (gen_q6k(rng, vocab, hidden), Q6_K)
+    m["tok_embd"] = (gen_q4k_u(rng, vocab, hidden), Q4_K)
+    m["output"] = (gen_q6k_u(rng, vocab, hidden), Q6_K)
     m["out_norm"] = nrm(hidden)
     return m
 

@@ -1,0 +1,98 @@
+"""Whole-decoder parity on a small random-init Qwen3-shaped model: greedy token stream against the CPU
+oracle's, logits within tolerance, fused and launch-for-launch kernel sequences bit-identical, graph
+replay identical to direct launches.
+
+Tolerance note.  Every kernel matches the oracle to an fp16 ULP or better (see the kernel tests), but the
+reference's decode path quantises activations to q8_1 in front of each Q/K/V and gate/up projection: a one-ULP
+difference in a group's largest activation re-rounds that group's 32 codes and moves the projection outputs by
+~1 % of their scale.  Stacked layers therefore differ by a few percent of the logit RMS between any two
+implementations that sum in a different order (the reference's own GPU and CPU paths included), so whole-model
+logits are held to 0.15 x RMS and a greedy stream may only part from the oracle's where the oracle's own top-2
+margin is below that bound; the margin is reported."""
+NOISE = 0.15
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from gpu_util import pkg
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(n_layers=3, hidden=512, n_heads=8, n_kv=2, hd=128, ffn=1024, vocab=3000)
+
+
+@pytest.fixture(scope="module")
+def small_model():
+    m = orc.gen_model(42, **SMALL)
+    return m, pkg().decoder.upload(m)
+
+
+def test_greedy_stream_matches_oracle(small_model):
+    jb = pkg()
+    m, w = small_model
+    rng = np.random.Generator(np.random.PCG64(1004))
+    prompt = rng.integers(0, SMALL["vocab"], 9)
+    n_new, ctx = 24, 64
+    od = orc.Decoder(m, ctx)
+    want = od.generate(prompt, n_new)
+    assert np.all(np.isfinite(od.logits)) and len(set(want)) > 1      # a live model, not an overflowed one
+    streams = {}
+    for flags in (0, jb.decoder.FUSED, jb.decoder.FUSED | jb.decoder.GRAPH):
+        d = jb.decoder.Decoder(m["cfg"], w, ctx, flags)
+        streams[flags] = list(d.generate(prompt, n_new))
+        d.close()
+    assert streams[0] == streams[1] == streams[3], "fused / graph paths changed the stream"
+    got = streams[3]
+    if got != want:
+        s = next(i for i in range(n_new) if got[i] != want[i])
+        # replay the oracle up to the first divergence and look at its margin there
+        od2 = orc.Decoder(m, ctx)
+        seq = list(prompt) + want[:s]
+        for pos, t in enumerate(seq):
+            od2.step(t, pos)
+        lg = od2.logits
+        rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
+        margin = float(lg[want[s]] - lg[got[s]])
+        print(f"stream parts at step {s}: oracle margin {margin:.4f} (logit RMS {rms:.3f})")
+        assert 0 <= margin <= NOISE * rms, (s, margin, rms)
+
+
+def test_logits_match_oracle_and_fused_equals_unfused(small_model):
+    import torch
+    jb = pkg()
+    m, w = small_model
+    ctx = 32
+    o = orc.Decoder(m, ctx)
+    a = jb.decoder.Decoder(m["cfg"], w, ctx, 0)
+    b = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED)
+    toks = [5, 77, 1234, 2999, 0, 13]
+    for pos, t in enumerate(toks):
+        nt_o = o.step(t, pos)
+        nt_a = a.step(t, pos)
+        nt_b = b.step(t, pos)
+        la, lb = a.logits(), b.logits()
+        assert torch.equal(la, lb)                                    # same bits, fewer launches
+        want = o.logits
+        got = la.cpu().numpy()
+        assert np.all(np.isfinite(want)) and np.all(np.isfinite(got))
+        rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        assert np.max(np.abs(got - want)) <= NOISE * rms, (pos, float(np.max(np.abs(got - want))), rms)
+        assert float(np.sqrt(np.mean((got - want) ** 2))) <= 0.05 * rms
+        assert nt_a == nt_b
+        if nt_a != nt_o:                                              # only acceptable at a near tie of the two top logits
+            assert abs(want[nt_a] - want[nt_o]) <= NOISE * rms
+    assert b.kernels_per_step() < a.kernels_per_step()
+    a.close(); b.close()
+
+
+def test_decoder_argument_errors(small_model):
+    jb = pkg()
+    m, w = small_model
+    d = jb.decoder.Decoder(m["cfg"], w, 16, jb.decoder.FUSED)
+    with pytest.raises(jb.JllmError):
+        d.generate(np.arange(10), 10)                 # 20 tokens > context 16
+    with pytest.raises(jb.JllmError):
+        d.generate([SMALL["vocab"] + 1], 2)           # token outside the vocabulary
+    with pytest.raises(jb.JllmError):
+        d.step(1, 16)                                 # position outside the context
+    d.close()
