@@ -70,6 +70,7 @@ struct jllm_b200_decoder {
     int* out_tokens = nullptr; int out_cap = 0;
     int* prompt_dev = nullptr; int prompt_cap = 0;
     cudaGraphExec_t graph_exec = nullptr; int graph_splits = 0;
+    int host_pos = 0;                    // host mirror of the device-side position (next step's position)
     cudaStream_t own_stream = nullptr;   // used when the caller passes the legacy default stream, which cannot be captured
     int kernels_per_step = 0;
     void* slab = nullptr;
@@ -155,6 +156,23 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
 
 static int splits_for_ctx(const jllm_b200_decoder* d, int upto_pos) { return attn_splits_for(upto_pos + 1); }
 
+// graph of one step; re-captured when the split count of the attention changes
+static int dec_graph_for(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
+    if (d->graph_exec && d->graph_splits == n_splits) return JB_OK;
+    if (d->graph_exec) { cudaGraphExecDestroy(d->graph_exec); d->graph_exec = nullptr; }
+    cudaGraph_t g = nullptr;
+    JB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    const int rc = dec_enqueue_step(d, n_splits, st);
+    const cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return cuda_error(e, "cudaStreamEndCapture");
+    const cudaError_t ie = cudaGraphInstantiate(&d->graph_exec, g, 0);
+    cudaGraphDestroy(g);
+    if (ie != cudaSuccess) { d->graph_exec = nullptr; return cuda_error(ie, "cudaGraphInstantiate"); }
+    d->graph_splits = n_splits;
+    return JB_OK;
+}
+
 extern "C" {
 
 jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, int flags) {
@@ -198,23 +216,6 @@ int jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, void* 
     return dec_enqueue_step(d, splits_for_ctx(d, position), st);
 }
 
-// graph of one step; re-captured when the split count of the attention changes
-static int dec_graph_for(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
-    if (d->graph_exec && d->graph_splits == n_splits) return JB_OK;
-    if (d->graph_exec) { cudaGraphExecDestroy(d->graph_exec); d->graph_exec = nullptr; }
-    cudaGraph_t g = nullptr;
-    JB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    const int rc = dec_enqueue_step(d, n_splits, st);
-    const cudaError_t e = cudaStreamEndCapture(st, &g);
-    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
-    if (e != cudaSuccess) return cuda_error(e, "cudaStreamEndCapture");
-    const cudaError_t ie = cudaGraphInstantiate(&d->graph_exec, g, 0);
-    cudaGraphDestroy(g);
-    if (ie != cudaSuccess) { d->graph_exec = nullptr; return cuda_error(ie, "cudaGraphInstantiate"); }
-    d->graph_splits = n_splits;
-    return JB_OK;
-}
-
 int jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (d->use_graph && (st == nullptr || st == cudaStreamLegacy)) {
@@ -249,6 +250,50 @@ int jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int
         JB_CUDA(cudaMemcpyAsync(host_out, d->out_tokens + (n_prompt - 1), (size_t)n_new * sizeof(int), cudaMemcpyDeviceToHost, st));
     JB_CUDA(cudaStreamSynchronize(st));
     return jllm_b200_device_status(stream);
+}
+// One user-facing step: token and position come from (pinned) host memory, the sampled token goes back to
+// host memory, and the call returns when it is there — the per-token host/device boundary of the reference
+// engine (src/engine/decode.cu:2170-2175), minus the 600 KB logits copy (sampling runs on the device).
+int jllm_b200_decoder_step_sync(jllm_b200_decoder* d, const int* host_pos_token, int* host_next, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!host_pos_token || !host_next) return set_error(JB_ERR_PTR, "decoder: null host pointer");
+    if (d->use_graph && (st == nullptr || st == cudaStreamLegacy)) {
+        if (!d->own_stream) JB_CUDA(cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking));
+        st = d->own_stream;
+    }
+    const int pos = host_pos_token[0], tok = host_pos_token[1];
+    if (pos < 0 || pos >= d->m.max_context) return set_error(JB_ERR_ARG, "decoder: position %d outside the context of %d", pos, d->m.max_context);
+    if (tok < 0 || tok >= d->m.vocab_size) return set_error(JB_ERR_ARG, "decoder: token %d outside the vocabulary", tok);
+    JB_CUDA(cudaMemcpyAsync(d->state, host_pos_token, 2 * sizeof(int), cudaMemcpyHostToDevice, st));
+    const int ns = splits_for_ctx(d, pos);
+    if (d->use_graph) {
+        DCHK(dec_graph_for(d, ns, st));
+        JB_CUDA(cudaGraphLaunch(d->graph_exec, st));
+        count_launch(d->kernels_per_step);
+    } else {
+        DCHK(dec_enqueue_step(d, ns, st));
+    }
+    JB_CUDA(cudaMemcpyAsync(host_next, d->state + 1, sizeof(int), cudaMemcpyDeviceToHost, st));
+    JB_CUDA(cudaStreamSynchronize(st));
+    d->host_pos = pos + 1;
+    return JB_OK;
+}
+// Enqueues the next step entirely from device-side state (position and token left by the previous step's argmax);
+// nothing crosses the host boundary and the call does not wait.
+int jllm_b200_decoder_step_device(jllm_b200_decoder* d, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d->use_graph && (st == nullptr || st == cudaStreamLegacy)) return set_error(JB_ERR_ARG, "decoder: graph replay needs a non-default stream");
+    if (d->host_pos >= d->m.max_context) return set_error(JB_ERR_LIMIT, "decoder: context of %d exhausted", d->m.max_context);
+    const int ns = splits_for_ctx(d, d->host_pos);
+    if (d->use_graph) {
+        DCHK(dec_graph_for(d, ns, st));
+        JB_CUDA(cudaGraphLaunch(d->graph_exec, st));
+        count_launch(d->kernels_per_step);
+    } else {
+        DCHK(dec_enqueue_step(d, ns, st));
+    }
+    d->host_pos += 1;
+    return JB_OK;
 }
 const float* jllm_b200_decoder_logits(jllm_b200_decoder* d) { return d->logits; }
 int jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream) {

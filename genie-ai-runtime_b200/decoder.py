@@ -66,6 +66,11 @@ class Decoder:
         check(lib.jllm_b200_decoder_step(C.c_void_p(self._h), int(token), int(position), _stream(stream)))
         return int(lib.jllm_b200_decoder_last_token(C.c_void_p(self._h), _stream(stream)))
 
+    def step_sync(self, host_pos_token, host_next, stream=None):
+        """host_pos_token: pinned int32 tensor [position, token]; host_next: pinned int32 tensor of one element."""
+        check(lib.jllm_b200_decoder_step_sync(C.c_void_p(self._h), C.c_void_p(host_pos_token.data_ptr()), C.c_void_p(host_next.data_ptr()),
+                                              _stream(stream)))
+
     def logits(self):
         import torch
         ptr = lib.jllm_b200_decoder_logits(C.c_void_p(self._h))

@@ -219,6 +219,11 @@ int    jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, voi
 /* Feeds `n_prompt` host tokens (one decode step each), then generates `n_new` tokens greedily; the
  * generated ids are copied to host_out.  Inputs and outputs cross the host/device boundary inside the call. */
 int    jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream);
+/* One step with the host boundary inside: host_pos_token = {position, token} (pinned host memory recommended) is copied
+ * to the device, the step runs, the greedy token is copied to *host_next and the call returns once it has arrived. */
+int    jllm_b200_decoder_step_sync(jllm_b200_decoder* d, const int* host_pos_token, int* host_next, void* stream);
+/* Enqueues the following step from the position and token the previous step left on the device; no host copy, no wait. */
+int    jllm_b200_decoder_step_device(jllm_b200_decoder* d, void* stream);
 const float* jllm_b200_decoder_logits(jllm_b200_decoder* d);     /* device pointer, vocab_size floats */
 int    jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream);   /* argmax of the last step (synchronises) */
 int    jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d);
