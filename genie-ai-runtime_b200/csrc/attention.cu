@@ -188,6 +188,17 @@ int launch_attention_general(const AttnCall& c, cudaStream_t st) {
     return JB_OK;
 }
 
-int launch_attention(const AttnCall& c, cudaStream_t st) { return launch_attention_general(c, st); }
+int launch_attn_reduce(__half* out, const float* part, int n_heads, int hd, int n_splits, int batch, cudaStream_t st) {
+    JB_CUDA(launch_k(attn_reduce_kernel, dim3(n_heads, batch), dim3(128), 0, st, pdl_enabled(), out, part, n_heads, hd, n_splits));
+    count_launch();
+    return JB_OK;
+}
+
+int launch_attention(const AttnCall& c, cudaStream_t st) {
+    if (c.n_heads <= 0 || c.n_kv <= 0 || c.n_heads % c.n_kv) return set_error(JB_ERR_ARG, "attention: n_heads=%d n_kv_heads=%d", c.n_heads, c.n_kv);
+    if (!c.out || !c.q) return set_error(JB_ERR_PTR, "attention: null q/out");
+    if (!c.k_list && (!c.k || !c.v)) return set_error(JB_ERR_PTR, "attention: null cache pointer");
+    return attention_fast_applies(c) ? launch_attention_fast(c, st) : launch_attention_general(c, st);
+}
 
 }  // namespace jb

@@ -21,5 +21,8 @@ int    attn_splits_for(int seq_len);
 float* splitk_buffer(size_t floats, bool may_alloc);
 int    launch_attention_general(const AttnCall& c, cudaStream_t st);
 int    launch_attention(const AttnCall& c, cudaStream_t st);      // picks the fast path when it applies
+int    launch_attn_reduce(__half* out, const float* part, int n_heads, int hd, int n_splits, int batch, cudaStream_t st);
+bool   attention_fast_applies(const AttnCall& c);                 // INT8 KV, head_dim 128, GQA group of 1, 2 or 4, no window
+int    launch_attention_fast(const AttnCall& c, cudaStream_t st);
 
 }  // namespace jb

@@ -25,14 +25,13 @@ namespace jb {
 constexpr int GV_WARPS   = 4;
 constexpr int GV_THREADS = GV_WARPS * 32;
 constexpr int GV_MAXSLOT = 8;
-constexpr int GV_SMEM_BUDGET = 110 * 1024;     // per CTA, two CTAs per SM
 
 struct GvSegDev {
     const uint8_t* W; void* y; int M; int type;
     int rb;          // row bytes
-    int U;           // 16-byte work items per row (Q4_K: 8/block, Q6_K: 4/block)
-    int R;           // rows per warp
-    int trc;         // rows per chunk
+    int U;           // work items per row: 4 per super-block for both types
+    int R;           // rows per warp pass ("row group")
+    int trc;         // rows per chunk = GV_WARPS * R
 };
 struct GvParams {
     GvSegDev seg[3]; int nseg;
@@ -42,15 +41,15 @@ struct GvParams {
     int32_t* dbg_dots; int* status;
     int slot_bytes, nslots, needA, needB, paired_rows;
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
-    long long total_bytes;
+    long long total_bytes;      // Σ over segments of (row groups x bytes per group)
 };
 
 // ── activation staging ───────────────────────────────────────────────────
-// Layout A (read by Q4_K items), per 256 elements: [8 runs of 16 low-nibble partners]
-// [8 runs of 16 high-nibble partners]: element e = 32j + 16h + i (sub-block j, half h)
-// lands at (j&1)*128 + (2*(j>>1)+h)*16 + i.  Layout B (Q6_K items): plane k (= 32-wide
-// quarter of a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a second
-// plane with the low bytes follows at +K.
+// Layout A (read by Q4_K items), per 256 elements: the 16-element run r = 2*(j>>1)+h of sub-block j = 2*il + p
+// (p = 0: low-nibble partners, p = 1: high-nibble partners) sits at p*128 + (16*r ^ 16*(blk&1)) — the xor keeps
+// the 16-byte reads of eight neighbouring lanes (two blocks x four il) on different banks.  Layout B (Q6_K
+// items): plane k (= 32-wide quarter of a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a
+// second plane with the low bytes follows at +K.
 template <int XM>
 __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -125,7 +124,7 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         }
         if (p.needA) {
             const int j = r >> 5, wi = r & 31, h = wi >> 4, i = wi & 15;
-            const int off = blk * 256 + (j & 1) * 128 + (2 * (j >> 1) + h) * 16 + i;
+            const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4)) + i;
             *reinterpret_cast<uint32_t*>(xA + off) = w_hi;
             if (XM == 1) *reinterpret_cast<uint32_t*>(xA + K + off) = w_lo;
         }
@@ -148,52 +147,56 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     }
 }
 
-// ── Q4_K: one 16-byte run of quants per lane ─────────────────────────────
-// Run u (0..7) of a block holds the low nibbles of sub-block 2*(u>>1) (elements
-// 16*(u&1)..+15) and the high nibbles of sub-block 2*(u>>1)+1.  Lanes u and u^1
-// exchange one partial so that each ends with the complete 32-element integer dot of
-// sub-block u — the same accumulator the reference builds with eight dp4a
-// (src/kernels/gemv_q4.cu:487-494) — and applies  dall*sc*(d8*dot) - dmin*m*s8  (:499).
+__device__ __forceinline__ int dot16_us(const uint4& w, uint32_t mask, const int4& x) {
+    int d = dp4a_us(w.x & mask, x.x, 0); d = dp4a_us(w.y & mask, x.y, d);
+    d = dp4a_us(w.z & mask, x.z, d);     return dp4a_us(w.w & mask, x.w, d);
+}
+__device__ __forceinline__ int dot16_uu(const uint4& w, uint32_t mask, const uint4& x) {
+    int d = dp4a_uu(w.x & mask, x.x, 0); d = dp4a_uu(w.y & mask, x.y, d);
+    d = dp4a_uu(w.z & mask, x.z, d);     return dp4a_uu(w.w & mask, x.w, d);
+}
+
+// ── Q4_K: one 32-byte group of quants per lane ───────────────────────────
+// Group il (0..3) of a block holds the low nibbles of sub-block 2*il and the high nibbles of sub-block
+// 2*il+1, 32 elements each.  The lane builds both complete 32-element integer dots — the accumulators the
+// reference builds with eight dp4a each (src/kernels/gemv_q4.cu:487-494) — and folds them as
+//   dall * (sc0*dot0*d8_0 + sc1*dot1*d8_1) - dmin * (m0*s8_0 + m1*s8_1)
+// which is the reference's  Σ dall*sc*(d8*dot) - dmin*m*s8  (:499) with the common factors taken out.
 template <int XM>
-__device__ __forceinline__ float q4k_item(const uint8_t* sb, int u, int kblk, const GvParams& p,
-                                          const uint8_t* smem, int& dot_out) {
+__device__ __forceinline__ float q4k_item(const uint8_t* sb, int il, int kblk, const GvParams& p,
+                                          const uint8_t* smem, int& dot0, int& dot1) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(sb);
-    const uint4 w = *reinterpret_cast<const uint4*>(sb + 16 + 16 * u);
-    const uint8_t* xa = smem + p.off_xA + kblk * 256 + 16 * u;
-    const int4 xl = *reinterpret_cast<const int4*>(xa);
-    const int4 xh = *reinterpret_cast<const int4*>(xa + 128);
-    int dlo, dhi;
+    const uint4 w0 = *reinterpret_cast<const uint4*>(sb + 16 + 32 * il);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(sb + 32 + 32 * il);
+    const int sw = (kblk & 1) << 4;
+    const uint8_t* xa = smem + p.off_xA + kblk * 256;
+    const int o0 = (32 * il) ^ sw, o1 = (32 * il + 16) ^ sw;
+    const int4 xl0 = *reinterpret_cast<const int4*>(xa + o0), xl1 = *reinterpret_cast<const int4*>(xa + o1);
+    const int4 xh0 = *reinterpret_cast<const int4*>(xa + 128 + o0), xh1 = *reinterpret_cast<const int4*>(xa + 128 + o1);
     if (XM == 0) {
-        dlo = dp4a_us(w.x & 0x0F0F0F0Fu, xl.x, 0); dlo = dp4a_us(w.y & 0x0F0F0F0Fu, xl.y, dlo);
-        dlo = dp4a_us(w.z & 0x0F0F0F0Fu, xl.z, dlo); dlo = dp4a_us(w.w & 0x0F0F0F0Fu, xl.w, dlo);
-        dhi = dp4a_us(w.x & 0xF0F0F0F0u, xh.x, 0); dhi = dp4a_us(w.y & 0xF0F0F0F0u, xh.y, dhi);
-        dhi = dp4a_us(w.z & 0xF0F0F0F0u, xh.z, dhi); dhi = dp4a_us(w.w & 0xF0F0F0F0u, xh.w, dhi);
-        dhi >>= 4;      // the masked byte is 16*nibble, the sum is an exact multiple of 16
+        dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
+        dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
     } else {
-        const uint4 yl = *reinterpret_cast<const uint4*>(xa + p.K);
-        const uint4 yh = *reinterpret_cast<const uint4*>(xa + p.K + 128);
-        int a = dp4a_us(w.x & 0x0F0F0F0Fu, xl.x, 0); a = dp4a_us(w.y & 0x0F0F0F0Fu, xl.y, a);
-        a = dp4a_us(w.z & 0x0F0F0F0Fu, xl.z, a); a = dp4a_us(w.w & 0x0F0F0F0Fu, xl.w, a);
-        int b = dp4a_uu(w.x & 0x0F0F0F0Fu, yl.x, 0); b = dp4a_uu(w.y & 0x0F0F0F0Fu, yl.y, b);
-        b = dp4a_uu(w.z & 0x0F0F0F0Fu, yl.z, b); b = dp4a_uu(w.w & 0x0F0F0F0Fu, yl.w, b);
-        dlo = a * 256 + b;
-        a = dp4a_us(w.x & 0xF0F0F0F0u, xh.x, 0); a = dp4a_us(w.y & 0xF0F0F0F0u, xh.y, a);
-        a = dp4a_us(w.z & 0xF0F0F0F0u, xh.z, a); a = dp4a_us(w.w & 0xF0F0F0F0u, xh.w, a);
-        b = dp4a_uu(w.x & 0xF0F0F0F0u, yh.x, 0); b = dp4a_uu(w.y & 0xF0F0F0F0u, yh.y, b);
-        b = dp4a_uu(w.z & 0xF0F0F0F0u, yh.z, b); b = dp4a_uu(w.w & 0xF0F0F0F0u, yh.w, b);
-        dhi = (a * 256 + b) >> 4;
+        const uint8_t* xb = xa + p.K;
+        const uint4 yl0 = *reinterpret_cast<const uint4*>(xb + o0), yl1 = *reinterpret_cast<const uint4*>(xb + o1);
+        const uint4 yh0 = *reinterpret_cast<const uint4*>(xb + 128 + o0), yh1 = *reinterpret_cast<const uint4*>(xb + 128 + o1);
+        dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
+               (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
+        dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
+                ((dot16_uu(w0, 0xF0F0F0F0u, yh0) + dot16_uu(w1, 0xF0F0F0F0u, yh1)) >> 4));
     }
-    const bool odd = u & 1;
-    const int keep = odd ? dhi : dlo, send = odd ? dlo : dhi;
-    const int dot = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 1);
-    dot_out = dot;
-    int sc, mn;
-    scale_min_k4(u, hdr.y, hdr.z, hdr.w, sc, mn);
+    // scales / mins of sub-blocks 2*il and 2*il+1 (two adjacent bytes), both halves of get_scale_min_k4 at once
+    const int sh = 16 * (il & 1);
+    const uint32_t a = (hdr.y >> sh) & 0xFFFFu, b = (hdr.z >> sh) & 0xFFFFu, c = (hdr.w >> sh) & 0xFFFFu;
+    const bool hi = il >= 2;
+    const uint32_t sc2 = hi ? ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) : (a & 0x3F3Fu);
+    const uint32_t mn2 = hi ? (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) : (b & 0x3F3Fu);
     const float dall = h2f_bits(hdr.x & 0xFFFFu), dmin = h2f_bits(hdr.x >> 16);
-    const float d8 = reinterpret_cast<const float*>(smem + p.off_xd)[kblk * 8 + u];
-    const float s8 = reinterpret_cast<const float*>(smem + p.off_xs)[kblk * 8 + u];
-    return __fsub_rn(__fmul_rn(__fmul_rn(dall, (float)sc), __fmul_rn(d8, (float)dot)),
-                     __fmul_rn(__fmul_rn(dmin, (float)mn), s8));
+    const float2 d8 = *reinterpret_cast<const float2*>(smem + p.off_xd + (kblk * 8 + 2 * il) * 4);
+    const float2 s8 = *reinterpret_cast<const float2*>(smem + p.off_xs + (kblk * 8 + 2 * il) * 4);
+    const float pos = (float)((int)(sc2 & 0xFF) * dot0) * d8.x + (float)((int)(sc2 >> 8) * dot1) * d8.y;
+    const float neg = (float)(mn2 & 0xFF) * s8.x + (float)(mn2 >> 8) * s8.y;
+    return dall * pos - dmin * neg;
 }
 
 // 16 bytes from a 2-byte aligned shared-memory address: five aligned words, funnel-shifted.
@@ -206,9 +209,9 @@ __device__ __forceinline__ void lds16_unaligned(const uint8_t* ptr, uint32_t out
     for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
 }
 
-// ── Q6_K: one (half n, column run c) per lane = 64 weights in four 16-element scale
-// groups (quarters k = 0..3 at +32k), reference arithmetic src/kernels/gemv_q4.cu:581-618:
-// per group  d*sc*(d8*dot)  with dot = Σ(q6-32)·x = Σq6·x - 32·Σx.
+// ── Q6_K: one (half n, column run c) per lane = 64 weights in four 16-element scale groups (quarters k = 0..3
+// at +32k), reference arithmetic src/kernels/gemv_q4.cu:581-618: per group  d*sc*(d8*dot)  with
+// dot = Σ(q6-32)·x = Σq6·x - 32·Σx.
 template <int XM>
 __device__ __forceinline__ float q6k_item(const uint8_t* sb, int n, int c, int kblk, const GvParams& p,
                                           const uint8_t* smem, int dots_out[4]) {
@@ -220,7 +223,8 @@ __device__ __forceinline__ float q6k_item(const uint8_t* sb, int n, int c, int k
     const int8_t* scp = reinterpret_cast<const int8_t*>(sb + 192 + 8 * n + c);
     const uint8_t* xb = smem + p.off_xB + (kblk * 4 + 2 * n + c) * 16;
     const int*   xsum = reinterpret_cast<const int*>(smem + p.off_xsum) + kblk * 16 + 8 * n + c;
-    const float* xd   = reinterpret_cast<const float*>(smem + p.off_xd) + kblk * 8 + 4 * n;
+    const float4 xd4  = *reinterpret_cast<const float4*>(smem + p.off_xd + (kblk * 8 + 4 * n) * 4);
+    const float xdv[4] = { xd4.x, xd4.y, xd4.z, xd4.w };
     float acc = 0.f;
     #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -244,13 +248,12 @@ __device__ __forceinline__ float q6k_item(const uint8_t* sb, int n, int c, int k
         }
         const int dot = (XM == 1 ? dh * 256 + dl : dh) - 32 * xsum[2 * k];
         dots_out[k] = dot;
-        const float sc = (float)scp[2 * k];
-        acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(d, sc), __fmul_rn(xd[k], (float)dot)));
+        acc += (float)dot * ((float)scp[2 * k] * xdv[k]);
     }
-    return acc;
+    return d * acc;
 }
 
-struct GvPiece { int first, last, nch; };
+struct GvPiece { int first, last, nch; };   // rows [first, last) of a segment, chunks of trc rows
 
 __device__ __forceinline__ void gv_chunk(const GvParams& p, const GvPiece pc[3], int c, int& seg, int& r0, int& nrows) {
     seg = 0;
@@ -278,20 +281,20 @@ __device__ __forceinline__ void gv_issue(const GvParams& p, const GvPiece pc[3],
 }
 
 template <int XM>
-__global__ void __launch_bounds__(GV_THREADS, 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+__global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GV_MAXSLOT];
     __shared__ float red[GV_WARPS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    // this CTA's rows in every segment
+    // this CTA's rows in every segment: an even split of the row groups by bytes
     GvPiece pc[3];
     int nchunks = 0, pair_first = 0;
     {
         const long long G = gridDim.x, b = blockIdx.x;
         if (p.paired_rows) {      // out_mode 3: the same row range of both matrices
-            const int M = p.seg[0].M;
-            const int f = (int)((long long)M * b / G), l = (int)((long long)M * (b + 1) / G);
+            const int R = p.seg[0].R, M = p.seg[0].M, groups = (M + R - 1) / R;
+            const int f = min(M, (int)((long long)groups * b / G) * R), l = min(M, (int)((long long)groups * (b + 1) / G) * R);
             pair_first = f;
             #pragma unroll
             for (int i = 0; i < 2; ++i) { pc[i].first = f; pc[i].last = l; pc[i].nch = (l - f + p.seg[i].trc - 1) / p.seg[i].trc; nchunks += pc[i].nch; }
@@ -303,14 +306,14 @@ __global__ void __launch_bounds__(GV_THREADS, 2) gemv_stream_kernel(const __grid
             for (int i = 0; i < 3; ++i) {
                 pc[i].first = pc[i].last = pc[i].nch = 0;
                 if (i < p.nseg) {
-                    const long long rb = p.seg[i].rb, M = p.seg[i].M;
-                    long long f = lo - cum <= 0 ? 0 : (lo - cum + rb - 1) / rb;
-                    long long l = hi - cum <= 0 ? 0 : (hi - cum + rb - 1) / rb;
-                    f = f > M ? M : f; l = l > M ? M : l;
-                    pc[i].first = (int)f; pc[i].last = (int)l;
-                    pc[i].nch = (int)((l - f + p.seg[i].trc - 1) / p.seg[i].trc);
+                    const long long R = p.seg[i].R, M = p.seg[i].M, gb = R * p.seg[i].rb, groups = (M + R - 1) / R;
+                    long long f = lo - cum <= 0 ? 0 : (lo - cum + gb - 1) / gb;
+                    long long l = hi - cum <= 0 ? 0 : (hi - cum + gb - 1) / gb;
+                    f = f > groups ? groups : f; l = l > groups ? groups : l;
+                    pc[i].first = (int)min(M, f * R); pc[i].last = (int)min(M, l * R);
+                    pc[i].nch = (pc[i].last - pc[i].first + p.seg[i].trc - 1) / p.seg[i].trc;
                     nchunks += pc[i].nch;
-                    cum += rb * M;
+                    cum += gb * groups;
                 }
             }
         }
@@ -340,7 +343,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2) gemv_stream_kernel(const __grid
         gv_chunk(p, pc, c, seg, r0, nrows);
         const GvSegDev& s = p.seg[seg];
         const uintptr_t g0 = (uintptr_t)s.W + (size_t)r0 * s.rb;
-        uint8_t* sdata = smem + p.off_slots + (size_t)slot * p.slot_bytes + (g0 & 15);
+        uint8_t* sdata = smem + p.off_slots + (unsigned)slot * (unsigned)p.slot_bytes + (unsigned)(g0 & 15);
         {   // bytes between the last 16-byte boundary inside the tensor and its end
             const uintptr_t g1 = g0 + (size_t)nrows * s.rb;
             const uintptr_t endw = ((uintptr_t)s.W + (size_t)s.M * s.rb) & ~(uintptr_t)15;
@@ -350,31 +353,32 @@ __global__ void __launch_bounds__(GV_THREADS, 2) gemv_stream_kernel(const __grid
                 __syncthreads();
             }
         }
-        const int R = s.R, wrow0 = warp * R;
+        const int R = s.R, wrow0 = warp * R, type = s.type;
         const int nrw = max(0, min(R, nrows - wrow0));
         if (nrw > 0) {
-            const uint8_t* rows = sdata + (size_t)wrow0 * s.rb;
-            const int U = s.U, total = nrw * U;
+            const unsigned rb = (unsigned)s.rb, U = (unsigned)s.U;
+            const uint8_t* rows = sdata + (unsigned)wrow0 * rb;
+            const unsigned total = (unsigned)nrw * U;
             float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-            for (int base = 0; base < total; base += 32) {
-                const int i = base + lane;
+            for (unsigned base = 0; base < total; base += 32) {
+                const unsigned i = base + lane;
                 const bool valid = i < total;
-                const int ii = valid ? i : 0;
-                const int rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
-                const int j = ii - rl * U;
+                const unsigned ii = valid ? i : 0u;
+                const unsigned rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
+                const unsigned j = ii - rl * U, blk = j >> 2, sub = j & 3;
                 float term;
-                if (s.type == T_Q4K) {
-                    const int blk = j >> 3, u = j & 7;
-                    int dot;
-                    term = q4k_item<XM>(rows + (size_t)rl * s.rb + blk * Q4K_BYTES, u, blk, p, smem, dot);
-                    if (p.dbg_dots && seg == 0 && valid)
-                        p.dbg_dots[(size_t)(r0 + wrow0 + rl) * (U) + j] = dot;
-                } else {
-                    const int blk = j >> 2, n = (j >> 1) & 1, cc = j & 1;
-                    int dots[4];
-                    term = q6k_item<XM>(rows + (size_t)rl * s.rb + blk * Q6K_BYTES, n, cc, blk, p, smem, dots);
+                if (type == T_Q4K) {
+                    int d0, d1;
+                    term = q4k_item<XM>(rows + rl * rb + blk * Q4K_BYTES, (int)sub, (int)blk, p, smem, d0, d1);
                     if (p.dbg_dots && seg == 0 && valid) {
-                        int32_t* o = p.dbg_dots + (size_t)(r0 + wrow0 + rl) * (U * 4) + blk * 16 + 8 * n + cc;
+                        int32_t* o = p.dbg_dots + (size_t)(r0 + wrow0 + rl) * (2 * U) + blk * 8 + 2 * sub;
+                        o[0] = d0; o[1] = d1;
+                    }
+                } else {
+                    int dots[4];
+                    term = q6k_item<XM>(rows + rl * rb + blk * Q6K_BYTES, (int)(sub >> 1), (int)(sub & 1), (int)blk, p, smem, dots);
+                    if (p.dbg_dots && seg == 0 && valid) {
+                        int32_t* o = p.dbg_dots + (size_t)(r0 + wrow0 + rl) * (4 * U) + blk * 16 + 8 * (sub >> 1) + (sub & 1);
                         o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
                     }
                 }
@@ -453,16 +457,8 @@ int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const
     return JB_OK;
 }
 
-static int pick_rows_per_warp(int U, int rb, int chunk_cap) {
-    int best = 1; double best_eff = -1.0;
-    for (int R = 1; R <= 4; R *= 2) {
-        if ((long long)GV_WARPS * R * rb + 16 > chunk_cap) break;
-        const int items = R * U, iters = (items + 31) / 32;
-        const double eff = (double)items / (32.0 * iters);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = R; }
-    }
-    return best;
-}
+// rows per warp pass: the count of 32-byte items of a row group should fill whole warps
+static double lane_eff(int R, int U) { const int items = R * U, iters = (items + 31) / 32; return (double)items / (32.0 * iters); }
 
 int launch_gemv(const GemvArgs& a, cudaStream_t st) {
     if (a.nseg < 1 || a.nseg > 3) return set_error(JB_ERR_ARG, "gemv: nseg=%d", a.nseg);
@@ -489,58 +485,79 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
     }
     if (total_rows == 0) return JB_OK;
     if (a.out_mode == 2 && (a.nseg != 1 || !a.residual)) return set_error(JB_ERR_ARG, "gemv: residual epilogue needs one matrix and a residual");
-    if (a.out_mode == 3 && (a.nseg != 2 || a.seg[0].M != a.seg[1].M)) return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height");
-    // shared-memory plan
-    const int K = a.K, planes = a.xmode ? 2 : 1;
-    uint32_t off = 0;
-    p.off_xA = off; off += p.needA ? planes * K : 0;
-    p.off_xB = off; off += p.needB ? planes * K : 0;
-    p.off_xd = off; off += (K / 32) * 4;
-    p.off_xs = off; off += (K / 32) * 4;
-    p.off_xsum = off; off += p.needB ? (K / 16) * 4 : 0;
-    int grid = cx->sm_count * 2;
+    if (a.out_mode == 3 && (a.nseg != 2 || a.seg[0].M != a.seg[1].M || a.seg[0].type != a.seg[1].type))
+        return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height and type");
     p.paired_rows = a.out_mode == 3;
-    {   // rows of one CTA in paired mode: at most max(ceil(M/grid), 16) + 2
-        int rows = p.paired_rows ? (a.seg[0].M + grid - 1) / grid : 0;
-        rows = rows < 16 ? 16 : rows;
-        p.off_gate = off; off += p.paired_rows ? (uint32_t)(rows + 2) * 4 : 0;
+    const int K = a.K, planes = a.xmode ? 2 : 1;
+    // Try 4, 2, then 1 CTA per SM: the shared-memory budget per CTA decides how many row groups fit a slot.
+    const int smem_sm = cx->max_smem_optin + 1024;           // per-SM shared memory (per-CTA opt-in limit + 1 KB reserve)
+    for (int cps = 4; cps >= 1; cps >>= 1) {
+        int budget = smem_sm / cps - 1024 - 256;              // 1 KB system reserve per CTA, 256 B for static shared memory
+        if (budget > cx->max_smem_optin - 1024) budget = cx->max_smem_optin - 1024;
+        uint32_t off = 0;
+        p.off_xA = off; off += p.needA ? planes * K : 0;
+        p.off_xB = off; off += p.needB ? planes * K : 0;
+        p.off_xd = off; off += (K / 32) * 4;
+        p.off_xs = off; off += (K / 32) * 4;
+        p.off_xsum = off; off += p.needB ? (K / 16) * 4 : 0;
+        int grid = cx->sm_count * cps;
+        {   // rows of one CTA in paired mode: at most max(ceil(M/grid), 16) + 8
+            int rows = p.paired_rows ? (a.seg[0].M + grid - 1) / grid : 0;
+            rows = rows < 16 ? 16 : rows;
+            p.off_gate = off; off += p.paired_rows ? (uint32_t)(rows + 8) * 4 : 0;
+        }
+        off = (off + 127) & ~127u;
+        p.off_slots = off;
+        const int ring = budget - (int)off;
+        const int chunk_cap = ring / 2 - 16;                  // at least two slots
+        bool fits = chunk_cap > 0;
+        int slot = 0;
+        p.total_bytes = 0;
+        double worst_eff = 1.0;
+        for (int i = 0; i < a.nseg && fits; ++i) {
+            GvSegDev& d = p.seg[i];
+            d.W = (const uint8_t*)a.seg[i].W; d.y = a.seg[i].y; d.M = a.seg[i].M; d.type = a.seg[i].type;
+            d.rb = nb * block_bytes(d.type);
+            d.U = nb * 4;
+            int best = 0; double be = -1.0;
+            for (int R = 1; R <= 4; R *= 2) {
+                if ((long long)GV_WARPS * R * d.rb + 16 > chunk_cap) break;
+                const double e = lane_eff(R, d.U);
+                if (e > be + 1e-9) { be = e; best = R; }
+            }
+            if (!best) { fits = false; break; }
+            d.R = best; d.trc = GV_WARPS * best;
+            worst_eff = be < worst_eff ? be : worst_eff;
+            const int need = ((d.trc * d.rb + 16 + 127) / 128) * 128;
+            slot = need > slot ? need : slot;
+            const long long groups = (d.M + d.R - 1) / d.R;
+            p.total_bytes += groups * d.R * d.rb;
+        }
+        if (!fits) {
+            if (cps == 1) return set_error(JB_ERR_LIMIT, "gemv: one row group does not fit the staging ring (K=%d)", K);
+            continue;
+        }
+        (void)worst_eff;
+        p.slot_bytes = slot;
+        p.nslots = ring / slot;
+        if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
+        if (p.nslots < 2) { if (cps == 1) return set_error(JB_ERR_LIMIT, "gemv: staging ring does not fit (slot %d B)", slot); continue; }
+        const size_t smem_bytes = (size_t)p.off_slots + (size_t)p.nslots * slot;
+        long long groups_total = 0;
+        for (int i = 0; i < a.nseg; ++i) groups_total += (p.seg[i].M + p.seg[i].R - 1) / p.seg[i].R;
+        if (p.paired_rows) groups_total /= 2;
+        if (grid > groups_total) grid = (int)groups_total;
+        if (grid < 1) grid = 1;
+        auto kern = a.xmode ? gemv_stream_kernel<1> : gemv_stream_kernel<0>;
+        if (!cx->gemv_attr[a.xmode ? 1 : 0]) {
+            JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 1024));
+            cx->gemv_attr[a.xmode ? 1 : 0] = true;
+        }
+        JB_CUDA(launch_k(kern, dim3(grid), dim3(GV_THREADS), smem_bytes, st, pdl_enabled(), p));
+        count_launch();
+        return JB_OK;
     }
-    off = (off + 127) & ~127u;
-    p.off_slots = off;
-    const int ring_budget = GV_SMEM_BUDGET - (int)off;
-    const int chunk_cap = ring_budget / 2 - 16;
-    int slot = 0;
-    for (int i = 0; i < a.nseg; ++i) {
-        GvSegDev& d = p.seg[i];
-        d.W = (const uint8_t*)a.seg[i].W; d.y = a.seg[i].y; d.M = a.seg[i].M; d.type = a.seg[i].type;
-        d.rb = nb * block_bytes(d.type);
-        d.U = d.type == T_Q4K ? nb * 8 : nb * 4;
-        if (d.rb + 16 > chunk_cap) return set_error(JB_ERR_LIMIT, "gemv: one row (%d B) does not fit a staging slot", d.rb);
-        d.R = pick_rows_per_warp(d.U, d.rb, chunk_cap);
-        d.trc = GV_WARPS * d.R;
-        if ((long long)d.trc * d.rb + 16 > chunk_cap) { d.R = 1; d.trc = (chunk_cap - 16) / d.rb; if (d.trc > GV_WARPS) d.trc = GV_WARPS; }
-        const int need = ((d.trc * d.rb + 16 + 127) / 128) * 128;
-        slot = need > slot ? need : slot;
-        p.total_bytes += (long long)d.rb * d.M;
-    }
-    p.slot_bytes = slot;
-    p.nslots = ring_budget / slot;
-    if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
-    if (p.nslots < 2) return set_error(JB_ERR_LIMIT, "gemv: staging ring does not fit (slot %d B)", slot);
-    const size_t smem_bytes = (size_t)p.off_slots + (size_t)p.nslots * slot;
-    int min_trc = p.seg[0].trc;
-    for (int i = 1; i < a.nseg; ++i) min_trc = p.seg[i].trc < min_trc ? p.seg[i].trc : min_trc;
-    const long long max_useful = (total_rows + min_trc - 1) / min_trc;
-    if (grid > max_useful) grid = (int)max_useful;
-    if (grid < 1) grid = 1;
-    auto kern = a.xmode ? gemv_stream_kernel<1> : gemv_stream_kernel<0>;
-    if (!cx->gemv_attr[a.xmode ? 1 : 0]) {
-        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GV_SMEM_BUDGET));
-        cx->gemv_attr[a.xmode ? 1 : 0] = true;
-    }
-    JB_CUDA(launch_k(kern, dim3(grid), dim3(GV_THREADS), smem_bytes, st, pdl_enabled(), p));
-    count_launch();
-    return JB_OK;
+    return set_error(JB_ERR_LIMIT, "gemv: no launch configuration fits (K=%d)", K);
 }
 
 }  // namespace jb

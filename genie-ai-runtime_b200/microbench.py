@@ -1,0 +1,138 @@
+"""Kernel-level micro-benchmarks of the hot path (configurations 0-3 of the baseline), timed with CUDA events.
+
+    python genie-ai-runtime_b200/microbench.py gemv  --type 12 --M 9728 --K 2560            # config 0
+    python genie-ai-runtime_b200/microbench.py gemv  --type 14 --M 2560 --K 9728            # config 1
+    python genie-ai-runtime_b200/microbench.py pair  --M 9728 --K 2560 [--swiglu]           # gate/up
+    python genie-ai-runtime_b200/microbench.py add   --type 14 --M 2560 --K 9728            # W_down + residual
+    python genie-ai-runtime_b200/microbench.py f32   --type 14 --M 151936 --K 2560          # logits
+    python genie-ai-runtime_b200/microbench.py attn  --L 8192 [--batch 64]                  # config 2
+    python genie-ai-runtime_b200/microbench.py mmq   --type 12 --M 9728 --K 2560 --N 512    # config 3
+
+Weights are random block images; `--copies` distinct copies (default: enough for 3x the 126 MB L2) are used in
+rotation so that every launch streams from HBM.  Prints one JSON line with the average launch time and the
+algorithmic GB/s (bytes every launch must move at least once: weights + activations in + results out).
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+L2_BYTES = 126 << 20
+
+
+def blocks(ggml_type, rows, K, dev, gen):
+    import torch
+    bb = 144 if ggml_type == 12 else 210
+    B = rows * (K // 256)
+    img = torch.randint(0, 256, (B, bb), dtype=torch.uint8, device=dev, generator=gen)
+    d = (torch.randn(B, device=dev, generator=gen).abs() * 0.01).to(torch.float16).view(torch.uint8).reshape(B, 2)
+    if ggml_type == 12:
+        img[:, 0:2] = d
+        img[:, 2:4] = (torch.randn(B, device=dev, generator=gen).abs() * 0.01).to(torch.float16).view(torch.uint8).reshape(B, 2)
+    else:
+        img[:, 208:210] = d
+    return img.reshape(rows, -1).contiguous()
+
+
+def main():
+    import torch
+    from __graft_entry__ import load_package
+    jb = load_package()
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "mmq"])
+    ap.add_argument("--type", type=int, default=12)
+    ap.add_argument("--M", type=int, default=9728)
+    ap.add_argument("--K", type=int, default=2560)
+    ap.add_argument("--N", type=int, default=512)
+    ap.add_argument("--L", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--copies", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    a = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000)
+    if a.no_pdl:
+        jb.lib.jllm_b200_set_pdl(0)
+    st = torch.cuda.Stream()
+    bb = lambda t: 144 if t == 12 else 210
+    M, K, t = a.M, a.K, a.type
+    calls, nbytes = [], 0
+    if a.kind in ("gemv", "add", "f32", "pair", "triple", "mmq"):
+        nmat = {"pair": 2, "triple": 3}.get(a.kind, 1)
+        Ms = [M] * nmat if a.kind != "triple" else [4096, 1024, 1024]
+        ts = [t] * nmat if a.kind != "triple" else [12, 12, 14]
+        wbytes = sum(m * (K // 256) * bb(tt) for m, tt in zip(Ms, ts))
+        copies = a.copies or max(2, int(np.ceil(3 * L2_BYTES / wbytes)))
+        Ws = [[blocks(tt, m, K, dev, gen) for m, tt in zip(Ms, ts)] for _ in range(copies)]
+        N = a.N if a.kind == "mmq" else 1
+        x = torch.randn(N * K, device=dev, generator=gen).to(torch.float16)
+        res = torch.randn(M, device=dev, generator=gen).to(torch.float16)
+        ys = [torch.zeros(N * m, dtype=torch.float32 if a.kind == "f32" else torch.float16, device=dev) for m in Ms]
+        nw = torch.ones(K, dtype=torch.float32, device=dev)
+        for W in Ws:
+            if a.kind == "gemv":
+                calls.append(lambda W=W: jb.gemv_quant(ys[0], W[0], t, x, M, K, st))
+            elif a.kind == "add":
+                calls.append(lambda W=W: jb.gemv_quant_add(ys[0], W[0], t, x, res, M, K, st))
+            elif a.kind == "f32":
+                calls.append(lambda W=W: jb.gemv_quant_f32(ys[0], W[0], t, x, M, K, st))
+            elif a.kind == "pair" and a.swiglu:
+                calls.append(lambda W=W: jb.norm_gemv_pair_swiglu(ys[0], W[0], W[1], t, M, x, nw, True, 1e-6, K, st))
+            elif a.kind == "pair":
+                calls.append(lambda W=W: jb.gemv_quant_pair(ys[0], W[0], t, M, ys[1], W[1], t, M, x, K, st))
+            elif a.kind == "triple":
+                calls.append(lambda W=W: jb.gemv_quant_triple(ys[0], W[0], 12, Ms[0], ys[1], W[1], 12, Ms[1], ys[2], W[2], 14, Ms[2], x, K, st))
+            else:
+                calls.append(lambda W=W: jb.gemm_quant_batched(ys[0], W[0], t, x, M, a.N, K, st))
+        nbytes = wbytes + N * K * 2 + sum(N * m * ys[0].element_size() for m in Ms)
+        shape = dict(M=Ms, K=K, types=ts, N=N, copies=copies)
+    else:
+        nh, nkv, hd, L, B = 32, 8, 128, a.L, a.batch
+        lens = [L] if B == 1 else [int(v) for v in np.random.Generator(np.random.PCG64(1002)).integers(256, 8193, B)]
+        per = sum(2112 * l + 16384 for l in lens)
+        copies = a.copies or max(2, int(np.ceil(3 * L2_BYTES / per)))
+        scale = float(1 / np.sqrt(hd))
+        mk = lambda ts_: torch.tensor([t_.data_ptr() for t_ in ts_], dtype=torch.int64, device=dev)
+        for _ in range(copies):
+            ks = [torch.randint(-127, 128, (l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
+            vs = [torch.randint(-127, 128, (l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
+            kss = [(torch.randn((l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
+            vss = [(torch.randn((l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
+            q = torch.randn(B * nh * hd, device=dev, generator=gen).to(torch.float16)
+            out = torch.zeros(B * nh * hd, dtype=torch.float16, device=dev)
+            if B == 1:
+                calls.append(lambda q=q, out=out, k=ks[0], v=vs[0], s1=kss[0], s2=vss[0]:
+                             jb.flash_attention_decode(out, q, k, v, nh, nkv, hd, hd, L, scale, True, s1, s2, 0, st))
+            else:
+                lists = (mk(ks), mk(vs), mk(kss), mk(vss), torch.tensor(lens, dtype=torch.int32, device=dev))
+                keep = (ks, vs, kss, vss)
+                calls.append(lambda q=q, out=out, ls=lists, keep=keep:
+                             jb.flash_attention_decode_batched(out, q, ls[0], ls[1], ls[2], ls[3], ls[4], B, max(lens), nh, nkv, hd, scale, True, st))
+        nbytes = per
+        shape = dict(L=L, batch=B, copies=copies)
+    with torch.cuda.stream(st):
+        for i in range(a.warmup):
+            calls[i % len(calls)]()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(st)
+        for i in range(a.iters):
+            calls[i % len(calls)]()
+        e1.record(st)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / a.iters
+    print(json.dumps({"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes,
+                      "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "device_status": jb.device_status(st)}))
+
+
+if __name__ == "__main__":
+    main()
