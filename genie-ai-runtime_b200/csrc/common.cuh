@@ -45,7 +45,7 @@ struct DeviceCtx {
     float* splitk = nullptr; size_t splitk_floats = 0;
     void*  mmq_act = nullptr; size_t mmq_act_bytes = 0;
     RopeTable rope[8]; int n_rope = 0;
-    bool gemv_attr[2] = { false, false };
+    bool gemv_attr[4] = { false, false, false, false };
 };
 DeviceCtx* ctx();                        // context of the current device (created on first use)
 

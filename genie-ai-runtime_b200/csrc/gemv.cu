@@ -57,11 +57,11 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     float rrms = 1.0f;
     if (p.do_norm) {   // reference: fused_rmsnorm_residual, src/kernels/fused_norm.cu:33-101
         float ss = 0.f;
-        for (int g4 = tid; g4 < K / 4; g4 += GV_THREADS) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(p.x + 4 * g4);
-            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-            ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+        for (int g8 = tid; g8 < K / 8; g8 += GV_THREADS) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * g8);
+            const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i])); ss += a.x * a.x + a.y * a.y; }
         }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
@@ -70,79 +70,100 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         #pragma unroll
         for (int w = 0; w < GV_WARPS; ++w) tot += red[w];
         rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
-        __syncthreads();
     }
     uint8_t* xA = smem + p.off_xA; uint8_t* xB = smem + p.off_xB;
     float* xd = reinterpret_cast<float*>(smem + p.off_xd);
     float* xs = reinterpret_cast<float*>(smem + p.off_xs);
     int*   xsum = reinterpret_cast<int*>(smem + p.off_xsum);
-    for (int g4 = tid; g4 < K / 4; g4 += GV_THREADS) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(p.x + 4 * g4);
-        float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-        float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-        float v[4] = { a.x, a.y, b.x, b.y };
-        if (p.do_norm) {
+    // one thread per 32-element group: no shuffles, one pair of divisions per group
+    for (int gi = tid; gi < K / 32; gi += GV_THREADS) {
+        float v[32];
+        #pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 32 * gi + 8 * q4);
+            const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
             #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float w = p.norm_w_fp32 ? reinterpret_cast<const float*>(p.norm_w)[4 * g4 + i]
-                                              : __half2float(reinterpret_cast<const __half*>(p.norm_w)[4 * g4 + i]);
-                v[i] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i], rrms), w)));
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                v[8 * q4 + 2 * i] = a.x; v[8 * q4 + 2 * i + 1] = a.y;
             }
         }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        if (p.do_norm) {
+            float wn[32];
+            if (p.norm_w_fp32) {
+                #pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + 32 * gi + 4 * q4);
+                    wn[4 * q4] = w4.x; wn[4 * q4 + 1] = w4.y; wn[4 * q4 + 2] = w4.z; wn[4 * q4 + 3] = w4.w;
+                }
+            } else {
+                #pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.norm_w) + 32 * gi + 8 * q4);
+                    const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                        wn[8 * q4 + 2 * i] = a.x; wn[8 * q4 + 2 * i + 1] = a.y;
+                    }
+                }
+            }
+            #pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i], rrms), wn[i])));
+        }
+        float amax = 0.f;
         #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        int q[4]; int qsum = 0; float d; float fsum = 0.f;
-        if (XM == 0) {     // q8_1: src/kernels/gemv_q4.cu:445-466
-            d = __fdiv_rn(amax, 127.0f);
-            const float id = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        const float lim = XM == 0 ? 127.0f : 32767.0f;
+        const float d = __fdiv_rn(amax, lim);                      // q8_1: src/kernels/gemv_q4.cu:445-466
+        const float id = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+        uint32_t hi[8], lo[8];
+        int s16[2] = { 0, 0 };
+        float fsum = 0.f;
+        #pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            hi[w] = 0; lo[w] = 0;
             #pragma unroll
-            for (int i = 0; i < 4; ++i) { q[i] = max(-127, min(127, __float2int_rn(__fmul_rn(v[i], id)))); qsum += q[i]; }
-        } else {           // 16-bit fixed point
-            d = __fdiv_rn(amax, 32767.0f);
-            const float id = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
-            #pragma unroll
-            for (int i = 0; i < 4; ++i) { q[i] = max(-32767, min(32767, __float2int_rn(__fmul_rn(v[i], id)))); qsum += q[i]; }
-            fsum = (v[0] + v[1]) + (v[2] + v[3]);
+            for (int i = 0; i < 4; ++i) {
+                const float x = v[4 * w + i];
+                const int q = max(-(int)lim, min((int)lim, __float2int_rn(__fmul_rn(x, id))));
+                s16[w >> 2] += q;
+                if (XM == 0) hi[w] |= (uint32_t)(q & 0xFF) << (8 * i);
+                else { hi[w] |= (uint32_t)((q >> 8) & 0xFF) << (8 * i); lo[w] |= (uint32_t)(q & 0xFF) << (8 * i); }
+            }
         }
-        // 16-element code sums (Q6_K subtracts 32*sum instead of re-centring every quant)
-        int s16 = qsum;
-        s16 += __shfl_xor_sync(0xFFFFFFFFu, s16, 1);
-        s16 += __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
-        int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 4);
         if (XM == 1) {
+            // fp32 sum of the group in the order of an 8-lane xor tree over 4-element partial sums
+            float ps[8];
             #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) fsum += __shfl_xor_sync(0xFFFFFFFFu, fsum, o);
+            for (int w = 0; w < 8; ++w) ps[w] = (v[4 * w] + v[4 * w + 1]) + (v[4 * w + 2] + v[4 * w + 3]);
+            fsum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         }
-        const int e0 = 4 * g4, blk = e0 >> 8, r = e0 & 255;
-        uint32_t w_hi, w_lo = 0;
-        if (XM == 0) {
-            w_hi = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-        } else {
-            w_hi = (uint32_t)((q[0] >> 8) & 0xFF) | ((uint32_t)((q[1] >> 8) & 0xFF) << 8) | ((uint32_t)((q[2] >> 8) & 0xFF) << 16) | ((uint32_t)((q[3] >> 8) & 0xFF) << 24);
-            w_lo = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
-        }
+        const int blk = gi >> 3, j = gi & 7;
         if (p.needA) {
-            const int j = r >> 5, wi = r & 31, h = wi >> 4, i = wi & 15;
-            const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4)) + i;
-            *reinterpret_cast<uint32_t*>(xA + off) = w_hi;
-            if (XM == 1) *reinterpret_cast<uint32_t*>(xA + K + off) = w_lo;
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4));
+                *reinterpret_cast<uint4*>(xA + off) = make_uint4(hi[4 * h], hi[4 * h + 1], hi[4 * h + 2], hi[4 * h + 3]);
+                if (XM == 1) *reinterpret_cast<uint4*>(xA + K + off) = make_uint4(lo[4 * h], lo[4 * h + 1], lo[4 * h + 2], lo[4 * h + 3]);
+            }
         }
         if (p.needB) {
-            const int n = r >> 7, k = (r & 127) >> 5, c = (r & 31) >> 4, i = r & 15;
-            const int off = k * (K >> 2) + (blk * 4 + 2 * n + c) * 16 + i;
-            *reinterpret_cast<uint32_t*>(xB + off) = w_hi;
-            if (XM == 1) *reinterpret_cast<uint32_t*>(xB + K + off) = w_lo;
-            if ((lane & 3) == 0) xsum[e0 >> 4] = s16;
-        }
-        if ((lane & 7) == 0) {
-            if (XM == 0) {
-                xd[e0 >> 5] = __half2float(__float2half_rn(d));
-                xs[e0 >> 5] = __half2float(__float2half_rn(__fmul_rn(d, (float)s32)));
-            } else {
-                xd[e0 >> 5] = d;
-                xs[e0 >> 5] = fsum;
+            const int n = j >> 2, k = j & 3;
+            #pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int off = k * (K >> 2) + (blk * 4 + 2 * n + c) * 16;
+                *reinterpret_cast<uint4*>(xB + off) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+                if (XM == 1) *reinterpret_cast<uint4*>(xB + K + off) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+                xsum[2 * gi + c] = s16[c];
             }
+        }
+        if (XM == 0) {
+            xd[gi] = __half2float(__float2half_rn(d));
+            xs[gi] = __half2float(__float2half_rn(__fmul_rn(d, (float)(s16[0] + s16[1]))));
+        } else {
+            xd[gi] = d;
+            xs[gi] = fsum;
         }
     }
 }
@@ -253,6 +274,39 @@ __device__ __forceinline__ float q6k_item(const uint8_t* sb, int n, int c, int k
     return d * acc;
 }
 
+// One warp, `nrw` (<= 4) consecutive rows in shared memory: lanes stride over the rows' 32-byte items
+// (4 per super-block), each lane adds its terms into the accumulator of the row the item belongs to.
+template <int XM, int TYPE, bool DBG>
+__device__ __forceinline__ void consume_rows(const uint8_t* rows, int nrw, int rb_, int U_, int lane, const GvParams& p,
+                                             const uint8_t* smem, float (&acc)[4], int32_t* dbg) {
+    const unsigned rb = (unsigned)rb_, U = (unsigned)U_, total = (unsigned)nrw * U;
+    constexpr unsigned BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    for (unsigned base = 0; base < total; base += 32) {
+        const unsigned i = base + lane;
+        const bool valid = i < total;
+        const unsigned ii = valid ? i : 0u;
+        const unsigned rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
+        const unsigned j = ii - rl * U, blk = j >> 2, sub = j & 3;
+        const uint8_t* sb = rows + rl * rb + blk * BB;
+        float term;
+        if (TYPE == T_Q4K) {
+            int d0, d1;
+            term = q4k_item<XM>(sb, (int)sub, (int)blk, p, smem, d0, d1);
+            if (DBG && dbg && valid) { int32_t* o = dbg + (size_t)rl * (2 * U) + blk * 8 + 2 * sub; o[0] = d0; o[1] = d1; }
+        } else {
+            int dots[4];
+            term = q6k_item<XM>(sb, (int)(sub >> 1), (int)(sub & 1), (int)blk, p, smem, dots);
+            if (DBG && dbg && valid) {
+                int32_t* o = dbg + (size_t)rl * (4 * U) + blk * 16 + 8 * (sub >> 1) + (sub & 1);
+                o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
+            }
+        }
+        if (!valid) term = 0.f;
+        acc[0] += rl == 0 ? term : 0.f; acc[1] += rl == 1 ? term : 0.f;
+        acc[2] += rl == 2 ? term : 0.f; acc[3] += rl == 3 ? term : 0.f;
+    }
+}
+
 struct GvPiece { int first, last, nch; };   // rows [first, last) of a segment, chunks of trc rows
 
 __device__ __forceinline__ void gv_chunk(const GvParams& p, const GvPiece pc[3], int c, int& seg, int& r0, int& nrows) {
@@ -280,7 +334,7 @@ __device__ __forceinline__ void gv_issue(const GvParams& p, const GvPiece pc[3],
     bulk_g2s(smem + p.off_slots + (size_t)slot * p.slot_bytes, (const void*)a0, bytes, &full[slot]);
 }
 
-template <int XM>
+template <int XM, bool DBG>
 __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GV_MAXSLOT];
@@ -356,36 +410,11 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
         const int R = s.R, wrow0 = warp * R, type = s.type;
         const int nrw = max(0, min(R, nrows - wrow0));
         if (nrw > 0) {
-            const unsigned rb = (unsigned)s.rb, U = (unsigned)s.U;
-            const uint8_t* rows = sdata + (unsigned)wrow0 * rb;
-            const unsigned total = (unsigned)nrw * U;
+            const uint8_t* rows = sdata + (unsigned)wrow0 * (unsigned)s.rb;
             float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-            for (unsigned base = 0; base < total; base += 32) {
-                const unsigned i = base + lane;
-                const bool valid = i < total;
-                const unsigned ii = valid ? i : 0u;
-                const unsigned rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
-                const unsigned j = ii - rl * U, blk = j >> 2, sub = j & 3;
-                float term;
-                if (type == T_Q4K) {
-                    int d0, d1;
-                    term = q4k_item<XM>(rows + rl * rb + blk * Q4K_BYTES, (int)sub, (int)blk, p, smem, d0, d1);
-                    if (p.dbg_dots && seg == 0 && valid) {
-                        int32_t* o = p.dbg_dots + (size_t)(r0 + wrow0 + rl) * (2 * U) + blk * 8 + 2 * sub;
-                        o[0] = d0; o[1] = d1;
-                    }
-                } else {
-                    int dots[4];
-                    term = q6k_item<XM>(rows + rl * rb + blk * Q6K_BYTES, (int)(sub >> 1), (int)(sub & 1), (int)blk, p, smem, dots);
-                    if (p.dbg_dots && seg == 0 && valid) {
-                        int32_t* o = p.dbg_dots + (size_t)(r0 + wrow0 + rl) * (4 * U) + blk * 16 + 8 * (sub >> 1) + (sub & 1);
-                        o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
-                    }
-                }
-                if (!valid) term = 0.f;
-                acc[0] += rl == 0 ? term : 0.f; acc[1] += rl == 1 ? term : 0.f;
-                acc[2] += rl == 2 ? term : 0.f; acc[3] += rl == 3 ? term : 0.f;
-            }
+            int32_t* dbg = (DBG && seg == 0) ? p.dbg_dots + (size_t)(r0 + wrow0) * (type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
+            if (type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(rows, nrw, s.rb, s.U, lane, p, smem, acc, dbg);
+            else               consume_rows<XM, T_Q6K, DBG>(rows, nrw, s.rb, s.U, lane, p, smem, acc, dbg);
             #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 if (r < nrw) {
@@ -548,10 +577,12 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         if (p.paired_rows) groups_total /= 2;
         if (grid > groups_total) grid = (int)groups_total;
         if (grid < 1) grid = 1;
-        auto kern = a.xmode ? gemv_stream_kernel<1> : gemv_stream_kernel<0>;
-        if (!cx->gemv_attr[a.xmode ? 1 : 0]) {
+        auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
+                               : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
+        const int ki = (a.xmode ? 1 : 0) + (a.dbg_dots ? 2 : 0);
+        if (!cx->gemv_attr[ki]) {
             JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 1024));
-            cx->gemv_attr[a.xmode ? 1 : 0] = true;
+            cx->gemv_attr[ki] = true;
         }
         JB_CUDA(launch_k(kern, dim3(grid), dim3(GV_THREADS), smem_bytes, st, pdl_enabled(), p));
         count_launch();

@@ -55,6 +55,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python every iteration instead of replaying a CUDA graph")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -120,18 +121,31 @@ def main():
         nbytes = per
         shape = dict(L=L, batch=B, copies=copies)
     with torch.cuda.stream(st):
-        for i in range(a.warmup):
+        for i in range(max(a.warmup, len(calls))):
             calls[i % len(calls)]()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
-        e0.record(st)
-        for i in range(a.iters):
-            calls[i % len(calls)]()
-        e1.record(st)
+        if a.no_graph:
+            e0.record(st)
+            for i in range(a.iters):
+                calls[i % len(calls)]()
+            e1.record(st)
+        else:
+            # one graph holding `iters` launches over the rotating copies: the host's per-call cost (several
+            # microseconds through ctypes) stays out of the measurement
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for i in range(a.iters):
+                    calls[i % len(calls)]()
+            g.replay()
+            torch.cuda.synchronize()
+            e0.record(st)
+            g.replay()
+            e1.record(st)
         torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / a.iters
     print(json.dumps({"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes,
-                      "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "device_status": jb.device_status(st)}))
+                      "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "graph": not a.no_graph, "device_status": jb.device_status(st)}))
 
 
 if __name__ == "__main__":
