@@ -187,3 +187,14 @@ def flash_attention_decode_batched(output, q, k_list, v_list, ks_list, vs_list, 
     check(lib.jllm_b200_flash_attention_decode_batched(_ptr(output), _ptr(q), _ptr(k_list), _ptr(v_list), _ptr(ks_list), _ptr(vs_list),
                                                        _ptr(seq_lens), i32(batch), i32(max_seq_len), i32(n_heads), i32(n_kv_heads),
                                                        i32(head_dim), f32(scale), i32(1 if kv_int8 else 0), _stream(stream)))
+
+
+def flash_attention_decode_noalloc(output, q, k_cache, v_cache, n_heads, n_kv_heads, head_dim, cache_head_dim, seq_len, scale, kv_int8,
+                                   k_scales, v_scales, window, stream=None):
+    """flash_attention_decode for hosts that must not let the library allocate: the split-K partials sit in a fixed
+    array inside the library (1 MiB per GPU).  Raises JllmError (code 6) when heads x slices x (head_dim + 2) floats
+    do not fit; calls that overlap on one GPU must be ordered by the caller."""
+    check(lib.jllm_b200_flash_attention_decode_noalloc(_ptr(output), _ptr(q), _ptr(k_cache), _ptr(v_cache), i32(n_heads), i32(n_kv_heads),
+                                                       i32(head_dim), i32(cache_head_dim), i32(seq_len), f32(scale),
+                                                       i32(1 if kv_int8 else 0), _ptr(k_scales), _ptr(v_scales), i32(window),
+                                                       _stream(stream)))

@@ -231,6 +231,24 @@ int    jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d);
  * 7 layer-0 K cache, 8 layer-0 K scales. */
 const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);
 
+/* ── allocation-free decode attention (no counterpart in the reference) ─────────────────────────
+ * For hosts that cannot let the library allocate device memory: an engine whose own pools already hold
+ * all of the GPU's free memory, a request loop that must avoid driver calls which can stall the device,
+ * or a CUDA-graph recording in progress.  Same arguments and result as jllm_b200_flash_attention_decode;
+ * the split-K partials live in a fixed array built into the library (JLLM_B200_NOALLOC_MAX_FLOATS floats
+ * per GPU that loads the library, held until the process exits) instead of a buffer grown on demand.
+ *   - n_heads * n_slices * (head_dim + 2) must not exceed JLLM_B200_NOALLOC_MAX_FLOATS (n_slices =
+ *     ceil(seq_len / max(128, ceil(seq_len / 32)))); larger requests return JLLM_B200_ERR_LIMIT.
+ *   - The first call on each device looks up the array's device address; make that call before starting
+ *     any stream capture.
+ *   - All calls share the array.  Nothing needs clearing between calls (every record read is written first),
+ *     but calls that overlap in time on one GPU race on it: keep them on one stream or order them.
+ *   - It never calls cudaMalloc / cudaFree or any allocating routine. */
+#define JLLM_B200_NOALLOC_MAX_FLOATS (256 * 1024)
+int jllm_b200_flash_attention_decode_noalloc(void* output, const void* q, const void* k_cache, const void* v_cache, int n_heads,
+                                             int n_kv_heads, int head_dim, int cache_head_dim, int seq_len, float scale, int kv_int8,
+                                             const float* k_scales, const float* v_scales, int window, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
