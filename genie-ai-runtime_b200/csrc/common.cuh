@@ -80,8 +80,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // hardware-defined short interval) and reports false; callers set the status word
 // and return instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
-    for (uint32_t i = 0; i < limit; ++i)
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (i > 4) __nanosleep(40);          // back off: waiting warps must not crowd the issue slots of working ones
+    }
     return false;
 }
 // 1-D bulk copy global -> shared through the TMA unit; both addresses 16-byte aligned,

@@ -168,14 +168,28 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     }
 }
 
-__device__ __forceinline__ int dot16_us(const uint4& w, uint32_t mask, const int4& x) {
-    int d = dp4a_us(w.x & mask, x.x, 0); d = dp4a_us(w.y & mask, x.y, d);
-    d = dp4a_us(w.z & mask, x.z, d);     return dp4a_us(w.w & mask, x.w, d);
+// ── shared-memory reads by 32-bit shared address (no generic-pointer arithmetic in the inner loop) ──
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) { uint32_t v; asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ int lds_s8(uint32_t a) { int v; asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+
+__device__ __forceinline__ int dot16_us(const uint4& w, uint32_t mask, const uint4& x) {
+    int d = dp4a_us(w.x & mask, (int)x.x, 0); d = dp4a_us(w.y & mask, (int)x.y, d);
+    d = dp4a_us(w.z & mask, (int)x.z, d);     return dp4a_us(w.w & mask, (int)x.w, d);
 }
 __device__ __forceinline__ int dot16_uu(const uint4& w, uint32_t mask, const uint4& x) {
     int d = dp4a_uu(w.x & mask, x.x, 0); d = dp4a_uu(w.y & mask, x.y, d);
     d = dp4a_uu(w.z & mask, x.z, d);     return dp4a_uu(w.w & mask, x.w, d);
 }
+
+// shared addresses of the staged activation image
+struct GvX { uint32_t xA, xB, xd, xs, xsum; int K; };
 
 // ── Q4_K: one 32-byte group of quants per lane ───────────────────────────
 // Group il (0..3) of a block holds the low nibbles of sub-block 2*il and the high nibbles of sub-block
@@ -183,24 +197,19 @@ __device__ __forceinline__ int dot16_uu(const uint4& w, uint32_t mask, const uin
 // reference builds with eight dp4a each (src/kernels/gemv_q4.cu:487-494) — and folds them as
 //   dall * (sc0*dot0*d8_0 + sc1*dot1*d8_1) - dmin * (m0*s8_0 + m1*s8_1)
 // which is the reference's  Σ dall*sc*(d8*dot) - dmin*m*s8  (:499) with the common factors taken out.
+// `sb` = shared address of the block, il is fixed per lane.
 template <int XM>
-__device__ __forceinline__ float q4k_item(const uint8_t* sb, int il, int kblk, const GvParams& p,
-                                          const uint8_t* smem, int& dot0, int& dot1) {
-    const uint4 hdr = *reinterpret_cast<const uint4*>(sb);
-    const uint4 w0 = *reinterpret_cast<const uint4*>(sb + 16 + 32 * il);
-    const uint4 w1 = *reinterpret_cast<const uint4*>(sb + 32 + 32 * il);
-    const int sw = (kblk & 1) << 4;
-    const uint8_t* xa = smem + p.off_xA + kblk * 256;
-    const int o0 = (32 * il) ^ sw, o1 = (32 * il + 16) ^ sw;
-    const int4 xl0 = *reinterpret_cast<const int4*>(xa + o0), xl1 = *reinterpret_cast<const int4*>(xa + o1);
-    const int4 xh0 = *reinterpret_cast<const int4*>(xa + 128 + o0), xh1 = *reinterpret_cast<const int4*>(xa + 128 + o1);
+__device__ __forceinline__ float q4k_item(uint32_t sb, int il, int kblk, const GvX& X, int& dot0, int& dot1) {
+    const uint4 hdr = lds128(sb);
+    const uint4 w0 = lds128(sb + 16 + 32 * il), w1 = lds128(sb + 32 + 32 * il);
+    const uint32_t xa = X.xA + kblk * 256 + ((32 * il) ^ ((kblk & 1) << 4));   // the two 16-byte runs sit at xa and xa^16
+    const uint4 xl0 = lds128(xa), xl1 = lds128(xa ^ 16), xh0 = lds128(xa + 128), xh1 = lds128((xa ^ 16) + 128);
     if (XM == 0) {
         dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
         dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
     } else {
-        const uint8_t* xb = xa + p.K;
-        const uint4 yl0 = *reinterpret_cast<const uint4*>(xb + o0), yl1 = *reinterpret_cast<const uint4*>(xb + o1);
-        const uint4 yh0 = *reinterpret_cast<const uint4*>(xb + 128 + o0), yh1 = *reinterpret_cast<const uint4*>(xb + 128 + o1);
+        const uint32_t xb = xa + X.K;
+        const uint4 yl0 = lds128(xb), yl1 = lds128(xb ^ 16), yh0 = lds128(xb + 128), yh1 = lds128((xb ^ 16) + 128);
         dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
                (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
         dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
@@ -212,90 +221,91 @@ __device__ __forceinline__ float q4k_item(const uint8_t* sb, int il, int kblk, c
     const bool hi = il >= 2;
     const uint32_t sc2 = hi ? ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) : (a & 0x3F3Fu);
     const uint32_t mn2 = hi ? (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) : (b & 0x3F3Fu);
-    const float dall = h2f_bits(hdr.x & 0xFFFFu), dmin = h2f_bits(hdr.x >> 16);
-    const float2 d8 = *reinterpret_cast<const float2*>(smem + p.off_xd + (kblk * 8 + 2 * il) * 4);
-    const float2 s8 = *reinterpret_cast<const float2*>(smem + p.off_xs + (kblk * 8 + 2 * il) * 4);
-    const float pos = (float)((int)(sc2 & 0xFF) * dot0) * d8.x + (float)((int)(sc2 >> 8) * dot1) * d8.y;
-    const float neg = (float)(mn2 & 0xFF) * s8.x + (float)(mn2 >> 8) * s8.y;
-    return dall * pos - dmin * neg;
-}
-
-// 16 bytes from a 2-byte aligned shared-memory address: five aligned words, funnel-shifted.
-__device__ __forceinline__ void lds16_unaligned(const uint8_t* ptr, uint32_t out[4]) {
-    const uint32_t a = smem_u32(ptr), base = a & ~3u, sh = (a & 2u) * 8u;
-    uint32_t w[5];
-    #pragma unroll
-    for (int i = 0; i < 5; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(base + 4 * i));
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+    const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));      // (d, dmin)
+    const uint2 d8r = lds64(X.xd + (kblk * 8 + 2 * il) * 4), s8r = lds64(X.xs + (kblk * 8 + 2 * il) * 4);
+    const float pos = (float)((int)(sc2 & 0xFF) * dot0) * __uint_as_float(d8r.x) + (float)((int)(sc2 >> 8) * dot1) * __uint_as_float(d8r.y);
+    const float neg = (float)(mn2 & 0xFF) * __uint_as_float(s8r.x) + (float)(mn2 >> 8) * __uint_as_float(s8r.y);
+    return dm.x * pos - dm.y * neg;
 }
 
 // ── Q6_K: one (half n, column run c) per lane = 64 weights in four 16-element scale groups (quarters k = 0..3
 // at +32k), reference arithmetic src/kernels/gemv_q4.cu:581-618: per group  d*sc*(d8*dot)  with
-// dot = Σ(q6-32)·x = Σq6·x - 32·Σx.
+// dot = Σ(q6-32)·x = Σq6·x - 32·Σx.  Blocks are 2-byte aligned: each 16-byte run is read as five aligned words
+// and funnel-shifted.  n and c are fixed per lane.
 template <int XM>
-__device__ __forceinline__ float q6k_item(const uint8_t* sb, int n, int c, int kblk, const GvParams& p,
-                                          const uint8_t* smem, int dots_out[4]) {
+__device__ __forceinline__ float q6k_item(uint32_t sb, int n, int c, int kblk, const GvX& X, int dots_out[4]) {
+    const uint32_t al = sb & ~3u, sh = (sb & 2u) * 8u;
     uint32_t A[4], B[4], H[4];
-    lds16_unaligned(sb + 64 * n + 16 * c, A);
-    lds16_unaligned(sb + 64 * n + 32 + 16 * c, B);
-    lds16_unaligned(sb + 128 + 32 * n + 16 * c, H);
-    const float d = h2f_bits(*reinterpret_cast<const unsigned short*>(sb + 208));
-    const int8_t* scp = reinterpret_cast<const int8_t*>(sb + 192 + 8 * n + c);
-    const uint8_t* xb = smem + p.off_xB + (kblk * 4 + 2 * n + c) * 16;
-    const int*   xsum = reinterpret_cast<const int*>(smem + p.off_xsum) + kblk * 16 + 8 * n + c;
-    const float4 xd4  = *reinterpret_cast<const float4*>(smem + p.off_xd + (kblk * 8 + 4 * n) * 4);
-    const float xdv[4] = { xd4.x, xd4.y, xd4.z, xd4.w };
+    {
+        const uint32_t pa = al + 64 * n + 16 * c, ph = al + 128 + 32 * n + 16 * c;
+        uint32_t wa[5], wb[5], wh[5];
+        #pragma unroll
+        for (int i = 0; i < 5; ++i) { wa[i] = lds32(pa + 4 * i); wb[i] = lds32(pa + 32 + 4 * i); wh[i] = lds32(ph + 4 * i); }
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            A[i] = __funnelshift_r(wa[i], wa[i + 1], sh); B[i] = __funnelshift_r(wb[i], wb[i + 1], sh); H[i] = __funnelshift_r(wh[i], wh[i + 1], sh);
+        }
+    }
+    const float d = h2f_bits(lds_u16(sb + 208));
+    const uint32_t sca = sb + 192 + 8 * n + c;
+    const uint32_t xb = X.xB + (kblk * 4 + 2 * n + c) * 16;
+    const uint32_t xsa = X.xsum + (kblk * 16 + 8 * n + c) * 4;
+    const uint4 xdr = lds128(X.xd + (kblk * 8 + 4 * n) * 4);
+    const float xdv[4] = { __uint_as_float(xdr.x), __uint_as_float(xdr.y), __uint_as_float(xdr.z), __uint_as_float(xdr.w) };
+    // high bit pairs of the four quarters, already in place (bits 4-5 of every byte)
+    uint32_t Hq[4][4];
+    #pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        Hq[0][w] = (H[w] << 4) & 0x30303030u; Hq[1][w] = (H[w] << 2) & 0x30303030u;
+        Hq[2][w] = H[w] & 0x30303030u;        Hq[3][w] = (H[w] >> 2) & 0x30303030u;
+    }
     float acc = 0.f;
     #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const int4 xv = *reinterpret_cast<const int4*>(xb + k * (p.K >> 2));
-        const int xw[4] = { xv.x, xv.y, xv.z, xv.w };
+        const uint4 xv = lds128(xb + k * (X.K >> 2));
+        const uint32_t xw[4] = { xv.x, xv.y, xv.z, xv.w };
         uint32_t yw[4] = { 0, 0, 0, 0 };
-        if (XM == 1) {
-            const uint4 yv = *reinterpret_cast<const uint4*>(xb + p.K + k * (p.K >> 2));
-            yw[0] = yv.x; yw[1] = yv.y; yw[2] = yv.z; yw[3] = yv.w;
-        }
+        if (XM == 1) { const uint4 yv = lds128(xb + X.K + k * (X.K >> 2)); yw[0] = yv.x; yw[1] = yv.y; yw[2] = yv.z; yw[3] = yv.w; }
         int dh = 0, dl = 0;
         #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            uint32_t v;
-            if (k == 0)      v = (A[w] & 0x0F0F0F0Fu) | ((H[w] << 4) & 0x30303030u);
-            else if (k == 1) v = (B[w] & 0x0F0F0F0Fu) | ((H[w] << 2) & 0x30303030u);
-            else if (k == 2) v = ((A[w] >> 4) & 0x0F0F0F0Fu) | (H[w] & 0x30303030u);
-            else             v = ((B[w] >> 4) & 0x0F0F0F0Fu) | ((H[w] >> 2) & 0x30303030u);
-            dh = dp4a_us(v, xw[w], dh);
+            const uint32_t src = (k & 1) ? B[w] : A[w];
+            const uint32_t v = (((k & 2) ? (src >> 4) : src) & 0x0F0F0F0Fu) | Hq[k][w];
+            dh = dp4a_us(v, (int)xw[w], dh);
             if (XM == 1) dl = dp4a_uu(v, yw[w], dl);
         }
-        const int dot = (XM == 1 ? dh * 256 + dl : dh) - 32 * xsum[2 * k];
+        const int dot = (XM == 1 ? dh * 256 + dl : dh) - 32 * (int)lds32(xsa + 8 * k);
         dots_out[k] = dot;
-        acc += (float)dot * ((float)scp[2 * k] * xdv[k]);
+        acc += (float)dot * ((float)lds_s8(sca + 2 * k) * xdv[k]);
     }
     return d * acc;
 }
 
 // One warp, `nrw` (<= 4) consecutive rows in shared memory: lanes stride over the rows' 32-byte items
 // (4 per super-block), each lane adds its terms into the accumulator of the row the item belongs to.
+// Item i of the group is (row i / U, block (i % U) / 4, sub-item i % 4); 32 and U are multiples of 4, so a
+// lane's sub-item never changes.
 template <int XM, int TYPE, bool DBG>
-__device__ __forceinline__ void consume_rows(const uint8_t* rows, int nrw, int rb_, int U_, int lane, const GvParams& p,
-                                             const uint8_t* smem, float (&acc)[4], int32_t* dbg) {
+__device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, int U_, int lane, const GvX& X,
+                                             float (&acc)[4], int32_t* dbg) {
     const unsigned rb = (unsigned)rb_, U = (unsigned)U_, total = (unsigned)nrw * U;
     constexpr unsigned BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    const int sub = lane & 3;
     for (unsigned base = 0; base < total; base += 32) {
         const unsigned i = base + lane;
         const bool valid = i < total;
-        const unsigned ii = valid ? i : 0u;
+        const unsigned ii = valid ? i : (unsigned)sub;
         const unsigned rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
-        const unsigned j = ii - rl * U, blk = j >> 2, sub = j & 3;
-        const uint8_t* sb = rows + rl * rb + blk * BB;
+        const unsigned blk = (ii - rl * U) >> 2;
+        const uint32_t sb = rows + rl * rb + blk * BB;
         float term;
         if (TYPE == T_Q4K) {
             int d0, d1;
-            term = q4k_item<XM>(sb, (int)sub, (int)blk, p, smem, d0, d1);
+            term = q4k_item<XM>(sb, sub, (int)blk, X, d0, d1);
             if (DBG && dbg && valid) { int32_t* o = dbg + (size_t)rl * (2 * U) + blk * 8 + 2 * sub; o[0] = d0; o[1] = d1; }
         } else {
             int dots[4];
-            term = q6k_item<XM>(sb, (int)(sub >> 1), (int)(sub & 1), (int)blk, p, smem, dots);
+            term = q6k_item<XM>(sb, sub >> 1, sub & 1, (int)blk, X, dots);
             if (DBG && dbg && valid) {
                 int32_t* o = dbg + (size_t)rl * (4 * U) + blk * 16 + 8 * (sub >> 1) + (sub & 1);
                 o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
@@ -307,142 +317,155 @@ __device__ __forceinline__ void consume_rows(const uint8_t* rows, int nrw, int r
     }
 }
 
-struct GvPiece { int first, last, nch; };   // rows [first, last) of a segment, chunks of trc rows
+// A warp's unit of work is one row group (R consecutive rows of one matrix).  Every warp runs its own
+// pipeline: its lane 0 issues the bulk copy of a group into one of the warp's slots, the warp waits on that
+// slot's mbarrier, consumes the rows and moves on — no CTA-wide barrier in the loop, so dot products start
+// as soon as the first group lands while the rest of the CTA's bytes are still in flight.
+struct GvRange { int gf[3], gl[3]; };   // row groups [gf, gl) of each segment owned by this CTA
 
-__device__ __forceinline__ void gv_chunk(const GvParams& p, const GvPiece pc[3], int c, int& seg, int& r0, int& nrows) {
-    seg = 0;
-    #pragma unroll
-    for (int i = 0; i < 2; ++i)
-        if (seg == i && c >= pc[i].nch && i + 1 < p.nseg) { c -= pc[i].nch; seg = i + 1; }
-    const int trc = p.seg[seg].trc;
-    r0 = pc[seg].first + c * trc;
-    nrows = min(trc, pc[seg].last - r0);
+// task `u` of warp `warp` -> segment, first row, number of rows
+__device__ __forceinline__ bool gv_task(const GvParams& p, const GvRange& rg, int warp, int u, int& seg, int& row0, int& nrows) {
+    int g;
+    if (p.paired_rows) {               // (gate group, up group) of the same rows, back to back on one warp
+        seg = u & 1;
+        g = rg.gf[0] + warp + GV_WARPS * (u >> 1);
+        if (g >= rg.gl[0]) return false;
+    } else {
+        int t = warp + GV_WARPS * u;
+        seg = -1;
+        #pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const int cnt = rg.gl[i] - rg.gf[i];
+            if (seg < 0 && i < p.nseg) { if (t < cnt) { seg = i; g = rg.gf[i] + t; } else t -= cnt; }
+        }
+        if (seg < 0) return false;
+    }
+    const int R = p.seg[seg].R;
+    row0 = g * R;
+    nrows = min(R, p.seg[seg].M - row0);
+    return nrows > 0;
 }
 
-__device__ __forceinline__ void gv_issue(const GvParams& p, const GvPiece pc[3], int c, uint8_t* smem, uint64_t* full) {
-    int seg, r0, nrows;
-    gv_chunk(p, pc, c, seg, r0, nrows);
+__device__ __forceinline__ void gv_issue(const GvParams& p, int seg, int row0, int nrows, uint8_t* slot, uint64_t* bar) {
     const GvSegDev& s = p.seg[seg];
-    const uintptr_t g0 = (uintptr_t)s.W + (size_t)r0 * s.rb, g1 = g0 + (size_t)nrows * s.rb;
+    const uintptr_t g0 = (uintptr_t)s.W + (size_t)row0 * s.rb, g1 = g0 + (size_t)nrows * s.rb;
     const uintptr_t a0 = g0 & ~(uintptr_t)15;
     const uintptr_t endw = ((uintptr_t)s.W + (size_t)s.M * s.rb) & ~(uintptr_t)15;
     uintptr_t a1 = (g1 + 15) & ~(uintptr_t)15;
     if (a1 > endw) a1 = endw;                     // never read past the tensor; the tail comes by plain loads
-    const int slot = c % p.nslots;
     const uint32_t bytes = (uint32_t)(a1 - a0);
-    mbar_expect_tx(&full[slot], bytes);
-    bulk_g2s(smem + p.off_slots + (size_t)slot * p.slot_bytes, (const void*)a0, bytes, &full[slot]);
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(slot, (const void*)a0, bytes, bar);
 }
 
 template <int XM, bool DBG>
 __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GV_MAXSLOT];
+    __shared__ __align__(8) uint64_t full[GV_WARPS][GV_MAXSLOT];
     __shared__ float red[GV_WARPS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    // this CTA's rows in every segment: an even split of the row groups by bytes
-    GvPiece pc[3];
-    int nchunks = 0, pair_first = 0;
+    // this CTA's row groups in every segment: an even split of all groups by bytes
+    GvRange rg;
     {
         const long long G = gridDim.x, b = blockIdx.x;
-        if (p.paired_rows) {      // out_mode 3: the same row range of both matrices
-            const int R = p.seg[0].R, M = p.seg[0].M, groups = (M + R - 1) / R;
-            const int f = min(M, (int)((long long)groups * b / G) * R), l = min(M, (int)((long long)groups * (b + 1) / G) * R);
-            pair_first = f;
-            #pragma unroll
-            for (int i = 0; i < 2; ++i) { pc[i].first = f; pc[i].last = l; pc[i].nch = (l - f + p.seg[i].trc - 1) / p.seg[i].trc; nchunks += pc[i].nch; }
-            pc[2].first = pc[2].last = pc[2].nch = 0;
+        if (p.paired_rows) {      // out_mode 3: the same groups of both matrices
+            const int R = p.seg[0].R, groups = (p.seg[0].M + R - 1) / R;
+            rg.gf[0] = rg.gf[1] = (int)((long long)groups * b / G);
+            rg.gl[0] = rg.gl[1] = (int)((long long)groups * (b + 1) / G);
+            rg.gf[2] = rg.gl[2] = 0;
         } else {
             const long long lo = p.total_bytes * b / G, hi = p.total_bytes * (b + 1) / G;
             long long cum = 0;
             #pragma unroll
             for (int i = 0; i < 3; ++i) {
-                pc[i].first = pc[i].last = pc[i].nch = 0;
+                rg.gf[i] = rg.gl[i] = 0;
                 if (i < p.nseg) {
-                    const long long R = p.seg[i].R, M = p.seg[i].M, gb = R * p.seg[i].rb, groups = (M + R - 1) / R;
+                    const long long R = p.seg[i].R, gb = R * p.seg[i].rb, groups = (p.seg[i].M + R - 1) / R;
                     long long f = lo - cum <= 0 ? 0 : (lo - cum + gb - 1) / gb;
                     long long l = hi - cum <= 0 ? 0 : (hi - cum + gb - 1) / gb;
-                    f = f > groups ? groups : f; l = l > groups ? groups : l;
-                    pc[i].first = (int)min(M, f * R); pc[i].last = (int)min(M, l * R);
-                    pc[i].nch = (pc[i].last - pc[i].first + p.seg[i].trc - 1) / p.seg[i].trc;
-                    nchunks += pc[i].nch;
+                    rg.gf[i] = (int)(f > groups ? groups : f); rg.gl[i] = (int)(l > groups ? groups : l);
                     cum += gb * groups;
                 }
             }
         }
     }
-    if (tid == 0) {
-        for (int s = 0; s < p.nslots; ++s) mbar_init(&full[s], 1);
+    uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
+    if (lane == 0) {
+        for (int s = 0; s < p.nslots; ++s) mbar_init(&full[warp][s], 1);
         fence_mbar_init();
     }
-    __syncthreads();
-    if (tid == 0) {
-        const int pre = nchunks < p.nslots ? nchunks : p.nslots;
-        for (int c = 0; c < pre; ++c) gv_issue(p, pc, c, smem, full);   // weights do not depend on the previous kernel
+    __syncwarp();
+    if (lane == 0) {              // weights do not depend on the previous kernel: start fetching at once
+        for (int u = 0; u < p.nslots; ++u) {
+            int seg, row0, nrows;
+            if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
+            gv_issue(p, seg, row0, nrows, ring + (unsigned)u * (unsigned)p.slot_bytes, &full[warp][u]);
+        }
     }
+    pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
     pdl_wait();                  // x (and the residual) come from the kernel before us
     stage_x<XM>(p, smem, red);
     __syncthreads();
-    pdl_launch();
 
-    float* gate_s = reinterpret_cast<float*>(smem + p.off_gate);
+    const uint32_t sm0 = smem_u32(smem);
+    const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K };
     bool timed_out = false;
-    for (int c = 0; c < nchunks; ++c) {
-        const int slot = c % p.nslots;
-        // a wait that runs out is recorded and the loop carries on (every thread still
-        // reaches every barrier below); later waits are skipped
-        if (!timed_out && !mbar_wait_bounded(&full[slot], (c / p.nslots) & 1)) timed_out = true;
-        int seg, r0, nrows;
-        gv_chunk(p, pc, c, seg, r0, nrows);
+    float gate_keep[4] = { 0.f, 0.f, 0.f, 0.f };
+    for (int u = 0;; ++u) {
+        int seg, row0, nrows;
+        if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
+        const int slot = u % p.nslots;
+        // a wait that runs out is recorded and the loop carries on; later waits are skipped
+        if (!timed_out && !mbar_wait_bounded(&full[warp][slot], (u / p.nslots) & 1)) timed_out = true;
         const GvSegDev& s = p.seg[seg];
-        const uintptr_t g0 = (uintptr_t)s.W + (size_t)r0 * s.rb;
-        uint8_t* sdata = smem + p.off_slots + (unsigned)slot * (unsigned)p.slot_bytes + (unsigned)(g0 & 15);
+        const uintptr_t g0 = (uintptr_t)s.W + (size_t)row0 * s.rb;
+        uint8_t* rows = ring + (unsigned)slot * (unsigned)p.slot_bytes + (unsigned)(g0 & 15);
         {   // bytes between the last 16-byte boundary inside the tensor and its end
             const uintptr_t g1 = g0 + (size_t)nrows * s.rb;
             const uintptr_t endw = ((uintptr_t)s.W + (size_t)s.M * s.rb) & ~(uintptr_t)15;
-            if (g1 > endw) {     // CTA-uniform
+            if (g1 > endw) {     // warp-uniform
                 const int tail = (int)(g1 - endw);
-                if (tid < tail) sdata[(endw - g0) + tid] = reinterpret_cast<const uint8_t*>(endw)[tid];
-                __syncthreads();
+                if (lane < tail) rows[(endw - g0) + lane] = reinterpret_cast<const uint8_t*>(endw)[lane];
+                __syncwarp();
             }
         }
-        const int R = s.R, wrow0 = warp * R, type = s.type;
-        const int nrw = max(0, min(R, nrows - wrow0));
-        if (nrw > 0) {
-            const uint8_t* rows = sdata + (unsigned)wrow0 * (unsigned)s.rb;
-            float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-            int32_t* dbg = (DBG && seg == 0) ? p.dbg_dots + (size_t)(r0 + wrow0) * (type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
-            if (type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(rows, nrw, s.rb, s.U, lane, p, smem, acc, dbg);
-            else               consume_rows<XM, T_Q6K, DBG>(rows, nrw, s.rb, s.U, lane, p, smem, acc, dbg);
+        float acc[4] = { 0.f, 0.f, 0.f, 0.f };
+        int32_t* dbg = (DBG && seg == 0) ? p.dbg_dots + (size_t)row0 * (s.type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
+        if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, s.U, lane, X, acc, dbg);
+        else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, s.U, lane, X, acc, dbg);
+        __syncwarp();                            // the warp is done reading this slot
+        if (lane == 0) {
+            int seg2, row2, nrows2;
+            if (gv_task(p, rg, warp, u + p.nslots, seg2, row2, nrows2)) {
+                fence_proxy_async();
+                gv_issue(p, seg2, row2, nrows2, ring + (unsigned)slot * (unsigned)p.slot_bytes, &full[warp][slot]);
+            }
+        }
+        // row sums; lane r finishes row r
+        float mine = 0.f;
+        #pragma unroll
+        for (int r = 0; r < 4; ++r) { const float v = warp_sum(acc[r]); if (lane == r) mine = v; }
+        if (p.out_mode == 3 && seg == 0) {       // gate values stay in registers until the matching up rows arrive
             #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                if (r < nrw) {
-                    const float v = warp_sum(acc[r]);
-                    if (lane == 0) {
-                        const int row = r0 + wrow0 + r;
-                        if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(v);
-                        else if (p.out_mode == 1) reinterpret_cast<float*>(s.y)[row] = v;
-                        else if (p.out_mode == 2) {   // src/kernels/gemv_q4.cu:996-999
-                            const __half pr = __float2half_rn(v);
-                            reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), __half2float(p.residual[row])));
-                        } else {                      // fused SwiGLU of the gate/up pair (src/kernels/convert.cu:85-104)
-                            const float hv = __half2float(__float2half_rn(v));
-                            if (seg == 0) gate_s[row - pair_first] = hv;
-                            else {
-                                const float g = gate_s[row - pair_first];
-                                reinterpret_cast<__half*>(p.seg[0].y)[row] =
-                                    __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), hv));
-                            }
-                        }
-                    }
-                }
+            for (int r = 0; r < 4; ++r) gate_keep[r] = __shfl_sync(0xFFFFFFFFu, __half2float(__float2half_rn(mine)), r);
+            continue;
+        }
+        if (lane < nrows) {
+            const int row = row0 + lane;
+            if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(mine);
+            else if (p.out_mode == 1) reinterpret_cast<float*>(s.y)[row] = mine;
+            else if (p.out_mode == 2) {   // src/kernels/gemv_q4.cu:996-999
+                const __half pr = __float2half_rn(mine);
+                reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), __half2float(p.residual[row])));
+            } else {                      // fused SwiGLU of the gate/up pair (src/kernels/convert.cu:85-104)
+                const float hv = __half2float(__float2half_rn(mine));
+                const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
+                reinterpret_cast<__half*>(p.seg[0].y)[row] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), hv));
             }
         }
-        __syncthreads();                         // every warp is done with this slot
-        if (tid == 0 && c + p.nslots < nchunks) { fence_proxy_async(); gv_issue(p, pc, c + p.nslots, smem, full); }
     }
-    if (timed_out && tid == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
+    if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
 }
 
 // ── Q5_K (and nothing else): plain warp-per-row kernel with the reference's float
@@ -518,10 +541,10 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height and type");
     p.paired_rows = a.out_mode == 3;
     const int K = a.K, planes = a.xmode ? 2 : 1;
-    // Try 4, 2, then 1 CTA per SM: the shared-memory budget per CTA decides how many row groups fit a slot.
+    // Try 4, 2, then 1 CTA per SM: the shared-memory budget per CTA decides how large a row group each warp can stage.
     const int smem_sm = cx->max_smem_optin + 1024;           // per-SM shared memory (per-CTA opt-in limit + 1 KB reserve)
     for (int cps = 4; cps >= 1; cps >>= 1) {
-        int budget = smem_sm / cps - 1024 - 256;              // 1 KB system reserve per CTA, 256 B for static shared memory
+        int budget = smem_sm / cps - 1024 - 512;              // 1 KB system reserve per CTA, 512 B for static shared memory
         if (budget > cx->max_smem_optin - 1024) budget = cx->max_smem_optin - 1024;
         uint32_t off = 0;
         p.off_xA = off; off += p.needA ? planes * K : 0;
@@ -529,20 +552,15 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         p.off_xd = off; off += (K / 32) * 4;
         p.off_xs = off; off += (K / 32) * 4;
         p.off_xsum = off; off += p.needB ? (K / 16) * 4 : 0;
-        int grid = cx->sm_count * cps;
-        {   // rows of one CTA in paired mode: at most max(ceil(M/grid), 16) + 8
-            int rows = p.paired_rows ? (a.seg[0].M + grid - 1) / grid : 0;
-            rows = rows < 16 ? 16 : rows;
-            p.off_gate = off; off += p.paired_rows ? (uint32_t)(rows + 8) * 4 : 0;
-        }
+        p.off_gate = off;
         off = (off + 127) & ~127u;
         p.off_slots = off;
-        const int ring = budget - (int)off;
-        const int chunk_cap = ring / 2 - 16;                  // at least two slots
-        bool fits = chunk_cap > 0;
+        const int ring = (budget - (int)off) / GV_WARPS;      // bytes of staging ring per warp
+        const int slot_cap = ring / 2;                        // at least two slots per warp
+        bool fits = slot_cap > 0;
         int slot = 0;
         p.total_bytes = 0;
-        double worst_eff = 1.0;
+        long long groups_total = 0;
         for (int i = 0; i < a.nseg && fits; ++i) {
             GvSegDev& d = p.seg[i];
             d.W = (const uint8_t*)a.seg[i].W; d.y = a.seg[i].y; d.M = a.seg[i].M; d.type = a.seg[i].type;
@@ -550,32 +568,30 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
             d.U = nb * 4;
             int best = 0; double be = -1.0;
             for (int R = 1; R <= 4; R *= 2) {
-                if ((long long)GV_WARPS * R * d.rb + 16 > chunk_cap) break;
+                if ((long long)R * d.rb + 16 > slot_cap) break;
                 const double e = lane_eff(R, d.U);
                 if (e > be + 1e-9) { be = e; best = R; }
             }
             if (!best) { fits = false; break; }
             d.R = best; d.trc = GV_WARPS * best;
-            worst_eff = be < worst_eff ? be : worst_eff;
-            const int need = ((d.trc * d.rb + 16 + 127) / 128) * 128;
+            const int need = ((d.R * d.rb + 16 + 127) / 128) * 128;
             slot = need > slot ? need : slot;
             const long long groups = (d.M + d.R - 1) / d.R;
             p.total_bytes += groups * d.R * d.rb;
+            groups_total += groups;
         }
-        if (!fits) {
+        if (!fits || ring / slot < 2) {
             if (cps == 1) return set_error(JB_ERR_LIMIT, "gemv: one row group does not fit the staging ring (K=%d)", K);
             continue;
         }
-        (void)worst_eff;
         p.slot_bytes = slot;
         p.nslots = ring / slot;
         if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
-        if (p.nslots < 2) { if (cps == 1) return set_error(JB_ERR_LIMIT, "gemv: staging ring does not fit (slot %d B)", slot); continue; }
-        const size_t smem_bytes = (size_t)p.off_slots + (size_t)p.nslots * slot;
-        long long groups_total = 0;
-        for (int i = 0; i < a.nseg; ++i) groups_total += (p.seg[i].M + p.seg[i].R - 1) / p.seg[i].R;
+        const size_t smem_bytes = (size_t)p.off_slots + (size_t)GV_WARPS * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
-        if (grid > groups_total) grid = (int)groups_total;
+        int grid = cx->sm_count * cps;
+        const long long ctas_useful = (groups_total + GV_WARPS - 1) / GV_WARPS;
+        if (grid > ctas_useful) grid = (int)ctas_useful;
         if (grid < 1) grid = 1;
         auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
                                : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);

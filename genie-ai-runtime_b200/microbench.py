@@ -53,7 +53,8 @@ def main():
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--swiglu", action="store_true", help="pair: SwiGLU applied in the epilogue")
+    ap.add_argument("--norm", action="store_true", help="pair/triple: RMSNorm fused in front of the activation quantiser")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python every iteration instead of replaying a CUDA graph")
     a = ap.parse_args()
@@ -87,7 +88,11 @@ def main():
             elif a.kind == "f32":
                 calls.append(lambda W=W: jb.gemv_quant_f32(ys[0], W[0], t, x, M, K, st))
             elif a.kind == "pair" and a.swiglu:
-                calls.append(lambda W=W: jb.norm_gemv_pair_swiglu(ys[0], W[0], W[1], t, M, x, nw, True, 1e-6, K, st))
+                calls.append(lambda W=W: jb.norm_gemv_pair_swiglu(ys[0], W[0], W[1], t, M, x, nw if a.norm else None, True, 1e-6, K, st))
+            elif a.kind == "pair" and a.norm:
+                calls.append(lambda W=W: jb.norm_gemv_quant_pair(ys[0], W[0], t, M, ys[1], W[1], t, M, x, nw, True, 1e-6, K, st))
+            elif a.kind == "triple" and a.norm:
+                calls.append(lambda W=W: jb.norm_gemv_quant_triple(ys[0], W[0], 12, Ms[0], ys[1], W[1], 12, Ms[1], ys[2], W[2], 14, Ms[2], x, nw, True, 1e-6, K, st))
             elif a.kind == "pair":
                 calls.append(lambda W=W: jb.gemv_quant_pair(ys[0], W[0], t, M, ys[1], W[1], t, M, x, K, st))
             elif a.kind == "triple":
