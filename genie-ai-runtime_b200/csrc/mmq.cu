@@ -5,6 +5,8 @@
 // weight sub-scales as half products, Q6_K keeps fp32 d (mmq_q4k_llama.cu:383-404,
 // :159-163, :321-322; mmq_q6k_llama.cu:424-438, :208, :361).
 #include "mmq.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace jb {
 
@@ -106,6 +108,14 @@ int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N
     if (type != T_Q4K && type != T_Q6K) return set_error(JB_ERR_TYPE, "batched gemm: ggml type %d", type);
     if (!y || !W || !x) return set_error(JB_ERR_PTR, "batched gemm: null pointer");
     if (type == T_Q4K && ((uintptr_t)W & 3)) return set_error(JB_ERR_PTR, "batched gemm: Q4_K weights must be 4-byte aligned");
+    // JLLM_B200_MMQ=cuda keeps the CUDA-core kernel (the one that can also export the integer accumulators)
+    static const bool tc_off = [] { const char* e = getenv("JLLM_B200_MMQ"); return e && !strcmp(e, "cuda"); }();
+    if (!dbg && !tc_off && mmq_tc_applies(W, type, M, N, K)) {
+        const size_t need_tc = mmq_tc_scratch_bytes(type, N, K);
+        __half* xq = (__half*)mmq_scratch(need_tc, !capturing(st));
+        if (!xq) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_tc);
+        return launch_mmq_tc(y, W, type, x, xq, M, N, K, st);
+    }
     const size_t need = mmq_scratch_bytes(N, K);
     uint8_t* base = (uint8_t*)mmq_scratch(need, !capturing(st));
     if (!base) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need);

@@ -1,0 +1,384 @@
+// mmq_tc.cu — batched K-quant GEMM (prefill) on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, the activation operand staged by TMA, for sm_100a.
+//
+// Replaces the reference's default prefill path (gemm_quant_batched -> mul_mat_q_llama, src/kernels/gemv_q4.cu:2478-2495,
+// mmq_q4k_llama.cu:408-512).  The reference multiplies int8 codes per 32-element sub-block and rescales every
+// partial sum on the CUDA cores (sum += dmA.x*dsB.x*C + dmA.y*dsB.y, mmq_q4k_llama.cu:321-322): on B200 that
+// epilogue, not the tensor pipe, would set the speed, because scales change every 32 elements.  Here the same
+// numbers are produced by ONE accumulation over the whole K range:
+//     y[t][r] = Σ_k  half(dA[r,sb(k)] * q4[r,k]) * half(d8[t,sb(k)] * q8[t,k])  +  Σ_sb half(-dmin*m)[r,sb] * half(Σx)[t,sb]
+// i.e. an fp16 x fp16 -> fp32 GEMM over K + K/32 columns whose A operand is dequantised on the fly from the GGUF
+// blocks with the reference's own half-precision scale products (mmq_q4k_llama.cu:159-163) and whose B operand is
+// the reference's quantised activation (codes x scale, and the per-group sums of the DS4 layout, :383-404).
+// The only difference from the reference's arithmetic is the rounding of the two products to fp16 (2^-11
+// relative each, random), about 1e-5 of the result.
+//
+// Shape of the kernel: CTA tile 128 (rows) x 256 (tokens), K tiles of 64; 6 warps:
+//   warp 0    TMA producer of the activation tile (cp.async.bulk.tensor.2d, 128-byte swizzle)
+//   warp 1    issues tcgen05.mma (one elected lane), commits stages back to the producers
+//   warps 2-5 dequantise the weight tile into the 128-byte-swizzled K-major layout, later drain the accumulator
+//             (tcgen05.ld) and store fp16 results token-major.
+// Every mbarrier wait is bounded; a wait that runs out sets the device status word, the kernel still frees
+// its tensor memory and returns.
+#include "mmq.cuh"
+#include <cuda.h>
+
+namespace jb {
+
+constexpr int TC_M = 128, TC_N = 256, TC_K = 64, TC_STAGES = 2;
+constexpr int TC_A_BYTES = TC_M * TC_K * 2;       // 16 KB
+constexpr int TC_B_BYTES = TC_N * TC_K * 2;       // 32 KB
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;    // + alignment slack
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+
+struct TcArgs {
+    __half* y; const uint8_t* W; int type; int M, N, K;
+    int n_main, n_min;        // K tiles of weights, K tiles of the min term
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// K-major operand tile, 128-byte rows, 128-byte swizzle, 8-row atoms 1024 bytes apart
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16 bytes = 8 fp16 weights of row `rl` written at K-chunk `c` (0..7) of a swizzled 128-byte row
+__device__ __forceinline__ void tc_store_chunk(uint8_t* a_tile, int rl, int c, uint4 v) {
+    *reinterpret_cast<uint4*>(a_tile + rl * 128 + ((c ^ (rl & 7)) << 4)) = v;
+}
+// four nibbles (already masked to 0x0F0F0F0F) -> four halves scaled by dA, as two half2 words
+__device__ __forceinline__ void tc_nib4(uint32_t n4, __half2 dA, uint32_t& lo, uint32_t& hi) {
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+    const uint32_t a = __byte_perm(n4, 0, 0x4140) | 0x64006400u, b = __byte_perm(n4, 0, 0x4342) | 0x64006400u;
+    const __half2 ha = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&a), k1024), dA);
+    const __half2 hb = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&b), k1024), dA);
+    lo = *reinterpret_cast<const uint32_t*>(&ha); hi = *reinterpret_cast<const uint32_t*>(&hb);
+}
+
+// a 32-bit word at a 2-byte-aligned address (Q6_K blocks are 210 bytes): two aligned loads and a funnel shift
+__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) {
+    const uintptr_t u = (uintptr_t)p;
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(u & ~(uintptr_t)3);
+    const uint32_t lo = __ldg(q);
+    if (!(u & 2)) return lo;
+    return __funnelshift_r(lo, __ldg(q + 1), 16);
+}
+
+// Q4_K: K tile `t` = quarter `il` of block `blk` = sub-blocks 2il (low nibbles) and 2il+1 (high nibbles)
+__device__ __forceinline__ void tc_dequant_q4k(uint8_t* a_tile, int rl, const uint8_t* b, int il) {
+    const uint32_t* hw = reinterpret_cast<const uint32_t*>(b);
+    const uint32_t dm = __ldg(hw), s0 = __ldg(hw + 1), s1 = __ldg(hw + 2), s2 = __ldg(hw + 3);
+    int sc0, mn0, sc1, mn1;
+    scale_min_k4(2 * il, s0, s1, s2, sc0, mn0);
+    scale_min_k4(2 * il + 1, s0, s1, s2, sc1, mn1);
+    const __half dh = __ushort_as_half((unsigned short)(dm & 0xFFFFu));
+    const __half2 dA0 = __half2half2(__hmul(dh, __int2half_rn(sc0)));      // half product, mmq_q4k_llama.cu:159-163
+    const __half2 dA1 = __half2half2(__hmul(dh, __int2half_rn(sc1)));
+    const uint4* qp = reinterpret_cast<const uint4*>(b + 16 + 32 * il);
+    #pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint4 q = __ldg(qp + h);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        #pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint4 lo, hi;
+            tc_nib4(w[2 * c] & 0x0F0F0F0Fu, dA0, lo.x, lo.y);
+            tc_nib4(w[2 * c + 1] & 0x0F0F0F0Fu, dA0, lo.z, lo.w);
+            tc_nib4((w[2 * c] >> 4) & 0x0F0F0F0Fu, dA1, hi.x, hi.y);
+            tc_nib4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, dA1, hi.z, hi.w);
+            tc_store_chunk(a_tile, rl, 2 * h + c, lo);
+            tc_store_chunk(a_tile, rl, 4 + 2 * h + c, hi);
+        }
+    }
+}
+
+// Q4_K min term: column j of tile `tm` is sub-block 64*tm + j; value half(-dmin) * half(m)
+__device__ __forceinline__ void tc_dequant_q4k_min(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm) {
+    #pragma unroll 1
+    for (int c = 0; c < 8; ++c) {
+        const int blk = 8 * tm + c;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row_blocks && blk < nb) {
+            const uint32_t* hw = reinterpret_cast<const uint32_t*>(row_blocks + (size_t)blk * Q4K_BYTES);
+            const uint32_t dm = __ldg(hw), s0 = __ldg(hw + 1), s1 = __ldg(hw + 2), s2 = __ldg(hw + 3);
+            const __half mh = __hneg(__ushort_as_half((unsigned short)(dm >> 16)));
+            unsigned short o[8];
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int sc, mn; scale_min_k4(j, s0, s1, s2, sc, mn);
+                o[j] = __half_as_ushort(__hmul(mh, __int2half_rn(mn)));
+            }
+            v = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
+        }
+        tc_store_chunk(a_tile, rl, c, v);
+    }
+}
+
+// Q6_K: K tile q4 (0..3) of a block = half n = q4>>1, quarters 2kp and 2kp+1 (kp = q4&1): low (kp=0) or high
+// (kp=1) nibbles of ql[64n .. 64n+63], bits 4kp..4kp+3 of qh[32n .. 32n+31], scales 8n+4kp .. +3.
+// Values d*sc*(q-32) are formed as q * hi + q * lo with (hi, lo) the fp16 split of the fp32 product d*sc,
+// so each weight is rounded to fp16 once.
+__device__ __forceinline__ void tc_dequant_q6k(uint8_t* a_tile, int rl, const uint8_t* b, int q4) {
+    const int n = q4 >> 1, kp = q4 & 1;
+    const float d = h2f_bits(__ldg(reinterpret_cast<const unsigned short*>(b + 208)));
+    const uint32_t sc4 = ldg_u32_a2(b + 192 + 8 * n + 4 * kp);
+    __half2 shi[4], slo[4];
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float ds = __fmul_rn(d, (float)(int)(int8_t)((sc4 >> (8 * i)) & 0xFF));
+        const __half h = __float2half_rn(ds);
+        shi[i] = __half2half2(h);
+        slo[i] = __half2half2(__float2half_rn(ds - __half2float(h)));
+    }
+    const __half2 k1056 = __half2half2(__ushort_as_half((unsigned short)0x6420));   // 1024 + 32
+    uint32_t H[8];
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) H[i] = ldg_u32_a2(b + 128 + 32 * n + 4 * i) >> (4 * kp);
+    #pragma unroll
+    for (int qq = 0; qq < 2; ++qq) {           // quarter 2kp + qq: elements 32qq .. 32qq+31 of the tile
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {          // chunk of 8 elements = two ql words
+            uint32_t out[4];
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int wi = 2 * c + h;      // word index inside the quarter (l = 4wi .. 4wi+3)
+                const uint32_t L = (ldg_u32_a2(b + 64 * n + 32 * qq + 4 * wi) >> (4 * kp)) & 0x0F0F0F0Fu;
+                const uint32_t q6 = L | (((H[wi] >> (2 * qq)) & 0x03030303u) << 4);
+                const uint32_t a = __byte_perm(q6, 0, 0x4140) | 0x64006400u, bb = __byte_perm(q6, 0, 0x4342) | 0x64006400u;
+                const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&a), k1056);
+                const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&bb), k1056);
+                const int si = 2 * qq + (wi >> 2);                      // 16-element scale group
+                const __half2 ra = __hfma2(qa, shi[si], __hmul2(qa, slo[si]));
+                const __half2 rb = __hfma2(qb, shi[si], __hmul2(qb, slo[si]));
+                out[2 * h] = *reinterpret_cast<const uint32_t*>(&ra);
+                out[2 * h + 1] = *reinterpret_cast<const uint32_t*>(&rb);
+            }
+            tc_store_chunk(a_tile, rl, 4 * qq + c, make_uint4(out[0], out[1], out[2], out[3]));
+        }
+    }
+}
+
+// activation operand: X'[t][0..K) = half(d*q) (codes x scale of the reference's quantiser, mmq_q4k_llama.cu:383-404,
+// mmq_q6k_llama.cu:424-438), X'[t][K + g] = half(sum of group g) for Q4_K, zero up to the padded width Kp.
+__global__ void mmq_tc_quantize_kernel(const __half* x, __half* xq, int N, int K, int Kp, int ds4) {
+    pdl_wait();
+    const long long g = (long long)blockIdx.x * blockDim.y + threadIdx.y;
+    const int lane = threadIdx.x, G = K / 32;
+    if (g >= (long long)N * G) return;
+    const long long t = g / G; const int gi = (int)(g - t * G);
+    const float v = __half2float(x[g * 32 + lane]);
+    const float amax = warp_max(fabsf(v));
+    float sum = v;
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    float d = __fdiv_rn(amax, 127.0f);
+    const float dinv = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+    const int q = __float2int_rn(__fmul_rn(v, dinv));
+    if (ds4) d = __half2float(__float2half_rn(d));
+    __half* row = xq + t * Kp;
+    row[gi * 32 + lane] = __float2half_rn(__fmul_rn(d, (float)q));
+    if (lane == 0 && K + gi < Kp) row[K + gi] = ds4 ? __float2half_rn(sum) : __float2half_rn(0.f);
+    if (gi == 0) for (int c = K + (ds4 ? G : 0) + lane; c < Kp; c += 32) row[c] = __float2half_rn(0.f);
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(TC_THREADS, 2) mmq_tc_kernel(const __grid_constant__ CUtensorMap xmap, TcArgs a, int n_tile) {
+    extern __shared__ uint8_t tc_smem_raw[];
+    __shared__ uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int fail;
+    uint8_t* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * n_tile, m0 = blockIdx.y * TC_M;
+    const int n_tiles = a.n_main + a.n_min;
+    const uint32_t b_bytes = (uint32_t)n_tile * TC_K * 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_a[s], 128); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(&acc_bar, 1);
+        fence_mbar_init();
+        fail = 0;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int t = 0; t < n_tiles && !fail; ++t) {
+                const int s = t % TC_STAGES, it = t / TC_STAGES;
+                if (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT)) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); break; }
+                mbar_expect_tx(&full_b[s], b_bytes);
+                tma_load_2d(smem + s * TC_STAGE_BYTES + TC_A_BYTES, &xmap, t * TC_K, n0, &full_b[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n_tile
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(n_tile >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+            bool ok = true;
+            for (int t = 0; t < n_tiles && !fail; ++t) {
+                const int s = t % TC_STAGES, it = t / TC_STAGES;
+                if (!mbar_wait_bounded(&full_a[s], it & 1, TC_WAIT_LIMIT) || !mbar_wait_bounded(&full_b[s], it & 1, TC_WAIT_LIMIT)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t ad = tc_smem_desc(smem_u32(smem + s * TC_STAGE_BYTES));
+                const uint64_t bd = tc_smem_desc(smem_u32(smem + s * TC_STAGE_BYTES + TC_A_BYTES));
+                #pragma unroll
+                for (int j = 0; j < TC_K / 16; ++j) tc_mma_f16(tmem, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((t | j) != 0));
+                tc_commit(&empty[s]);
+            }
+            if (!ok) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
+            tc_commit(&acc_bar);
+        }
+    } else {
+        const int rl = (warp & 3) * 32 + lane, row = m0 + rl;
+        const int nb = a.K / QK_K;
+        const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * (TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES) : nullptr;
+        bool ok = true;
+        for (int t = 0; t < n_tiles && !fail; ++t) {
+            const int s = t % TC_STAGES, it = t / TC_STAGES;
+            if (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT)) { ok = false; break; }
+            uint8_t* at = smem + s * TC_STAGE_BYTES;
+            if (!rowp) {
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) tc_store_chunk(at, rl, c, make_uint4(0, 0, 0, 0));
+            } else if (t < a.n_main) {
+                if (TYPE == T_Q4K) tc_dequant_q4k(at, rl, rowp + (size_t)(t >> 2) * Q4K_BYTES, t & 3);
+                else               tc_dequant_q6k(at, rl, rowp + (size_t)(t >> 2) * Q6K_BYTES, t & 3);
+            } else {
+                tc_dequant_q4k_min(at, rl, rowp, nb, t - a.n_main);
+            }
+            fence_proxy_async();
+            mbar_arrive(&full_a[s]);
+        }
+        if (!ok) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
+        // drain the accumulator: this warp owns TMEM lanes 32*(warp%4) .. +31 = rows rl
+        if (!fail && mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT)) {
+            tc_fence_after();
+            for (int cb = 0; cb < n_tile; cb += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cb, r);
+                if (row < a.M) {
+                    #pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = n0 + cb + j;
+                        if (tok < a.N) a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+        } else if (!fail) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        // a timed-out run may still have MMAs in flight: give them the same bounded wait before the columns are freed
+        if (fail && lane == 0) mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT);
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+size_t mmq_tc_scratch_bytes(int type, int N, int K) {
+    const int n_min = type == T_Q4K ? (K / 32 + TC_K - 1) / TC_K : 0;
+    return (size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half) + 256;
+}
+
+bool mmq_tc_applies(const void* W, int type, int M, int N, int K) {
+    if (type != T_Q4K && type != T_Q6K) return false;
+    if (type == T_Q4K && ((uintptr_t)W & 15)) return false;      // 16-byte loads of the nibble words
+    if (type == T_Q6K && ((uintptr_t)W & 1)) return false;
+    return N >= 2 && M >= 1 && K % QK_K == 0 && encode_tiled_fn() != nullptr;
+}
+
+int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* xq, int M, int N, int K, cudaStream_t st) {
+    DeviceCtx* c = ctx();
+    if (!c) return set_error(JB_ERR_STATE, "batched gemm: library not initialised");
+    TcArgs a;
+    a.y = y; a.W = (const uint8_t*)W; a.type = type; a.M = M; a.N = N; a.K = K;
+    a.n_main = K / TC_K;
+    a.n_min = type == T_Q4K ? (K / 32 + TC_K - 1) / TC_K : 0;
+    a.status = c->d_status;
+    const int Kp = (a.n_main + a.n_min) * TC_K;
+    const int n_tile = N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;
+
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)Kp, (cuuint64_t)N};
+    const cuuint64_t gstr[1] = {(cuuint64_t)Kp * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_K, (cuuint32_t)n_tile};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xq, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(JB_ERR_CUDA, "batched gemm: tensor map for the activation tile refused (driver code %d)", (int)r);
+
+    static bool attr_done[2] = {false, false};
+    const int ti = type == T_Q4K ? 0 : 1;
+    if (!attr_done[ti]) {
+        if (ti == 0) JB_CUDA(cudaFuncSetAttribute(mmq_tc_kernel<T_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+        else         JB_CUDA(cudaFuncSetAttribute(mmq_tc_kernel<T_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+        attr_done[ti] = true;
+    }
+    const long long groups = (long long)N * (K / 32);
+    JB_CUDA(launch_k(mmq_tc_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xq, N, K, Kp, (int)(type == T_Q4K)));
+    count_launch();
+    const dim3 grid((N + n_tile - 1) / n_tile, (M + TC_M - 1) / TC_M);
+    if (ti == 0) JB_CUDA(launch_k(mmq_tc_kernel<T_Q4K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
+    else         JB_CUDA(launch_k(mmq_tc_kernel<T_Q6K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
+    count_launch();
+    return JB_OK;
+}
+
+}  // namespace jb

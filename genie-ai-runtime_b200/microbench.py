@@ -149,7 +149,8 @@ def main():
             e1.record(st)
         torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / a.iters
-    print(json.dumps({"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes,
+    extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else {}
+    print(json.dumps({"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes, **extra,
                       "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "graph": not a.no_graph, "device_status": jb.device_status(st)}))
 
 
