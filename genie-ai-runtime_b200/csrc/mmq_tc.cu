@@ -13,15 +13,16 @@
 // The only difference from the reference's arithmetic is the rounding of the two products to fp16 (2^-11
 // relative each, random), about 1e-5 of the result.
 //
-// Shape of the kernel: CTA tile 128 (rows) x 256 (tokens), K tiles of 64; 6 warps:
+// Shape of the kernel: CTA tile 128 (rows) x 256 (tokens), K tiles of 64; 10 warps:
 //   warp 0    TMA producer of the activation tile (cp.async.bulk.tensor.2d, 128-byte swizzle)
 //   warp 1    issues tcgen05.mma (one elected lane), commits stages back to the producers
-//   warps 2-5 dequantise the weight tile into the 128-byte-swizzled K-major layout, later drain the accumulator
+//   warps 2-9 dequantise the weight tile (two threads per row) into the 128-byte-swizzled K-major layout, later drain the accumulator
 //             (tcgen05.ld) and store fp16 results token-major.
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word, the kernel still frees
 // its tensor memory and returns.
 #include "mmq.cuh"
 #include <cuda.h>
+#include <type_traits>
 
 namespace jb {
 
@@ -30,7 +31,7 @@ constexpr int TC_A_BYTES = TC_M * TC_K * 2;       // 16 KB
 constexpr int TC_B_BYTES = TC_N * TC_K * 2;       // 32 KB
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;    // + alignment slack
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;        // TMA warp, MMA warp, 8 dequantise/drain warps
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 struct TcArgs {
@@ -82,57 +83,52 @@ __device__ __forceinline__ void tc_nib4(uint32_t n4, __half2 dA, uint32_t& lo, u
     lo = *reinterpret_cast<const uint32_t*>(&ha); hi = *reinterpret_cast<const uint32_t*>(&hb);
 }
 
-// a 32-bit word at a 2-byte-aligned address (Q6_K blocks are 210 bytes): two aligned loads and a funnel shift
-__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) {
-    const uintptr_t u = (uintptr_t)p;
-    const uint32_t* q = reinterpret_cast<const uint32_t*>(u & ~(uintptr_t)3);
-    const uint32_t lo = __ldg(q);
-    if (!(u & 2)) return lo;
-    return __funnelshift_r(lo, __ldg(q + 1), 16);
-}
+// Two threads share a weight row: thread `h` (0/1) of a row owns bytes 16h..16h+15 of every 32-byte run of
+// packed codes, i.e. elements 16h..16h+15 of each 32-element sub-block or quarter.  Raw bytes are fetched one
+// whole group of K tiles ahead (Q4_K: a block = 4 tiles; Q6_K: half a block = 2 tiles), so the global-load
+// latency overlaps the dequantisation of the group before.
+struct RawQ4 { uint4 hdr; uint4 q[4]; };                     // header + this thread's 16 bytes of each tile
+struct RawQ6 { uint32_t ql[2][5], qh[5], sc[3], d; };        // aligned words around this thread's bytes
 
-// Q4_K: K tile `t` = quarter `il` of block `blk` = sub-blocks 2il (low nibbles) and 2il+1 (high nibbles)
-__device__ __forceinline__ void tc_dequant_q4k(uint8_t* a_tile, int rl, const uint8_t* b, int il) {
-    const uint32_t* hw = reinterpret_cast<const uint32_t*>(b);
-    const uint32_t dm = __ldg(hw), s0 = __ldg(hw + 1), s1 = __ldg(hw + 2), s2 = __ldg(hw + 3);
+__device__ __forceinline__ void tc_load_q4k(RawQ4& r, const uint8_t* b, int h) {
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(b));
+    #pragma unroll
+    for (int il = 0; il < 4; ++il) r.q[il] = __ldg(reinterpret_cast<const uint4*>(b + 16 + 32 * il + 16 * h));
+}
+// tile il of the block: low nibbles -> sub-block 2il (tile columns 16h..), high nibbles -> sub-block 2il+1 (32+16h..)
+__device__ __forceinline__ void tc_dequant_q4k(uint8_t* a_tile, int rl, const RawQ4& r, int il, int h) {
     int sc0, mn0, sc1, mn1;
-    scale_min_k4(2 * il, s0, s1, s2, sc0, mn0);
-    scale_min_k4(2 * il + 1, s0, s1, s2, sc1, mn1);
-    const __half dh = __ushort_as_half((unsigned short)(dm & 0xFFFFu));
+    scale_min_k4(2 * il, r.hdr.y, r.hdr.z, r.hdr.w, sc0, mn0);
+    scale_min_k4(2 * il + 1, r.hdr.y, r.hdr.z, r.hdr.w, sc1, mn1);
+    const __half dh = __ushort_as_half((unsigned short)(r.hdr.x & 0xFFFFu));
     const __half2 dA0 = __half2half2(__hmul(dh, __int2half_rn(sc0)));      // half product, mmq_q4k_llama.cu:159-163
     const __half2 dA1 = __half2half2(__hmul(dh, __int2half_rn(sc1)));
-    const uint4* qp = reinterpret_cast<const uint4*>(b + 16 + 32 * il);
+    const uint32_t w[4] = {r.q[il].x, r.q[il].y, r.q[il].z, r.q[il].w};
     #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint4 q = __ldg(qp + h);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-        #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            uint4 lo, hi;
-            tc_nib4(w[2 * c] & 0x0F0F0F0Fu, dA0, lo.x, lo.y);
-            tc_nib4(w[2 * c + 1] & 0x0F0F0F0Fu, dA0, lo.z, lo.w);
-            tc_nib4((w[2 * c] >> 4) & 0x0F0F0F0Fu, dA1, hi.x, hi.y);
-            tc_nib4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, dA1, hi.z, hi.w);
-            tc_store_chunk(a_tile, rl, 2 * h + c, lo);
-            tc_store_chunk(a_tile, rl, 4 + 2 * h + c, hi);
-        }
+    for (int c = 0; c < 2; ++c) {
+        uint4 lo, hi;
+        tc_nib4(w[2 * c] & 0x0F0F0F0Fu, dA0, lo.x, lo.y);
+        tc_nib4(w[2 * c + 1] & 0x0F0F0F0Fu, dA0, lo.z, lo.w);
+        tc_nib4((w[2 * c] >> 4) & 0x0F0F0F0Fu, dA1, hi.x, hi.y);
+        tc_nib4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, dA1, hi.z, hi.w);
+        tc_store_chunk(a_tile, rl, 2 * h + c, lo);
+        tc_store_chunk(a_tile, rl, 4 + 2 * h + c, hi);
     }
 }
 
-// Q4_K min term: column j of tile `tm` is sub-block 64*tm + j; value half(-dmin) * half(m)
-__device__ __forceinline__ void tc_dequant_q4k_min(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm) {
+// Q4_K min term: column j of tile `tm` is sub-block 64*tm + j; value half(-dmin) * half(m); thread h writes chunks 4h..4h+3
+__device__ __forceinline__ void tc_dequant_q4k_min(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm, int h) {
     #pragma unroll 1
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 4 * h; c < 4 * h + 4; ++c) {
         const int blk = 8 * tm + c;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row_blocks && blk < nb) {
-            const uint32_t* hw = reinterpret_cast<const uint32_t*>(row_blocks + (size_t)blk * Q4K_BYTES);
-            const uint32_t dm = __ldg(hw), s0 = __ldg(hw + 1), s1 = __ldg(hw + 2), s2 = __ldg(hw + 3);
-            const __half mh = __hneg(__ushort_as_half((unsigned short)(dm >> 16)));
+            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(row_blocks + (size_t)blk * Q4K_BYTES));
+            const __half mh = __hneg(__ushort_as_half((unsigned short)(hd.x >> 16)));
             unsigned short o[8];
             #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                int sc, mn; scale_min_k4(j, s0, s1, s2, sc, mn);
+                int sc, mn; scale_min_k4(j, hd.y, hd.z, hd.w, sc, mn);
                 o[j] = __half_as_ushort(__hmul(mh, __int2half_rn(mn)));
             }
             v = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
@@ -142,45 +138,59 @@ __device__ __forceinline__ void tc_dequant_q4k_min(uint8_t* a_tile, int rl, cons
 }
 
 // Q6_K: K tile q4 (0..3) of a block = half n = q4>>1, quarters 2kp and 2kp+1 (kp = q4&1): low (kp=0) or high
-// (kp=1) nibbles of ql[64n .. 64n+63], bits 4kp..4kp+3 of qh[32n .. 32n+31], scales 8n+4kp .. +3.
+// (kp=1) nibbles of ql[64n .. 64n+63], bits 4kp..4kp+3 of qh[32n .. 32n+31], scales 8n+4kp .. +3.  Both tiles of a
+// half use the same bytes, so one fetch serves two tiles.  Blocks are 210 bytes, hence only 2-byte aligned:
+// every field is read as aligned words around it and re-aligned with a funnel shift (all fields of a block share
+// its misalignment).  The word past a field is fetched only when the block is misaligned, so nothing beyond the
+// block is touched.
+__device__ __forceinline__ void tc_load_q6k(RawQ6& r, const uint8_t* b, int n, int h) {
+    const bool mis = ((uintptr_t)b & 2) != 0;
+    const uint32_t* base = reinterpret_cast<const uint32_t*>((uintptr_t)b & ~(uintptr_t)3);
+    #pragma unroll
+    for (int qq = 0; qq < 2; ++qq) {
+        const uint32_t* pl = base + 16 * n + 8 * qq + 4 * h;
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) r.ql[qq][i] = __ldg(pl + i);
+        r.ql[qq][4] = mis ? __ldg(pl + 4) : 0u;
+    }
+    const uint32_t* ph = base + 32 + 8 * n + 4 * h;
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) r.qh[i] = __ldg(ph + i);
+    r.qh[4] = mis ? __ldg(ph + 4) : 0u;
+    const uint32_t* ps = base + 48 + 2 * n;
+    r.sc[0] = __ldg(ps); r.sc[1] = __ldg(ps + 1); r.sc[2] = mis ? __ldg(ps + 2) : 0u;
+    r.d = __ldg(reinterpret_cast<const unsigned short*>(b + 208));
+}
 // Values d*sc*(q-32) are formed as q * hi + q * lo with (hi, lo) the fp16 split of the fp32 product d*sc,
 // so each weight is rounded to fp16 once.
-__device__ __forceinline__ void tc_dequant_q6k(uint8_t* a_tile, int rl, const uint8_t* b, int q4) {
-    const int n = q4 >> 1, kp = q4 & 1;
-    const float d = h2f_bits(__ldg(reinterpret_cast<const unsigned short*>(b + 208)));
-    const uint32_t sc4 = ldg_u32_a2(b + 192 + 8 * n + 4 * kp);
-    __half2 shi[4], slo[4];
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float ds = __fmul_rn(d, (float)(int)(int8_t)((sc4 >> (8 * i)) & 0xFF));
-        const __half h = __float2half_rn(ds);
-        shi[i] = __half2half2(h);
-        slo[i] = __half2half2(__float2half_rn(ds - __half2float(h)));
-    }
+__device__ __forceinline__ void tc_dequant_q6k(uint8_t* a_tile, int rl, const RawQ6& r, int kp, int h, uint32_t sh) {
+    const float d = h2f_bits(r.d);
+    const uint32_t s0 = __funnelshift_r(r.sc[0], r.sc[1], sh), s1 = __funnelshift_r(r.sc[1], r.sc[2], sh);
+    const uint32_t sc4 = kp ? s1 : s0;                     // scales 8n+4kp .. +3; this thread uses 2qq + h
     const __half2 k1056 = __half2half2(__ushort_as_half((unsigned short)0x6420));   // 1024 + 32
-    uint32_t H[8];
     #pragma unroll
-    for (int i = 0; i < 8; ++i) H[i] = ldg_u32_a2(b + 128 + 32 * n + 4 * i) >> (4 * kp);
-    #pragma unroll
-    for (int qq = 0; qq < 2; ++qq) {           // quarter 2kp + qq: elements 32qq .. 32qq+31 of the tile
+    for (int qq = 0; qq < 2; ++qq) {           // quarter 2kp + qq: tile columns 32qq + 16h .. +15
+        const float ds = __fmul_rn(d, (float)(int)(int8_t)((sc4 >> (8 * (2 * qq + h))) & 0xFF));
+        const __half hs = __float2half_rn(ds);
+        const __half2 shi = __half2half2(hs), slo = __half2half2(__float2half_rn(ds - __half2float(hs)));
         #pragma unroll
-        for (int c = 0; c < 4; ++c) {          // chunk of 8 elements = two ql words
+        for (int c = 0; c < 2; ++c) {          // chunk of 8 elements = two ql words
             uint32_t out[4];
             #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int wi = 2 * c + h;      // word index inside the quarter (l = 4wi .. 4wi+3)
-                const uint32_t L = (ldg_u32_a2(b + 64 * n + 32 * qq + 4 * wi) >> (4 * kp)) & 0x0F0F0F0Fu;
-                const uint32_t q6 = L | (((H[wi] >> (2 * qq)) & 0x03030303u) << 4);
+            for (int e = 0; e < 2; ++e) {
+                const int wi = 2 * c + e;
+                const uint32_t L = (__funnelshift_r(r.ql[qq][wi], r.ql[qq][wi + 1], sh) >> (4 * kp)) & 0x0F0F0F0Fu;
+                const uint32_t H = __funnelshift_r(r.qh[wi], r.qh[wi + 1], sh) >> (4 * kp + 2 * qq);
+                const uint32_t q6 = L | ((H & 0x03030303u) << 4);
                 const uint32_t a = __byte_perm(q6, 0, 0x4140) | 0x64006400u, bb = __byte_perm(q6, 0, 0x4342) | 0x64006400u;
                 const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&a), k1056);
                 const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&bb), k1056);
-                const int si = 2 * qq + (wi >> 2);                      // 16-element scale group
-                const __half2 ra = __hfma2(qa, shi[si], __hmul2(qa, slo[si]));
-                const __half2 rb = __hfma2(qb, shi[si], __hmul2(qb, slo[si]));
-                out[2 * h] = *reinterpret_cast<const uint32_t*>(&ra);
-                out[2 * h + 1] = *reinterpret_cast<const uint32_t*>(&rb);
+                const __half2 ra = __hfma2(qa, shi, __hmul2(qa, slo));
+                const __half2 rb = __hfma2(qb, shi, __hmul2(qb, slo));
+                out[2 * e] = *reinterpret_cast<const uint32_t*>(&ra);
+                out[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&rb);
             }
-            tc_store_chunk(a_tile, rl, 4 * qq + c, make_uint4(out[0], out[1], out[2], out[3]));
+            tc_store_chunk(a_tile, rl, 4 * qq + 2 * h + c, make_uint4(out[0], out[1], out[2], out[3]));
         }
     }
 }
@@ -221,7 +231,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mmq_tc_kernel(const __grid_cons
     const uint32_t b_bytes = (uint32_t)n_tile * TC_K * 2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_a[s], 128); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_a[s], TC_THREADS - 64); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(&acc_bar, 1);
         fence_mbar_init();
         fail = 0;
@@ -264,31 +274,57 @@ __global__ void __launch_bounds__(TC_THREADS, 2) mmq_tc_kernel(const __grid_cons
             tc_commit(&acc_bar);
         }
     } else {
-        const int rl = (warp & 3) * 32 + lane, row = m0 + rl;
+        // producers, later the epilogue: warp w works on TMEM lanes / tile rows 32*(w%4) .. +31; of the two warps that
+        // share a row group, h = 0/1 picks the byte half while dequantising and the column half while draining
+        const int rl = (warp & 3) * 32 + lane, row = m0 + rl, h = (warp - 2) >> 2;
         const int nb = a.K / QK_K;
-        const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * (TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES) : nullptr;
+        constexpr int BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
+        constexpr int GT = TYPE == T_Q4K ? 4 : 2;               // K tiles per fetched group
+        const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
+        const int n_groups = a.n_main / GT;
         bool ok = true;
-        for (int t = 0; t < n_tiles && !fail; ++t) {
-            const int s = t % TC_STAGES, it = t / TC_STAGES;
-            if (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT)) { ok = false; break; }
-            uint8_t* at = smem + s * TC_STAGE_BYTES;
-            if (!rowp) {
-                #pragma unroll
-                for (int c = 0; c < 8; ++c) tc_store_chunk(at, rl, c, make_uint4(0, 0, 0, 0));
-            } else if (t < a.n_main) {
-                if (TYPE == T_Q4K) tc_dequant_q4k(at, rl, rowp + (size_t)(t >> 2) * Q4K_BYTES, t & 3);
-                else               tc_dequant_q6k(at, rl, rowp + (size_t)(t >> 2) * Q6K_BYTES, t & 3);
-            } else {
-                tc_dequant_q4k_min(at, rl, rowp, nb, t - a.n_main);
+        typename std::conditional<TYPE == T_Q4K, RawQ4, RawQ6>::type cur, nxt;
+        auto fetch = [&](decltype(cur)& r, int g) {
+            if (!rowp || g >= n_groups) return;
+            if constexpr (TYPE == T_Q4K) tc_load_q4k(r, rowp + (size_t)g * Q4K_BYTES, h);
+            else                         tc_load_q6k(r, rowp + (size_t)(g >> 1) * Q6K_BYTES, g & 1, h);
+        };
+        fetch(cur, 0);
+        int t = 0;
+        for (int g = 0; g < n_groups && ok; ++g) {
+            fetch(nxt, g + 1);
+            #pragma unroll
+            for (int u = 0; u < GT; ++u, ++t) {
+                const int s = t % TC_STAGES, it = t / TC_STAGES;
+                if (fail || (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT))) { ok = false; break; }
+                uint8_t* at = smem + s * TC_STAGE_BYTES;
+                if (!rowp) {
+                    #pragma unroll
+                    for (int c = 0; c < 4; ++c) tc_store_chunk(at, rl, (c & 1) + 2 * h + 4 * (c >> 1), make_uint4(0, 0, 0, 0));
+                } else if constexpr (TYPE == T_Q4K) {
+                    tc_dequant_q4k(at, rl, cur, u, h);
+                } else {
+                    tc_dequant_q6k(at, rl, cur, u, h, (uint32_t)(((uintptr_t)(rowp + (size_t)(g >> 1) * Q6K_BYTES)) & 2) * 8);
+                }
+                fence_proxy_async();
+                mbar_arrive(&full_a[s]);
             }
+            cur = nxt;
+        }
+        for (; t < n_tiles && ok; ++t) {                        // Q4_K: the min-term tiles
+            const int s = t % TC_STAGES, it = t / TC_STAGES;
+            if (fail || (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT))) { ok = false; break; }
+            tc_dequant_q4k_min(smem + s * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
             fence_proxy_async();
             mbar_arrive(&full_a[s]);
         }
-        if (!ok) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
-        // drain the accumulator: this warp owns TMEM lanes 32*(warp%4) .. +31 = rows rl
-        if (!fail && mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT)) {
+        if (!ok && !fail) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
+        // drain the accumulator: rows rl, columns [h * n_tile/2, (h+1) * n_tile/2) in pieces of 32
+        const bool mine = ok && !fail && mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT);
+        if (__all_sync(0xFFFFFFFFu, mine)) {
             tc_fence_after();
-            for (int cb = 0; cb < n_tile; cb += 32) {
+            const int c_lo = n_tile >= 64 ? h * (n_tile >> 1) : 0, c_hi = n_tile >= 64 ? c_lo + (n_tile >> 1) : (h ? 0 : n_tile);
+            for (int cb = c_lo; cb < c_hi; cb += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cb, r);
                 if (row < a.M) {
