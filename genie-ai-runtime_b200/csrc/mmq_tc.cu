@@ -13,26 +13,30 @@
 // The only difference from the reference's arithmetic is the rounding of the two products to fp16 (2^-11
 // relative each, random), about 1e-5 of the result.
 //
-// Shape of the kernel: CTA tile 128 (rows) x 256 (tokens), K tiles of 64; 10 warps:
-//   warp 0    TMA producer of the activation tile (cp.async.bulk.tensor.2d, 128-byte swizzle)
-//   warp 1    issues tcgen05.mma (one elected lane), commits stages back to the producers
-//   warps 2-9 dequantise the weight tile (two threads per row) into the 128-byte-swizzled K-major layout, later drain the accumulator
-//             (tcgen05.ld) and store fp16 results token-major.
+// Shape of the kernel: one persistent CTA per SM; output tile 128 (rows) x 256 (tokens), K tiles of 64, four
+// operand stages, two accumulators in tensor memory; 14 warps:
+//   warp 0      TMA producer of the activation tile (cp.async.bulk.tensor.2d, 128-byte swizzle)
+//   warp 1      issues tcgen05.mma (one elected lane), commits stages back to the producers
+//   warps 2-9   dequantise the weight tile (two threads per row) into the 128-byte-swizzled K-major layout
+//   warps 10-13 drain the finished accumulator (tcgen05.ld) and store fp16 results token-major while the
+//               other accumulator is being filled.
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word, the kernel still frees
 // its tensor memory and returns.
 #include "mmq.cuh"
 #include <cuda.h>
 #include <type_traits>
+#include <cstdlib>
 
 namespace jb {
 
-constexpr int TC_M = 128, TC_N = 256, TC_K = 64, TC_STAGES = 2;
+constexpr int TC_M = 128, TC_N = 256, TC_K = 64, TC_STAGES = 4;
 constexpr int TC_A_BYTES = TC_M * TC_K * 2;       // 16 KB
 constexpr int TC_B_BYTES = TC_N * TC_K * 2;       // 32 KB
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024;    // + alignment slack
-constexpr int TC_THREADS = 320;        // TMA warp, MMA warp, 8 dequantise/drain warps
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr int TC_PRODUCERS = 256;      // two dequantising threads per weight row
+constexpr int TC_THREADS = 64 + TC_PRODUCERS + 128;   // TMA warp, MMA warp, 8 dequantising warps, 4 draining warps
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
 
 struct TcArgs {
     __half* y; const uint8_t* W; int type; int M, N, K;
@@ -44,6 +48,19 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// Bounded wait without a sleep between polls: in this kernel every wait sits on the critical path between the
+// tensor pipe and the warps that feed it, and a sleeping warp wakes up far later than the barrier flips.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tc_fail(volatile int* fail, int* status) { *fail = 1; atomicExch(status, JB_ERR_TIMEOUT); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -52,8 +69,8 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // K-major operand tile, 128-byte rows, 128-byte swizzle, 8-row atoms 1024 bytes apart
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
@@ -218,134 +235,183 @@ __global__ void mmq_tc_quantize_kernel(const __half* x, __half* xq, int N, int K
     if (gi == 0) for (int c = K + (ds4 ? G : 0) + lane; c < Kp; c += 32) row[c] = __float2half_rn(0.f);
 }
 
+// Persistent kernel: one CTA per SM walks output tiles (token tile fastest, so the CTAs running at one time
+// share a few weight row tiles and the whole activation panel in L2).  Four operand stages; two accumulators of
+// 256 tensor-memory columns each, so the drain of one tile overlaps the K loop of the next.
+//
+// The thread that issues the MMAs is the scarce resource: it must start a 128x256x16 MMA every 128 cycles, and a
+// single thread retires only a few dozen instructions in that time.  So its loop holds one barrier wait per K
+// tile (weights and activations complete the same barrier), descriptors formed by one addition, and nothing else;
+// and the other warps stay off the shared-memory pipe while they wait: one lane per role polls an mbarrier, the
+// rest of the role sleeps in a hardware named barrier.
 template <int TYPE>
-__global__ void __launch_bounds__(TC_THREADS, 2) mmq_tc_kernel(const __grid_constant__ CUtensorMap xmap, TcArgs a, int n_tile) {
+__global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_constant__ CUtensorMap xmap, TcArgs a, int n_tile) {
     extern __shared__ uint8_t tc_smem_raw[];
-    __shared__ uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_bar;
+    __shared__ uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], drain_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int fail;
+    __shared__ volatile int drain_go[2];     // verdict of the draining role's polling lane, double-buffered across tiles
     uint8_t* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * n_tile, m0 = blockIdx.y * TC_M;
+    const int tiles_n = (a.N + n_tile - 1) / n_tile, tiles_m = (a.M + TC_M - 1) / TC_M;
+    const int n_work = tiles_n * tiles_m;
     const int n_tiles = a.n_main + a.n_min;
     const uint32_t b_bytes = (uint32_t)n_tile * TC_K * 2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_a[s], TC_THREADS - 64); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(&acc_bar, 1);
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], TC_PRODUCERS / 32 + 1); mbar_init(&empty[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        mbar_init(&drain_bar, 1);
         fence_mbar_init();
         fail = 0;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    pdl_wait();
 
     if (warp == 0) {
+        // activation tiles by TMA; the quantised activations are the previous kernel's output
+        pdl_wait();
         if (lane == 0) {
-            for (int t = 0; t < n_tiles && !fail; ++t) {
-                const int s = t % TC_STAGES, it = t / TC_STAGES;
-                if (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT)) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); break; }
-                mbar_expect_tx(&full_b[s], b_bytes);
-                tma_load_2d(smem + s * TC_STAGE_BYTES + TC_A_BYTES, &xmap, t * TC_K, n0, &full_b[s]);
+            uint32_t it = 0;
+            for (int w = blockIdx.x; w < n_work && !fail; w += gridDim.x) {
+                const int n0 = (w % tiles_n) * n_tile;
+                for (int t = 0; t < n_tiles; ++t, ++it) {
+                    const int s = it % TC_STAGES;
+                    if (!tc_wait(&empty[s], ((it / TC_STAGES) & 1) ^ 1) || fail) { tc_fail(&fail, a.status); break; }
+                    mbar_expect_tx(&full[s], b_bytes);
+                    tma_load_2d(smem + s * TC_STAGE_BYTES + TC_A_BYTES, &xmap, t * TC_K, n0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n_tile
             const uint32_t idesc = (1u << 4) | ((uint32_t)(n_tile >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+            const uint64_t ad0 = tc_smem_desc(smem_u32(smem)), bd0 = tc_smem_desc(smem_u32(smem + TC_A_BYTES));
+            uint32_t it = 0, j = 0;
             bool ok = true;
-            for (int t = 0; t < n_tiles && !fail; ++t) {
-                const int s = t % TC_STAGES, it = t / TC_STAGES;
-                if (!mbar_wait_bounded(&full_a[s], it & 1, TC_WAIT_LIMIT) || !mbar_wait_bounded(&full_b[s], it & 1, TC_WAIT_LIMIT)) { ok = false; break; }
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++j) {
+                const uint32_t d_tmem = tmem + (j & 1) * 256u;
+                if (!tc_wait(&acc_empty[j & 1], ((j >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t ad = tc_smem_desc(smem_u32(smem + s * TC_STAGE_BYTES));
-                const uint64_t bd = tc_smem_desc(smem_u32(smem + s * TC_STAGE_BYTES + TC_A_BYTES));
-                #pragma unroll
-                for (int j = 0; j < TC_K / 16; ++j) tc_mma_f16(tmem, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((t | j) != 0));
-                tc_commit(&empty[s]);
+                for (int t = 0; t < n_tiles; ++t, ++it) {
+                    const uint32_t s = it % TC_STAGES;
+                    if (!tc_wait(&full[s], (it / TC_STAGES) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t ad = ad0 + (uint64_t)(s * (TC_STAGE_BYTES >> 4)), bd = bd0 + (uint64_t)(s * (TC_STAGE_BYTES >> 4));
+                    tc_mma_f16(d_tmem, ad, bd, idesc, (uint32_t)(t != 0));
+                    tc_mma_f16(d_tmem, ad + 2, bd + 2, idesc, 1u);
+                    tc_mma_f16(d_tmem, ad + 4, bd + 4, idesc, 1u);
+                    tc_mma_f16(d_tmem, ad + 6, bd + 6, idesc, 1u);
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[j & 1]);
             }
-            if (!ok) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
-            tc_commit(&acc_bar);
+            if (!ok) tc_fail(&fail, a.status);
+            // nothing of this CTA may still be running on the tensor pipe when the columns are freed
+            tc_commit(&drain_bar);
+            tc_wait(&drain_bar, 0);
         }
-    } else {
-        // producers, later the epilogue: warp w works on TMEM lanes / tile rows 32*(w%4) .. +31; of the two warps that
-        // share a row group, h = 0/1 picks the byte half while dequantising and the column half while draining
-        const int rl = (warp & 3) * 32 + lane, row = m0 + rl, h = (warp - 2) >> 2;
+    } else if (warp < 2 + TC_PRODUCERS / 32) {
+        // weight tiles: thread (rl, h) dequantises its half of row rl of every K tile
+        const int pw = warp - 2, rl = (pw & 3) * 32 + lane, h = pw >> 2;
         const int nb = a.K / QK_K;
         constexpr int BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
         constexpr int GT = TYPE == T_Q4K ? 4 : 2;               // K tiles per fetched group
-        const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
         const int n_groups = a.n_main / GT;
-        bool ok = true;
         typename std::conditional<TYPE == T_Q4K, RawQ4, RawQ6>::type cur, nxt;
-        auto fetch = [&](decltype(cur)& r, int g) {
-            if (!rowp || g >= n_groups) return;
-            if constexpr (TYPE == T_Q4K) tc_load_q4k(r, rowp + (size_t)g * Q4K_BYTES, h);
-            else                         tc_load_q6k(r, rowp + (size_t)(g >> 1) * Q6K_BYTES, g & 1, h);
+        uint32_t it = 0;
+        bool ok = true;
+        // stage s is free again: every producer thread watches the mbarrier itself (an extra hop through one polling
+        // lane and a named barrier measured slower: the wake-up latency sits on the critical path)
+        auto stage_free = [&](uint32_t it_) -> bool {
+            return tc_wait(&empty[it_ % TC_STAGES], ((it_ / TC_STAGES) & 1) ^ 1) && !fail;
         };
-        fetch(cur, 0);
-        int t = 0;
-        for (int g = 0; g < n_groups && ok; ++g) {
-            fetch(nxt, g + 1);
-            #pragma unroll
-            for (int u = 0; u < GT; ++u, ++t) {
-                const int s = t % TC_STAGES, it = t / TC_STAGES;
-                if (fail || (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT))) { ok = false; break; }
-                uint8_t* at = smem + s * TC_STAGE_BYTES;
-                if (!rowp) {
-                    #pragma unroll
-                    for (int c = 0; c < 4; ++c) tc_store_chunk(at, rl, (c & 1) + 2 * h + 4 * (c >> 1), make_uint4(0, 0, 0, 0));
-                } else if constexpr (TYPE == T_Q4K) {
-                    tc_dequant_q4k(at, rl, cur, u, h);
-                } else {
-                    tc_dequant_q6k(at, rl, cur, u, h, (uint32_t)(((uintptr_t)(rowp + (size_t)(g >> 1) * Q6K_BYTES)) & 2) * 8);
-                }
-                fence_proxy_async();
-                mbar_arrive(&full_a[s]);
-            }
-            cur = nxt;
-        }
-        for (; t < n_tiles && ok; ++t) {                        // Q4_K: the min-term tiles
-            const int s = t % TC_STAGES, it = t / TC_STAGES;
-            if (fail || (it > 0 && !mbar_wait_bounded(&empty[s], (it - 1) & 1, TC_WAIT_LIMIT))) { ok = false; break; }
-            tc_dequant_q4k_min(smem + s * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
+        auto stage_done = [&](uint32_t it_) {
             fence_proxy_async();
-            mbar_arrive(&full_a[s]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[it_ % TC_STAGES]);
+        };
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            const int row = (w / tiles_n) * TC_M + rl;
+            const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
+            auto fetch = [&](decltype(cur)& r, int g) {
+                if (!rowp || g >= n_groups) return;
+                if constexpr (TYPE == T_Q4K) tc_load_q4k(r, rowp + (size_t)g * Q4K_BYTES, h);
+                else                         tc_load_q6k(r, rowp + (size_t)(g >> 1) * Q6K_BYTES, g & 1, h);
+            };
+            fetch(cur, 0);
+            int t = 0;
+            for (int g = 0; g < n_groups && ok; ++g) {
+                fetch(nxt, g + 1);
+                #pragma unroll
+                for (int u = 0; u < GT; ++u, ++t, ++it) {
+                    if (!stage_free(it)) { ok = false; break; }
+                    uint8_t* at = smem + (it % TC_STAGES) * TC_STAGE_BYTES;
+                    if (!rowp) {
+                        #pragma unroll
+                        for (int c = 0; c < 4; ++c) tc_store_chunk(at, rl, (c & 1) + 2 * h + 4 * (c >> 1), make_uint4(0, 0, 0, 0));
+                    } else if constexpr (TYPE == T_Q4K) {
+                        tc_dequant_q4k(at, rl, cur, u, h);
+                    } else {
+                        tc_dequant_q6k(at, rl, cur, u, h, (uint32_t)(((uintptr_t)(rowp + (size_t)(g >> 1) * Q6K_BYTES)) & 2) * 8);
+                    }
+                    stage_done(it);
+                }
+                cur = nxt;
+            }
+            for (; t < n_tiles && ok; ++t, ++it) {                  // Q4_K: the min-term tiles
+                if (!stage_free(it)) { ok = false; break; }
+                tc_dequant_q4k_min(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
+                stage_done(it);
+            }
         }
-        if (!ok && !fail) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
-        // drain the accumulator: rows rl, columns [h * n_tile/2, (h+1) * n_tile/2) in pieces of 32
-        const bool mine = ok && !fail && mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT);
-        if (__all_sync(0xFFFFFFFFu, mine)) {
+        if (!ok) tc_fail(&fail, a.status);
+    } else {
+        // drain: warp e owns TMEM lanes 32*(warp%4) .. +31 = tile rows; results go out token-major as fp16.
+        // Other kernels may still read or write y until the previous kernel in the stream has finished.
+        pdl_wait();
+        const int rl = (warp & 3) * 32 + lane, dw = warp - 2 - TC_PRODUCERS / 32;
+        uint32_t j = 0;
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++j) {
+            const uint32_t acc = j & 1;
+            const int n0 = (w % tiles_n) * n_tile, row = (w / tiles_n) * TC_M + rl;
+            if (dw == 0 && lane == 0) {
+                const bool good = tc_wait(&acc_full[acc], (j >> 1) & 1) && !fail;
+                if (!good) tc_fail(&fail, a.status);
+                drain_go[j & 1] = good;
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (!drain_go[j & 1]) break;
             tc_fence_after();
-            const int c_lo = n_tile >= 64 ? h * (n_tile >> 1) : 0, c_hi = n_tile >= 64 ? c_lo + (n_tile >> 1) : (h ? 0 : n_tile);
-            for (int cb = c_lo; cb < c_hi; cb += 32) {
+            for (int cb = 0; cb < n_tile; cb += 32) {
                 uint32_t r[32];
-                tc_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)cb, r);
+                tc_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + acc * 256u + (uint32_t)cb, r);
                 if (row < a.M) {
                     #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int tok = n0 + cb + j;
-                        if (tok < a.N) a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[j]));
+                    for (int c = 0; c < 32; ++c) {
+                        const int tok = n0 + cb + c;
+                        if (tok < a.N) a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[c]));
                     }
                 }
             }
-        } else if (!fail) { fail = 1; atomicExch(a.status, JB_ERR_TIMEOUT); }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
     }
     __syncwarp();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        // a timed-out run may still have MMAs in flight: give them the same bounded wait before the columns are freed
-        if (fail && lane == 0) mbar_wait_bounded(&acc_bar, 0, TC_WAIT_LIMIT);
-        __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -389,7 +455,20 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     a.n_min = type == T_Q4K ? (K / 32 + TC_K - 1) / TC_K : 0;
     a.status = c->d_status;
     const int Kp = (a.n_main + a.n_min) * TC_K;
-    const int n_tile = N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;
+    // token-tile width: the widest tile amortises the dequantisation best, a narrower one can fill the last round of
+    // the persistent grid better; cost model = rounds x max(width/256, 0.65) (0.65: MMA issue and dequantisation floor of a K tile)
+    int n_tile = 256;
+    {
+        const int tiles_m = (M + TC_M - 1) / TC_M;
+        float best = 1e30f;
+        for (int cand = 256; cand >= 32; cand >>= 1) {
+            if (cand < 256 && cand >= 2 * N) continue;
+            const int work = tiles_m * ((N + cand - 1) / cand);
+            const int rounds = (work + c->sm_count - 1) / c->sm_count;
+            const float w = cand / 256.f, cost = rounds * (w > 0.65f ? w : 0.65f);
+            if (cost < best - 1e-6f) { best = cost; n_tile = cand; }
+        }
+    }
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)Kp, (cuuint64_t)N};
@@ -410,7 +489,8 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     const long long groups = (long long)N * (K / 32);
     JB_CUDA(launch_k(mmq_tc_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xq, N, K, Kp, (int)(type == T_Q4K)));
     count_launch();
-    const dim3 grid((N + n_tile - 1) / n_tile, (M + TC_M - 1) / TC_M);
+    const int n_work = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    const dim3 grid(n_work < c->sm_count ? n_work : c->sm_count);
     if (ti == 0) JB_CUDA(launch_k(mmq_tc_kernel<T_Q4K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     else         JB_CUDA(launch_k(mmq_tc_kernel<T_Q6K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     count_launch();
