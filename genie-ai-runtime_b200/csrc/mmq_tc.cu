@@ -6,12 +6,14 @@
 // partial sum on the CUDA cores (sum += dmA.x*dsB.x*C + dmA.y*dsB.y, mmq_q4k_llama.cu:321-322): on B200 that
 // epilogue, not the tensor pipe, would set the speed, because scales change every 32 elements.  Here the same
 // numbers are produced by ONE accumulation over the whole K range:
-//     y[t][r] = Σ_k  half(dA[r,sb(k)] * q4[r,k]) * half(d8[t,sb(k)] * q8[t,k])  +  Σ_sb half(-dmin*m)[r,sb] * half(Σx)[t,sb]
-// i.e. an fp16 x fp16 -> fp32 GEMM over K + K/32 columns whose A operand is dequantised on the fly from the GGUF
+//     y[t][r] = Σ_k  half(dA[r,sb(k)] * (q4[r,k]-8)) * half(d8[t,sb(k)] * q8[t,k])
+//             + Σ_sb half(-dmin*m)[r,sb] * half(Σx)[t,sb]  +  Σ_sb (8*dA[r,sb]) * half(d8*Σq8)[t,sb]
+// i.e. an fp16 x fp16 -> fp32 GEMM over K + 2K/32 columns whose A operand is dequantised on the fly from the GGUF
 // blocks with the reference's own half-precision scale products (mmq_q4k_llama.cu:159-163) and whose B operand is
 // the reference's quantised activation (codes x scale, and the per-group sums of the DS4 layout, :383-404).
-// The only difference from the reference's arithmetic is the rounding of the two products to fp16 (2^-11
-// relative each, random), about 1e-5 of the result.
+// The only difference from the reference's arithmetic is the rounding of the two operand products to fp16
+// (2^-11 relative each, independent from term to term); the codes are centred (q4-8) so that this rounding acts on
+// zero-mean values and does not grow with the cancellation between the scale and the min terms.
 //
 // Shape of the kernel: one persistent CTA per SM; output tile 128 (rows) x 256 (tokens), K tiles of 64, four
 // operand stages, two accumulators in tensor memory; 14 warps:
@@ -40,7 +42,7 @@ constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
 
 struct TcArgs {
     __half* y; const uint8_t* W; int type; int M, N, K;
-    int n_main, n_min;        // K tiles of weights, K tiles of the min term
+    int n_main, n_min;        // K tiles of weights, K tiles of the min and centring terms (Q4_K)
     int* status;
 };
 
@@ -91,9 +93,11 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_store_chunk(uint8_t* a_tile, int rl, int c, uint4 v) {
     *reinterpret_cast<uint4*>(a_tile + rl * 128 + ((c ^ (rl & 7)) << 4)) = v;
 }
-// four nibbles (already masked to 0x0F0F0F0F) -> four halves scaled by dA, as two half2 words
+// four nibbles (already masked to 0x0F0F0F0F) -> four halves (q - 8) * dA, as two half2 words.  The codes are
+// centred so that the fp16 rounding of the products acts on values of half the magnitude and zero mean; the
+// constant 8 * dA comes back through an extra K column per sub-block (see tc_dequant_q4k_extra).
 __device__ __forceinline__ void tc_nib4(uint32_t n4, __half2 dA, uint32_t& lo, uint32_t& hi) {
-    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6408));    // 1024 + 8
     const uint32_t a = __byte_perm(n4, 0, 0x4140) | 0x64006400u, b = __byte_perm(n4, 0, 0x4342) | 0x64006400u;
     const __half2 ha = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&a), k1024), dA);
     const __half2 hb = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&b), k1024), dA);
@@ -133,20 +137,26 @@ __device__ __forceinline__ void tc_dequant_q4k(uint8_t* a_tile, int rl, const Ra
     }
 }
 
-// Q4_K min term: column j of tile `tm` is sub-block 64*tm + j; value half(-dmin) * half(m); thread h writes chunks 4h..4h+3
-__device__ __forceinline__ void tc_dequant_q4k_min(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm, int h) {
+// Q4_K extra K tiles: 8 columns per chunk = the 8 sub-blocks of one block.  Chunks [0, nb) hold the min term
+// half(-dmin) * half(m) (multiplied by the per-group sums of x, as in the reference); chunks [nb, 2nb) hold
+// 8 * half(d * sc), which multiplied by the per-group sums of the quantised activations restores the centring of
+// the codes.  Thread h writes chunks 4h..4h+3 of tile `tm`.
+__device__ __forceinline__ void tc_dequant_q4k_extra(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm, int h) {
     #pragma unroll 1
     for (int c = 4 * h; c < 4 * h + 4; ++c) {
-        const int blk = 8 * tm + c;
+        const int bi = 8 * tm + c;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row_blocks && blk < nb) {
-            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(row_blocks + (size_t)blk * Q4K_BYTES));
+        if (row_blocks && bi < 2 * nb) {
+            const bool centre = bi >= nb;
+            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(row_blocks + (size_t)(centre ? bi - nb : bi) * Q4K_BYTES));
+            const __half dh = __ushort_as_half((unsigned short)(hd.x & 0xFFFFu));
             const __half mh = __hneg(__ushort_as_half((unsigned short)(hd.x >> 16)));
+            const __half eight = __ushort_as_half((unsigned short)0x4800);
             unsigned short o[8];
             #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 int sc, mn; scale_min_k4(j, hd.y, hd.z, hd.w, sc, mn);
-                o[j] = __half_as_ushort(__hmul(mh, __int2half_rn(mn)));
+                o[j] = __half_as_ushort(centre ? __hmul(eight, __hmul(dh, __int2half_rn(sc))) : __hmul(mh, __int2half_rn(mn)));
             }
             v = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
         }
@@ -213,7 +223,8 @@ __device__ __forceinline__ void tc_dequant_q6k(uint8_t* a_tile, int rl, const Ra
 }
 
 // activation operand: X'[t][0..K) = half(d*q) (codes x scale of the reference's quantiser, mmq_q4k_llama.cu:383-404,
-// mmq_q6k_llama.cu:424-438), X'[t][K + g] = half(sum of group g) for Q4_K, zero up to the padded width Kp.
+// mmq_q6k_llama.cu:424-438); for Q4_K also X'[t][K + g] = half(sum of x over group g) (the reference's DS4 sum)
+// and X'[t][K + K/32 + g] = half(d * sum of codes of group g); zero up to the padded width Kp.
 __global__ void mmq_tc_quantize_kernel(const __half* x, __half* xq, int N, int K, int Kp, int ds4) {
     pdl_wait();
     const long long g = (long long)blockIdx.x * blockDim.y + threadIdx.y;
@@ -228,11 +239,17 @@ __global__ void mmq_tc_quantize_kernel(const __half* x, __half* xq, int N, int K
     float d = __fdiv_rn(amax, 127.0f);
     const float dinv = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
     const int q = __float2int_rn(__fmul_rn(v, dinv));
+    int qsum = q;
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, o);
     if (ds4) d = __half2float(__float2half_rn(d));
     __half* row = xq + t * Kp;
     row[gi * 32 + lane] = __float2half_rn(__fmul_rn(d, (float)q));
-    if (lane == 0 && K + gi < Kp) row[K + gi] = ds4 ? __float2half_rn(sum) : __float2half_rn(0.f);
-    if (gi == 0) for (int c = K + (ds4 ? G : 0) + lane; c < Kp; c += 32) row[c] = __float2half_rn(0.f);
+    if (ds4 && lane == 0) {
+        row[K + gi] = __float2half_rn(sum);
+        row[K + G + gi] = __float2half_rn(__fmul_rn(d, (float)qsum));
+    }
+    if (gi == 0) for (int c = K + (ds4 ? 2 * G : 0) + lane; c < Kp; c += 32) row[c] = __float2half_rn(0.f);
 }
 
 // Persistent kernel: one CTA per SM walks output tiles (token tile fastest, so the CTAs running at one time
@@ -366,9 +383,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                 }
                 cur = nxt;
             }
-            for (; t < n_tiles && ok; ++t, ++it) {                  // Q4_K: the min-term tiles
+            for (; t < n_tiles && ok; ++t, ++it) {                  // Q4_K: the min-term and centring tiles
                 if (!stage_free(it)) { ok = false; break; }
-                tc_dequant_q4k_min(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
+                tc_dequant_q4k_extra(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
                 stage_done(it);
             }
         }
@@ -435,7 +452,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 size_t mmq_tc_scratch_bytes(int type, int N, int K) {
-    const int n_min = type == T_Q4K ? (K / 32 + TC_K - 1) / TC_K : 0;
+    const int n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     return (size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half) + 256;
 }
 
@@ -452,7 +469,7 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     TcArgs a;
     a.y = y; a.W = (const uint8_t*)W; a.type = type; a.M = M; a.N = N; a.K = K;
     a.n_main = K / TC_K;
-    a.n_min = type == T_Q4K ? (K / 32 + TC_K - 1) / TC_K : 0;
+    a.n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     a.status = c->d_status;
     const int Kp = (a.n_main + a.n_min) * TC_K;
     // token-tile width: the widest tile amortises the dequantisation best, a narrower one can fill the last round of

@@ -22,3 +22,21 @@ def close(got, want, rel=1e-3, floor=None):
         floor = 2e-3 * float(np.sqrt(np.mean(want ** 2)) + 1e-30)
     bad = np.abs(got - want) > rel * np.abs(want) + floor
     return not bad.any(), float(np.abs(got - want).max())
+
+
+def close_gemm(got, want, N, M, rel=1e-3, floor=3e-3, rms_bound=6e-4):
+    """Bound for a batched product y[t][r] whose error scales with the magnitudes of token t and row r:
+    |got-want| <= rel*|want| + floor*s[t][r] with s[t][r] = RMS(want[t,:]) * RMS(want[:,r]) / RMS(want), and the
+    RMS of the whole error at most rms_bound of the RMS of `want`.  The tensor-core prefill path rounds each
+    operand product to fp16 (2^-11 relative): measured error RMS 3.7e-4 of the output scale, so `floor` is an
+    8-sigma bound for the millions of outputs a test holds and `rms_bound` the accuracy statement proper."""
+    g = np.asarray(got, np.float64).reshape(N, M)
+    w = np.asarray(want, np.float64).reshape(N, M)
+    rt = np.sqrt(np.mean(w ** 2, axis=1, keepdims=True)) + 1e-30
+    rr = np.sqrt(np.mean(w ** 2, axis=0, keepdims=True)) + 1e-30
+    ra = float(np.sqrt(np.mean(w ** 2)) + 1e-30)
+    s = rt * rr / ra
+    err = np.abs(g - w)
+    bad = err > rel * np.abs(w) + floor * s
+    e_rms = float(np.sqrt(np.mean((g - w) ** 2))) / ra
+    return (not bad.any()) and e_rms <= rms_bound, "max |d| %.4g, error rms %.3g of output rms, %d outside" % (float(err.max()), e_rms, int(bad.sum()))

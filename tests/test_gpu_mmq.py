@@ -6,13 +6,16 @@ import numpy as np
 import pytest
 
 from oracle import oracle as orc
-from gpu_util import pkg, dev, close
+from gpu_util import pkg, dev, close, close_gemm
 
 pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("t,M,N,K", [(12, 128, 16, 512), (12, 130, 7, 1024), (12, 64, 65, 2560), (14, 128, 16, 512), (14, 33, 9, 2560),
-                                      (14, 20, 3, 9728), (13, 16, 3, 512)])
+                                      (14, 20, 3, 9728), (13, 16, 3, 512),
+                                      # several output tiles per persistent CTA, ragged last row / token tile, every token-tile width
+                                      (12, 300, 300, 2560), (14, 260, 270, 1024), (12, 1, 2, 256), (14, 129, 33, 256), (12, 257, 129, 768),
+                                      (12, 40000, 40, 256), (14, 19000, 70, 512)])
 def test_gemm_quant_batched_matches_oracle(t, M, N, K):
     import torch
     jb = pkg()
@@ -22,7 +25,7 @@ def test_gemm_quant_batched_matches_oracle(t, M, N, K):
     y = torch.zeros(N * M, dtype=torch.float16, device="cuda")
     jb.gemm_quant_batched(y, dev(W), t, dev(X), M, N, K)
     want = orc.entry_gemm_quant_batched(W, t, X, M, N, K).astype(np.float32).reshape(-1)
-    ok, md = close(y.float().cpu().numpy(), want)
+    ok, md = close_gemm(y.float().cpu().numpy(), want, N, M)
     assert ok, md
 
 
@@ -52,6 +55,25 @@ def test_reference_golden_vectors(golden_dir, name, t):
     jb.gemm_quant_batched(y, dev(g["W"]), t, dev(g["X"].view(np.float16)), M, N, K)
     ref = g["Y_int8"].view(np.float16).astype(np.float32)
     assert np.max(np.abs(y.float().cpu().numpy() - ref)) <= 0.5
+
+
+@pytest.mark.parametrize("t", [12, 14])
+def test_tensor_core_and_cuda_core_paths_agree(t):
+    """The tcgen05 kernel and the CUDA-core kernel (the one that exports the integer accumulators) compute the same
+    quantised product; they differ by the fp16 rounding of the operand products only."""
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1006 + t))
+    M, N, K = 200, 48, 1536
+    W = dev(orc.gen_weight(rng, t, M, K)); X = dev(orc.gen_act(rng, N * K))
+    G = K // 32 if t == 12 else K // 16
+    dots = torch.zeros((N, M, G), dtype=torch.int32, device="cuda")
+    a = torch.zeros(N * M, dtype=torch.float16, device="cuda"); b = torch.zeros_like(a)
+    jb.gemm_quant_batched(a, W, t, X, M, N, K)
+    jb.gemm_quant_batched_int_dots(b, dots, W, t, X, M, N, K)
+    ok, md = close_gemm(a.float().cpu().numpy(), b.float().cpu().numpy(), N, M)
+    assert ok, md
+    assert jb.device_status() == 0
 
 
 def test_n_equal_one_routes_to_gemv():
