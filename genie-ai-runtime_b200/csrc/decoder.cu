@@ -9,6 +9,7 @@
 #include "gemv.cuh"
 #include "elementwise.cuh"
 #include "attention.cuh"
+#include "tp.cuh"
 #include <cfloat>
 #include <new>
 #include <vector>
@@ -74,10 +75,17 @@ struct jllm_b200_decoder {
     cudaStream_t own_stream = nullptr;   // used when the caller passes the legacy default stream, which cannot be captured
     int kernels_per_step = 0;
     void* slab = nullptr;
+    // tensor-parallel session: m keeps the full dimensions, the weights are this rank's row slices
+    bool tp_on = false;
+    TpDev tp;
+    int tp_off[6] = {0, 0, 0, 0, 0, 0};
+    int nh_l = 0, nkv_l = 0, I_l = 0, H_l = 0, V_l = 0;
+    uint32_t* seq = nullptr;
 };
 
 static int dec_alloc(jllm_b200_decoder* d) {
     const jllm_b200_model_desc& m = d->m;
+    // (a tensor-parallel rank could do with slice-sized buffers; the full sizes are a few hundred KB)
     const size_t H = m.hidden_dim, QD = (size_t)m.n_heads * m.head_dim, KVD = (size_t)m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
     auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
     const size_t total = 3 * al(H * 2) + 2 * al(QD * 2) + 2 * al(KVD * 2) + 3 * al(I * 2) + al((size_t)m.vocab_size * 4) + al(64) +
@@ -101,7 +109,9 @@ static int dec_alloc(jllm_b200_decoder* d) {
 
 // Enqueues one decode step that reads position and token from d->state.  n_splits is fixed per
 // enqueue (a captured graph keeps the value it was captured with).
+static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t st);
 static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
+    if (d->tp_on) return dec_enqueue_step_tp(d, n_splits, st);
     const jllm_b200_model_desc& m = d->m;
     const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, KVD = m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
     const int* d_pos = d->state; const int* d_tok = d->state + 1;
@@ -154,6 +164,47 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
     return JB_OK;
 }
 
+
+// One decode step of a tensor-parallel rank: the single-GPU sequence on this rank's rows and heads, with the four
+// gathers of a layer in between.  Full vectors live in this rank's exchange region.
+static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
+    const jllm_b200_model_desc& m = d->m;
+    const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, I = m.intermediate_dim, hd = m.head_dim;
+    const int QD_l = d->nh_l * hd, KVD_l = d->nkv_l * hd, rank = d->tp.rank;
+    unsigned char* mine = d->tp.peer[rank];
+    __half* att_full = (__half*)(mine + d->tp_off[0]); __half* x2_full = (__half*)(mine + d->tp_off[1]);
+    __half* sw_full = (__half*)(mine + d->tp_off[2]);  __half* x_full = (__half*)(mine + d->tp_off[3]);
+    const int* d_pos = d->state; const int* d_tok = d->state + 1;
+    const float scale = 1.0f / sqrtf((float)hd);
+    const long long l0 = jllm_b200_launch_count();
+    DCHK(launch_embed_row(x_full, m.tok_embd, m.embd_type, 0, d_tok, H, st));
+    for (int l = 0; l < m.n_layers; ++l) {
+        const jllm_b200_layer_desc& w = d->layers[l];
+        int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
+        float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
+        DCHK(jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD_l, d->k, w.wk, w.type_wk, KVD_l, d->v, w.wv, w.type_wv, KVD_l,
+                                              x_full, w.rms_attn, 1, m.rms_eps, H, st));
+        DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, d->nh_l, d->nkv_l, hd,
+                             0, d_pos, m.rope_theta, m.rope_neox != 0, true, st));
+        AttnCall c;
+        c.out = d->att; c.q = d->q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = d->nh_l; c.n_kv = d->nkv_l;
+        c.hd = hd; c.chd = hd; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
+        DCHK(launch_attention(c, st));
+        DCHK(launch_tp_allgather(d->tp, d->att, QD_l * 2, d->tp_off[0], TP_POINT_ATT, l, st));
+        DCHK(jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st));
+        DCHK(launch_tp_allgather(d->tp, d->x2, d->H_l * 2, d->tp_off[1], TP_POINT_X2, l, st));
+        DCHK(jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st));
+        DCHK(launch_tp_allgather(d->tp, d->sw, d->I_l * 2, d->tp_off[2], TP_POINT_SW, l, st));
+        DCHK(jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st));
+        DCHK(launch_tp_allgather(d->tp, d->x, d->H_l * 2, d->tp_off[3], TP_POINT_X, l, st));
+    }
+    DCHK(launch_rmsnorm(d->normed, x_full, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
+    DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, d->V_l, H, st));
+    DCHK(launch_tp_argmax(d->tp, d->logits, d->V_l, d->state, d->out_tokens, d->out_cap, st));
+    d->kernels_per_step = (int)(jllm_b200_launch_count() - l0);
+    return JB_OK;
+}
+
 static int splits_for_ctx(const jllm_b200_decoder* d, int upto_pos) { return attn_splits_for(upto_pos + 1); }
 
 // graph of one step; re-captured when the split count of the attention changes
@@ -194,11 +245,47 @@ jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, i
     splitk_buffer((size_t)model->n_heads * 64 * (model->head_dim + 2), true);
     return d;
 }
+
+jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model, int flags, int rank, int world, void* const* regions) {
+    if (!model || !model->layers || model->n_layers <= 0 || !regions) { set_error(JB_ERR_ARG, "decoder: empty model description"); return nullptr; }
+    if (world < 2 || world > TP_MAX_WORLD || rank < 0 || rank >= world) { set_error(JB_ERR_ARG, "decoder: rank %d of %d", rank, world); return nullptr; }
+    const int hd = model->head_dim;
+    if (model->n_heads % world || model->n_kv_heads % world || model->intermediate_dim % world || model->hidden_dim % world || model->vocab_size % world ||
+        ((model->n_heads / world) * hd * 2) % 16 || ((model->hidden_dim / world) * 2) % 16 || ((model->intermediate_dim / world) * 2) % 16) {
+        set_error(JB_ERR_ARG, "decoder: heads, hidden, intermediate and vocabulary sizes must split evenly over %d ranks in 16-byte slices", world); return nullptr;
+    }
+    if (model->hidden_dim % QK_K || model->intermediate_dim % QK_K || (model->n_heads * hd) % QK_K) {
+        set_error(JB_ERR_ARG, "decoder: hidden/intermediate/q dims must be multiples of 256"); return nullptr;
+    }
+    if (!ctx()) return nullptr;
+    jllm_b200_decoder* d = new (std::nothrow) jllm_b200_decoder();
+    if (!d) return nullptr;
+    d->m = *model;
+    d->layers.assign(model->layers, model->layers + model->n_layers);
+    d->m.layers = d->layers.data();
+    d->fused = true; d->use_graph = (flags & 2) != 0;
+    d->tp_on = true;
+    d->nh_l = model->n_heads / world; d->nkv_l = model->n_kv_heads / world; d->I_l = model->intermediate_dim / world;
+    d->H_l = model->hidden_dim / world; d->V_l = model->vocab_size / world;
+    tp_region_layout(model->hidden_dim, model->n_heads * hd, model->intermediate_dim, d->tp_off);
+    for (int r = 0; r < TP_MAX_WORLD; ++r) d->tp.peer[r] = r < world ? (unsigned char*)regions[r] : nullptr;
+    d->tp.rank = rank; d->tp.world = world; d->tp.flags_off = d->tp_off[4]; d->tp.argmax_off = d->tp_off[5];
+    d->tp.epochs_per_step = model->n_layers; d->tp.status = ctx()->d_status;
+    if (cudaMalloc(&d->seq, 256) != cudaSuccess) { cudaGetLastError(); set_error(JB_ERR_NOMEM, "decoder: step counter"); delete d; return nullptr; }
+    cudaMemset(d->seq, 0, 256);
+    d->tp.seq = d->seq;
+    jllm::KVCachePool::Config c = { model->n_layers, d->nkv_l, hd, model->max_context, 0, 1 };
+    if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); cudaFree(d->seq); delete d; return nullptr; }
+    if (dec_alloc(d)) { d->kv.destroy(); cudaFree(d->seq); delete d; return nullptr; }
+    splitk_buffer((size_t)d->nh_l * 64 * (hd + 2), true);
+    return d;
+}
 void jllm_b200_decoder_destroy(jllm_b200_decoder* d) {
     if (!d) return;
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->own_stream) cudaStreamDestroy(d->own_stream);
     if (d->slab) cudaFree(d->slab);
+    if (d->seq) cudaFree(d->seq);
     d->kv.destroy();
     delete d;
 }

@@ -231,6 +231,24 @@ int    jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d);
  * 7 layer-0 K cache, 8 layer-0 K scales. */
 const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);
 
+/* ── tensor-parallel decoder session (extension; the reference is single-GPU) ───────────────────────────
+ * One process per GPU.  Rank r of `world` (2, 4 or 8) owns rows [r*M/world, (r+1)*M/world) of every weight matrix
+ * (a contiguous byte range of the GGUF image) and the KV heads that go with its query heads.  `model` carries the
+ * FULL dimensions, the weight pointers are the rank's slices (tok_embd and the norm vectors are whole).  After each
+ * sharded product the slices are gathered through the exchange regions: regions[i] is rank i's region as mapped
+ * into this process (jllm_b200_tp_alloc on the owner, jllm_b200_tp_export / _open across processes), all of
+ * jllm_b200_tp_region_bytes() bytes.  All ranks must run the same steps in the same order; the greedy token is
+ * reduced across ranks on the device, so every rank returns the same token.  jllm_b200_decoder_logits() gives the
+ * rank's vocab_size/world slice.  Waits between ranks are bounded: a rank that never arrives shows up as
+ * JLLM_B200_ERR_TIMEOUT in jllm_b200_device_status(). */
+jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model, int flags, int rank, int world, void* const* regions);
+size_t jllm_b200_tp_region_bytes(int hidden_dim, int q_dim, int intermediate_dim);
+void*  jllm_b200_tp_alloc(size_t bytes);                    /* zeroed device memory for an exchange region */
+int    jllm_b200_tp_free(void* region);
+int    jllm_b200_tp_export(void* region, void* handle64);   /* 64-byte CUDA IPC handle */
+void*  jllm_b200_tp_open(const void* handle64);             /* maps a peer's region, enabling peer access */
+int    jllm_b200_tp_close(void* mapped);
+
 /* ── allocation-free decode attention (no counterpart in the reference) ─────────────────────────
  * For hosts that cannot let the library allocate device memory: an engine whose own pools already hold
  * all of the GPU's free memory, a request loop that must avoid driver calls which can stall the device,

@@ -1,0 +1,106 @@
+"""Tensor-parallel decode.
+
+CPU (gloo, world_size 2): the sharding plan and the gather points reproduce the single-rank oracle bit for bit.
+GPU (needs 2 devices): the library's push-style exchange gives the single-GPU token stream on every rank."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import tp_worker  # noqa: E402
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
+    return p
+
+
+def _run_ranks(mode, world, tmp_path, timeout):
+    port = _free_port()
+    outs = [str(tmp_path / f"{mode}_r{r}.npz") for r in range(world)]
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), mode, str(r), str(world), str(port), outs[r]],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(world)]
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill(); o, _ = p.communicate()
+        logs.append(o.decode(errors="replace")[-3000:])
+    assert all(p.returncode == 0 for p in procs), "\n---\n".join(logs)
+    return [np.load(o) for o in outs]
+
+
+def _single_rank_reference():
+    model = orc.gen_model(tp_worker.SEED, **tp_worker.SMALL)
+    d = orc.Decoder(model, 64)
+    toks = d.generate(tp_worker.PROMPT, tp_worker.N_NEW)
+    return model, np.array(toks, np.int32), d.logits.copy()
+
+
+def test_row_ranges_cover_every_matrix_once():
+    from __graft_entry__ import load_package
+    import importlib
+    tp = importlib.import_module(load_package().__name__ + ".tp")
+    cfg = dict(n_layers=36, hidden=2560, n_heads=32, n_kv_heads=8, head_dim=128, ffn=9728, vocab=151936)
+    for world in (2, 4, 8):
+        seen = {}
+        for r in range(world):
+            for k, (a, b) in tp.row_ranges(cfg, world, r).items():
+                seen.setdefault(k, []).append((a, b))
+        for k, spans in seen.items():
+            assert spans[0][0] == 0 and all(spans[i][1] == spans[i + 1][0] for i in range(world - 1)), (k, spans)
+        assert seen["wq"][-1][1] == 4096 and seen["wk"][-1][1] == 1024 and seen["output"][-1][1] == 151936
+        # a rank's query heads attend to its own KV heads only
+        for r in range(world):
+            q0, q1 = seen["wq"][r]; k0, k1 = seen["wk"][r]
+            assert q0 // 128 // 4 == k0 // 128 and (q1 // 128 - 1) // 4 == k1 // 128 - 1
+    with pytest.raises(ValueError):
+        tp.row_ranges(dict(cfg, n_kv_heads=6), 4, 0)
+
+
+def test_slices_are_views_of_contiguous_byte_ranges():
+    from __graft_entry__ import load_package
+    import importlib
+    tp = importlib.import_module(load_package().__name__ + ".tp")
+    rng = np.random.Generator(np.random.PCG64(5))
+    W = orc.gen_weight(rng, 14, 12, 512)
+    s = tp.slice_rows(W, 14, 512, 3, 9)
+    assert s.base is not None and s.size == 6 * 2 * 210 and np.array_equal(s, W.reshape(-1)[3 * 420:9 * 420])
+
+
+def test_gloo_two_ranks_match_single_rank_oracle(tmp_path):
+    model, want_tokens, want_logits = _single_rank_reference()
+    res = _run_ranks("cpu", 2, tmp_path, 600)
+    V_l = tp_worker.SMALL["vocab"] // 2
+    for r, z in enumerate(res):
+        assert np.array_equal(z["tokens"], want_tokens), (r, z["tokens"], want_tokens)
+        assert np.array_equal(z["logits"], want_logits[r * V_l:(r + 1) * V_l])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_gpu_ranks_match_single_gpu(tmp_path, world):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from gpu_util import pkg
+    import importlib
+    jb = pkg()
+    decmod = importlib.import_module(jb.__name__ + ".decoder")
+    model = orc.gen_model(tp_worker.SEED, **tp_worker.SMALL)
+    d = decmod.Decoder(model["cfg"], decmod.upload(model), 64)
+    want = d.generate(tp_worker.PROMPT, tp_worker.N_NEW, torch.cuda.Stream())
+    d.close()
+    res = _run_ranks("gpu", world, tmp_path, 600)
+    for r, z in enumerate(res):
+        assert int(z["status"]) == 0
+        assert np.array_equal(z["tokens"], want), (r, z["tokens"], want)
+        assert np.array_equal(z["tokens2"], want)
