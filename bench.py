@@ -16,8 +16,10 @@ call, which copies {position, token} host->device and the sampled token device->
 over the 36 layers' distinct weights with CUDA events on its own stream.  `cpu_baseline` runs the CPU oracle
 (oracle/, the reference's golden arithmetic restated in C with OpenMP) on a bounded sample of the same steps.
 
-N > 1 (torchrun): every rank runs an independent replica of the same request on its own GPU (weak scaling,
-no data-path collective); times are reduced with MAX over ranks.
+N > 1 (torchrun): the same single request is decoded tensor-parallel — weight rows and KV heads sharded over the N
+GPUs, slices gathered after each sharded product by the library's own NVLink push kernels — so `value` is the
+tok/s of that one stream (strong scaling).  --parallelism replicas runs N independent copies of the 1-GPU
+engine instead (weak scaling, no data-path collective).  Times are reduced with MAX over ranks.
 
 --impl reference: times the CPU oracle port of the reference's arithmetic on the host cores (the reference has
 no CPU implementation of INT8-KV attention, src/kernels/attention.cu:1078-1082, and its CPU GEMV golden is
@@ -64,22 +66,29 @@ def gen_blocks_gpu(gen, ggml_type, rows, K, dev):
     return img.reshape(rows, -1).contiguous()
 
 
-def gen_model_gpu(dev, cfg=CFG, seed=SEED):
+def gen_model_gpu(dev, cfg=CFG, seed=SEED, shard=None):
+    """Whole model, or with shard=(rank, world) the row slices of one tensor-parallel rank: sharded matrices hold
+    rows/world rows drawn from a per-rank generator, replicated tensors (embedding, norms) come from the shared one."""
     import torch
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
+    gl, div = g, 1
+    if shard is not None:
+        gl = torch.Generator(device=dev)
+        gl.manual_seed(seed * 1000 + shard[0])
+        div = shard[1]
     H, QD, KVD, I, V = cfg["hidden"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["ffn"], cfg["vocab"]
     nrm = lambda n: (1.0 + 0.02 * torch.randn(n, device=dev, generator=g)).float()
     w = dict(layers=[])
     for _ in range(cfg["n_layers"]):
         w["layers"].append(dict(
-            wq=(gen_blocks_gpu(g, Q4_K, QD, H, dev), Q4_K), wk=(gen_blocks_gpu(g, Q4_K, KVD, H, dev), Q4_K),
-            wv=(gen_blocks_gpu(g, Q6_K, KVD, H, dev), Q6_K), wo=(gen_blocks_gpu(g, Q4_K, H, QD, dev), Q4_K),
-            gate=(gen_blocks_gpu(g, Q4_K, I, H, dev), Q4_K), up=(gen_blocks_gpu(g, Q4_K, I, H, dev), Q4_K),
-            down=(gen_blocks_gpu(g, Q6_K, H, I, dev), Q6_K),
+            wq=(gen_blocks_gpu(gl, Q4_K, QD // div, H, dev), Q4_K), wk=(gen_blocks_gpu(gl, Q4_K, KVD // div, H, dev), Q4_K),
+            wv=(gen_blocks_gpu(gl, Q6_K, KVD // div, H, dev), Q6_K), wo=(gen_blocks_gpu(gl, Q4_K, H // div, QD, dev), Q4_K),
+            gate=(gen_blocks_gpu(gl, Q4_K, I // div, H, dev), Q4_K), up=(gen_blocks_gpu(gl, Q4_K, I // div, H, dev), Q4_K),
+            down=(gen_blocks_gpu(gl, Q6_K, H // div, I, dev), Q6_K),
             rms_attn=nrm(H), rms_ffn=nrm(H), q_norm=nrm(cfg["head_dim"]), k_norm=nrm(cfg["head_dim"])))
     w["tok_embd"] = (gen_blocks_gpu(g, Q4_K, V, H, dev), Q4_K)
-    w["output"] = (gen_blocks_gpu(g, Q6_K, V, H, dev), Q6_K)
+    w["output"] = (gen_blocks_gpu(gl, Q6_K, V // div, H, dev), Q6_K)
     w["out_norm"] = nrm(H)
     return w
 
@@ -172,6 +181,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
+                    help="N > 1: one request decoded tensor-parallel over the N GPUs (default), or N independent replicas")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -180,7 +191,10 @@ def main():
     K = a.steps
     config = {"workload": "qwen3-4b-shape decoder, Q4_K_M mix (Q6_K attn_v/ffn_down/output), INT8 KV, greedy decode after a "
                           f"{N_PROMPT}-token random-id prompt, batch 1",
-              "n_prompt": N_PROMPT, "parallelism": "replicas" if world > 1 else "single",
+              "n_prompt": N_PROMPT,
+              "parallelism": "single" if int(os.environ.get("WORLD_SIZE", "1")) == 1 else
+                             (f"tp{os.environ.get('WORLD_SIZE')} (weight rows and KV heads sharded, push gathers over NVLink)" if a.parallelism == "tp"
+                              else f"{os.environ.get('WORLD_SIZE')} independent replicas"),
               "l2": "2.6 GB of weights are streamed per step (>> 126 MB L2); no explicit flush"}
 
     import torch
@@ -215,9 +229,17 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    weights = gen_model_gpu(dev)
+    tp_mode = world > 1 and a.parallelism == "tp"
     prompt = np.random.Generator(np.random.PCG64(SEED)).integers(0, CFG["vocab"], N_PROMPT).astype(np.int32)
-    dec = jb.decoder.Decoder(CFG, weights, MAX_CTX, jb.decoder.FUSED | jb.decoder.GRAPH)
+    if tp_mode:
+        import importlib
+        tpm = importlib.import_module(jb.__name__ + ".tp")
+        weights = gen_model_gpu(dev, shard=(rank, world))
+        dec = tpm.TPDecoder(CFG, weights, MAX_CTX, rank, world)
+    else:
+        weights = gen_model_gpu(dev)
+        dec = jb.decoder.Decoder(CFG, weights, MAX_CTX, jb.decoder.FUSED | jb.decoder.GRAPH)
+    streams = 1 if (tp_mode or world == 1) else world        # requests decoded at the same time
     stream = torch.cuda.Stream(device=dev)
 
     def barrier():
@@ -283,7 +305,7 @@ def main():
     status = jb.device_status(stream)
 
     # ── roofline of the dominant kernel: fused norm + gate/up GEMV + SwiGLU over the 36 layers' weights ──
-    H, I = CFG["hidden"], CFG["ffn"]
+    H, I = CFG["hidden"], CFG["ffn"] // (world if tp_mode else 1)
     x = (torch.randn(H, device=dev) * 1.0).to(torch.float16)
     sw = torch.zeros(I, dtype=torch.float16, device=dev)
     reps = 5
@@ -312,10 +334,10 @@ def main():
     if rank == 0:
         wbytes = weight_bytes_per_token()
         line = {
-            "metric": "decode_tok_s", "value": world * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": "decode_tok_s", "value": streams * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if tp_mode else "weak", "vs_baseline": None,
             "dtype": "int8xq4/q6 dots, fp32 accumulate, fp16 activations", "data": "synthetic", "config": config,
-            "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+            "e2e": {"value": streams * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "kernels_per_step": dec.kernels_per_step(),
             "clocks": clk.summary(),
@@ -323,7 +345,7 @@ def main():
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "peak_source": peak_src},
             "step_hbm": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (dev_ms / K * 1e-3) / 1e9,
-                         "frac_of_peak": wbytes / (dev_ms / K * 1e-3) / 1e9 / peak},
+                         "frac_of_peak": wbytes / (dev_ms / K * 1e-3) / 1e9 / (peak * (world if tp_mode else 1))},
             "device_status": status,
         }
         # CPU baseline on a bounded sample (rank 0, N = 1 only)

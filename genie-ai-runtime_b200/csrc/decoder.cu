@@ -76,7 +76,7 @@ struct jllm_b200_decoder {
     int kernels_per_step = 0;
     void* slab = nullptr;
     // tensor-parallel session: m keeps the full dimensions, the weights are this rank's row slices
-    bool tp_on = false;
+    bool tp_on = false, tp_fused = true;
     TpDev tp;
     int tp_off[6] = {0, 0, 0, 0, 0, 0};
     int nh_l = 0, nkv_l = 0, I_l = 0, H_l = 0, V_l = 0;
@@ -166,38 +166,72 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
 
 
 // One decode step of a tensor-parallel rank: the single-GPU sequence on this rank's rows and heads, with the four
-// gathers of a layer in between.  Full vectors live in this rank's exchange region.
+// gathers of a layer in between.  Full vectors live in this rank's exchange region.  tp_fused: the Wo, gate/up and
+// W_down kernels store their rows straight into every rank's region and raise the flag from their last CTA, and
+// each consuming GEMV waits for the flags itself after it has started its weight prefetch, so an exchange costs no
+// launch and its latency hides behind the weight stream; only the attention output still goes through a push kernel.
 static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
     const jllm_b200_model_desc& m = d->m;
     const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, I = m.intermediate_dim, hd = m.head_dim;
-    const int QD_l = d->nh_l * hd, KVD_l = d->nkv_l * hd, rank = d->tp.rank;
+    const int QD_l = d->nh_l * hd, KVD_l = d->nkv_l * hd, rank = d->tp.rank, world = d->tp.world;
     unsigned char* mine = d->tp.peer[rank];
     __half* att_full = (__half*)(mine + d->tp_off[0]); __half* x2_full = (__half*)(mine + d->tp_off[1]);
     __half* sw_full = (__half*)(mine + d->tp_off[2]);  __half* x_full = (__half*)(mine + d->tp_off[3]);
     const int* d_pos = d->state; const int* d_tok = d->state + 1;
     const float scale = 1.0f / sqrtf((float)hd);
     const long long l0 = jllm_b200_launch_count();
+    const bool fused = d->tp_fused;
+    auto wait_hook = [&](int point, int layer) {
+        GemvTpWait w;
+        w.flags = reinterpret_cast<const uint32_t*>(mine + d->tp.flags_off) + point * TP_MAX_WORLD;
+        w.world = world; w.seq = d->seq; w.epochs_per_step = m.n_layers; w.layer = layer;
+        return w;
+    };
+    auto push_hook = [&](int point, int layer, int rows_local) {
+        GemvTpPush q;
+        for (int r = 0; r < 8; ++r) q.peer[r] = r < world ? d->tp.peer[r] : nullptr;
+        q.world = world; q.buf_off = d->tp_off[point]; q.row_off = rank * rows_local;
+        q.flag_off = d->tp.flags_off + (point * TP_MAX_WORLD + rank) * 4;
+        q.seq = d->seq; q.epochs_per_step = m.n_layers; q.layer = layer; q.counter = d->seq + 8 + point;
+        return q;
+    };
     DCHK(launch_embed_row(x_full, m.tok_embd, m.embd_type, 0, d_tok, H, st));
     for (int l = 0; l < m.n_layers; ++l) {
         const jllm_b200_layer_desc& w = d->layers[l];
         int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
         float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
-        DCHK(jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD_l, d->k, w.wk, w.type_wk, KVD_l, d->v, w.wv, w.type_wv, KVD_l,
-                                              x_full, w.rms_attn, 1, m.rms_eps, H, st));
+        if (fused && l > 0) { const GemvTpWait wh = wait_hook(TP_POINT_X, l - 1); gemv_set_tp_hooks(&wh, nullptr); }
+        int rc = jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD_l, d->k, w.wk, w.type_wk, KVD_l, d->v, w.wv, w.type_wv, KVD_l,
+                                                  x_full, w.rms_attn, 1, m.rms_eps, H, st);
+        gemv_set_tp_hooks(nullptr, nullptr);
+        DCHK(rc);
         DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, d->nh_l, d->nkv_l, hd,
                              0, d_pos, m.rope_theta, m.rope_neox != 0, true, st));
         AttnCall c;
         c.out = d->att; c.q = d->q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = d->nh_l; c.n_kv = d->nkv_l;
         c.hd = hd; c.chd = hd; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
         DCHK(launch_attention(c, st));
-        DCHK(launch_tp_allgather(d->tp, d->att, QD_l * 2, d->tp_off[0], TP_POINT_ATT, l, st));
-        DCHK(jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st));
-        DCHK(launch_tp_allgather(d->tp, d->x2, d->H_l * 2, d->tp_off[1], TP_POINT_X2, l, st));
-        DCHK(jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st));
-        DCHK(launch_tp_allgather(d->tp, d->sw, d->I_l * 2, d->tp_off[2], TP_POINT_SW, l, st));
-        DCHK(jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st));
-        DCHK(launch_tp_allgather(d->tp, d->x, d->H_l * 2, d->tp_off[3], TP_POINT_X, l, st));
+        DCHK(launch_tp_allgather(d->tp, d->att, QD_l * 2, d->tp_off[0], TP_POINT_ATT, l, !fused, st));
+        if (fused) {
+            const GemvTpWait wh = wait_hook(TP_POINT_ATT, l); const GemvTpPush ph = push_hook(TP_POINT_X2, l, d->H_l);
+            gemv_set_tp_hooks(&wh, &ph);
+        }
+        rc = jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st);
+        gemv_set_tp_hooks(nullptr, nullptr);
+        DCHK(rc);
+        if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_X2, l); const GemvTpPush ph = push_hook(TP_POINT_SW, l, d->I_l); gemv_set_tp_hooks(&wh, &ph); }
+        else DCHK(launch_tp_allgather(d->tp, d->x2, d->H_l * 2, d->tp_off[1], TP_POINT_X2, l, true, st));
+        rc = jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st);
+        gemv_set_tp_hooks(nullptr, nullptr);
+        DCHK(rc);
+        if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_SW, l); const GemvTpPush ph = push_hook(TP_POINT_X, l, d->H_l); gemv_set_tp_hooks(&wh, &ph); }
+        else DCHK(launch_tp_allgather(d->tp, d->sw, d->I_l * 2, d->tp_off[2], TP_POINT_SW, l, true, st));
+        rc = jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st);
+        gemv_set_tp_hooks(nullptr, nullptr);
+        DCHK(rc);
+        if (!fused) DCHK(launch_tp_allgather(d->tp, d->x, d->H_l * 2, d->tp_off[3], TP_POINT_X, l, true, st));
     }
+    if (fused) DCHK(launch_tp_allgather(d->tp, nullptr, 0, d->tp_off[3], TP_POINT_X, m.n_layers - 1, true, st));
     DCHK(launch_rmsnorm(d->normed, x_full, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
     DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, d->V_l, H, st));
     DCHK(launch_tp_argmax(d->tp, d->logits, d->V_l, d->state, d->out_tokens, d->out_cap, st));
@@ -264,7 +298,7 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
     d->layers.assign(model->layers, model->layers + model->n_layers);
     d->m.layers = d->layers.data();
     d->fused = true; d->use_graph = (flags & 2) != 0;
-    d->tp_on = true;
+    d->tp_on = true; d->tp_fused = (flags & 4) == 0;      // bit 2: keep every gather in its own kernel (the unfused baseline)
     d->nh_l = model->n_heads / world; d->nkv_l = model->n_kv_heads / world; d->I_l = model->intermediate_dim / world;
     d->H_l = model->hidden_dim / world; d->V_l = model->vocab_size / world;
     tp_region_layout(model->hidden_dim, model->n_heads * hd, model->intermediate_dim, d->tp_off);

@@ -42,7 +42,18 @@ struct GvParams {
     int slot_bytes, nslots, needA, needB, paired_rows;
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
     long long total_bytes;      // Σ over segments of (row groups x bytes per group)
+    int tp_wait_on, tp_push_on;
+    GemvTpWait tpw;
+    GemvTpPush tpp;
 };
+
+static thread_local bool g_tp_wait_set = false, g_tp_push_set = false;
+static thread_local GemvTpWait g_tp_wait;
+static thread_local GemvTpPush g_tp_push;
+void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
+    g_tp_wait_set = w != nullptr; if (w) g_tp_wait = *w;
+    g_tp_push_set = q != nullptr; if (q) g_tp_push = *q;
+}
 
 // ── activation staging ───────────────────────────────────────────────────
 // Layout A (read by Q4_K items), per 256 elements: the 16-element run r = 2*(j>>1)+h of sub-block j = 2*il + p
@@ -405,6 +416,19 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
     }
     pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
     pdl_wait();                  // x (and the residual) come from the kernel before us
+    if (p.tp_wait_on) {          // ... and, tensor-parallel, partly from the other ranks: their flags must have reached this exchange's epoch
+        if (tid < p.tpw.world) {
+            const uint32_t epoch = p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u;
+            uint32_t v, i = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.tpw.flags + tid) : "memory");
+                if (v >= epoch) break;
+                if (++i > (1u << 22)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
+                __nanosleep(32);
+            }
+        }
+        __syncthreads();
+    }
     stage_x<XM>(p, smem, red);
     __syncthreads();
 
@@ -451,6 +475,26 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
             for (int r = 0; r < 4; ++r) gate_keep[r] = __shfl_sync(0xFFFFFFFFu, __half2float(__float2half_rn(mine)), r);
             continue;
         }
+        if (p.tp_push_on) {
+            if (lane < nrows) {
+                const int row = row0 + lane;
+                __half hv;
+                if (p.out_mode == 2) {
+                    const __half pr = __float2half_rn(mine);
+                    hv = __float2half_rn(__fadd_rn(__half2float(pr), __half2float(p.residual[row])));
+                } else if (p.out_mode == 3) {
+                    const float u = __half2float(__float2half_rn(mine));
+                    const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
+                    hv = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u));
+                } else {
+                    hv = __float2half_rn(mine);
+                }
+                #pragma unroll 1
+                for (int r = 0; r < p.tpp.world; ++r)
+                    reinterpret_cast<__half*>(p.tpp.peer[r] + p.tpp.buf_off)[p.tpp.row_off + row] = hv;
+            }
+            continue;
+        }
         if (lane < nrows) {
             const int row = row0 + lane;
             if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(mine);
@@ -466,6 +510,21 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
         }
     }
     if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
+    if (p.tp_push_on) {
+        // every store above must be visible on the peers before the flag: fence, count the CTA in, and let the last one signal
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int done = atomicAdd(p.tpp.counter, 1u);
+            if (done == gridDim.x - 1) {
+                *p.tpp.counter = 0u;
+                __threadfence_system();
+                const uint32_t epoch = p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u;
+                for (int r = 0; r < p.tpp.world; ++r)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tpp.peer[r] + p.tpp.flag_off), "r"(epoch) : "memory");
+            }
+        }
+    }
 }
 
 // ── Q5_K (and nothing else): plain warp-per-row kernel with the reference's float
@@ -523,6 +582,12 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
     p.nseg = a.nseg; p.x = a.x; p.K = a.K; p.out_mode = a.out_mode; p.residual = a.residual;
     p.do_norm = a.do_norm; p.norm_w = a.norm_w; p.norm_w_fp32 = a.norm_w_fp32; p.eps = a.eps;
     p.dbg_dots = a.dbg_dots; p.status = cx->d_status;
+    p.tp_wait_on = g_tp_wait_set; p.tp_push_on = g_tp_push_set;
+    if (g_tp_wait_set) p.tpw = g_tp_wait;
+    if (g_tp_push_set) p.tpp = g_tp_push;
+    g_tp_wait_set = g_tp_push_set = false;
+    if (p.tp_push_on && (a.out_mode == 1 || a.nseg > 2 || (a.nseg == 2 && a.out_mode != 3)))
+        return set_error(JB_ERR_ARG, "gemv: a pushed result must be one fp16 vector");
     const int nb = a.K / QK_K;
     long long total_rows = 0;
     for (int i = 0; i < a.nseg; ++i) {

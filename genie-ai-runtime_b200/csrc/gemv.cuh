@@ -26,6 +26,18 @@ struct GemvArgs {
     int32_t* dbg_dots = nullptr;      // optional: integer accumulators of seg 0
 };
 
+// Tensor-parallel hooks of one launch (csrc/tp.cu describes the exchange).  `wait`: before the activation vector is
+// read, flags[0..world) of this rank's own region must have reached the epoch seq[0]*epochs_per_step + layer + 1.
+// `push`: results are stored into the same slot of EVERY rank's region (row `row_off + row` of the fp16 vector at
+// buf_off) instead of seg.y, and the last CTA to finish raises this rank's flag in every region.
+struct GemvTpWait { const uint32_t* flags; int world; const uint32_t* seq; int epochs_per_step; int layer; };
+struct GemvTpPush {
+    unsigned char* peer[8]; int world; int buf_off; int row_off; int flag_off;      // flag_off: byte offset of this rank's flag word
+    const uint32_t* seq; int epochs_per_step; int layer; unsigned int* counter;     // counter: zeroed device word, one per exchange point
+};
+// The next launch_gemv on this thread takes the hooks (either may be null) and forgets them.
+void gemv_set_tp_hooks(const GemvTpWait* wait, const GemvTpPush* push);
+
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
 int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const __half* residual,
                     int M, int K, cudaStream_t st);

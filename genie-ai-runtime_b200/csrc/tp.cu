@@ -43,20 +43,23 @@ __device__ __forceinline__ bool tp_wait_flags(const TpDev& tp, int point, uint32
     return ok;
 }
 
-// all-gather of one slice: src (local, `bytes` long, a multiple of 16) -> offset buf_off + rank*bytes of every region
-__global__ void __launch_bounds__(256) tp_allgather_kernel(TpDev tp, const uint4* src, int bytes, int buf_off, int point, int layer) {
+// all-gather of one slice: src (local, `bytes` long, a multiple of 16) -> offset buf_off + rank*bytes of every region.
+// bytes = 0: nothing to push (the producer kernel pushed from its epilogue); wait = 0: the consumer kernel waits itself.
+__global__ void __launch_bounds__(256) tp_allgather_kernel(TpDev tp, const uint4* src, int bytes, int buf_off, int point, int layer, int wait) {
     pdl_wait();
     const int tid = threadIdx.x, n16 = bytes >> 4;
     const uint32_t epoch = tp.seq[0] * (uint32_t)tp.epochs_per_step + (uint32_t)layer + 1u;
-    for (int r = 0; r < tp.world; ++r) {
-        uint4* dst = reinterpret_cast<uint4*>(tp.peer[r] + buf_off + (size_t)tp.rank * bytes);
-        for (int i = tid; i < n16; i += blockDim.x) dst[i] = src[i];
+    if (bytes > 0) {
+        for (int r = 0; r < tp.world; ++r) {
+            uint4* dst = reinterpret_cast<uint4*>(tp.peer[r] + buf_off + (size_t)tp.rank * bytes);
+            for (int i = tid; i < n16; i += blockDim.x) dst[i] = src[i];
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < tp.world)
+            st_release_sys(reinterpret_cast<uint32_t*>(tp.peer[tid] + tp.flags_off) + point * TP_MAX_WORLD + tp.rank, epoch);
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < tp.world)
-        st_release_sys(reinterpret_cast<uint32_t*>(tp.peer[tid] + tp.flags_off) + point * TP_MAX_WORLD + tp.rank, epoch);
-    if (!tp_wait_flags(tp, point, epoch, tid)) atomicExch(tp.status, JB_ERR_TIMEOUT);
+    if (wait && !tp_wait_flags(tp, point, epoch, tid)) atomicExch(tp.status, JB_ERR_TIMEOUT);
 }
 
 // Greedy sampling over sharded logits: local argmax (lowest index among equal maxima, non-finite skipped, as the
@@ -114,10 +117,10 @@ __global__ void __launch_bounds__(1024) tp_argmax_advance_kernel(TpDev tp, const
     }
 }
 
-int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, cudaStream_t st) {
-    if (bytes <= 0 || (bytes & 15) || ((uintptr_t)src & 15) || (buf_off & 15))
+int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, bool wait, cudaStream_t st) {
+    if (bytes < 0 || (bytes & 15) || ((uintptr_t)src & 15) || (buf_off & 15))
         return set_error(JB_ERR_ARG, "tensor-parallel exchange: slice of %d bytes at offset %d is not 16-byte granular", bytes, buf_off);
-    JB_CUDA(launch_k(tp_allgather_kernel, dim3(1), dim3(256), 0, st, pdl_enabled(), tp, (const uint4*)src, bytes, buf_off, point, layer));
+    JB_CUDA(launch_k(tp_allgather_kernel, dim3(1), dim3(256), 0, st, pdl_enabled(), tp, (const uint4*)src, bytes, buf_off, point, layer, (int)wait));
     count_launch();
     return JB_OK;
 }

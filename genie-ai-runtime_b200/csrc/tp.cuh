@@ -35,7 +35,8 @@ inline size_t tp_region_layout(int hidden, int q_dim, int inter, int* offs) {
     return o;
 }
 
-int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, cudaStream_t st);
+// push (bytes > 0) and/or wait; the fused path pushes from GEMV epilogues and waits in the consuming GEMV (gemv.cuh hooks)
+int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, bool wait, cudaStream_t st);
 int launch_tp_argmax(const TpDev& tp, const float* logits, int n_local, int* state, int* out, int out_cap, cudaStream_t st);
 
 }  // namespace jb

@@ -102,5 +102,8 @@ def test_gpu_ranks_match_single_gpu(tmp_path, world):
     res = _run_ranks("gpu", world, tmp_path, 600)
     for r, z in enumerate(res):
         assert int(z["status"]) == 0
-        assert np.array_equal(z["tokens"], want), (r, z["tokens"], want)
-        assert np.array_equal(z["tokens2"], want)
+        for name in ("fused", "unfused", "nograph"):
+            assert np.array_equal(z[name], want), (r, name, z[name], want)
+            assert np.array_equal(z[name + "2"], want), (r, name)
+        # the fused path needs one launch per layer for the exchanges (attention output), the baseline four
+        assert int(z["unfused_kernels"]) - int(z["fused_kernels"]) == 3 * tp_worker.SMALL["n_layers"] - 1

@@ -98,13 +98,15 @@ def main():
         decmod = importlib.import_module(pk.__name__ + ".decoder")
         torch.cuda.set_device(rank)
         local = decmod.upload(tp.shard_model(model, world, rank))
-        d = tp.TPDecoder(model["cfg"], local, 64, rank, world)
         st = torch.cuda.Stream()
-        toks = d.generate(PROMPT, N_NEW, st)
-        toks2 = d.generate(PROMPT, N_NEW, st)          # a second run through the same exchange regions
-        status = pk.device_status(st)
-        np.savez(out_path, tokens=toks, tokens2=toks2, status=np.int32(status), kernels=np.int32(d.kernels_per_step()))
-        d.close()
+        res = {}
+        for name, flags in (("fused", 3), ("unfused", 7), ("nograph", 1)):
+            d = tp.TPDecoder(model["cfg"], local, 64, rank, world, flags=flags)
+            res[name] = d.generate(PROMPT, N_NEW, st)
+            res[name + "2"] = d.generate(PROMPT, N_NEW, st)          # a second run through the same exchange regions
+            res[name + "_kernels"] = np.int32(d.kernels_per_step())
+            d.close()
+        np.savez(out_path, status=np.int32(pk.device_status(st)), **res)
     dist.barrier()
     dist.destroy_process_group()
 
