@@ -167,7 +167,7 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
 
 // One decode step of a tensor-parallel rank: the single-GPU sequence on this rank's rows and heads, with the four
 // gathers of a layer in between.  Full vectors live in this rank's exchange region.  tp_fused: the Wo, gate/up and
-// W_down kernels store their rows straight into every rank's region and raise the flag from their last CTA, and
+// W_down kernels write their rows into this rank's region, their last CTA copies the slice to the peers and raises the flag, and
 // each consuming GEMV waits for the flags itself after it has started its weight prefetch, so an exchange costs no
 // launch and its latency hides behind the weight stream; only the attention output still goes through a push kernel.
 static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
@@ -190,7 +190,7 @@ static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t 
     auto push_hook = [&](int point, int layer, int rows_local) {
         GemvTpPush q;
         for (int r = 0; r < 8; ++r) q.peer[r] = r < world ? d->tp.peer[r] : nullptr;
-        q.world = world; q.buf_off = d->tp_off[point]; q.row_off = rank * rows_local;
+        q.world = world; q.rank = rank; q.buf_off = d->tp_off[point]; q.row_off = rank * rows_local; q.rows = rows_local;
         q.flag_off = d->tp.flags_off + (point * TP_MAX_WORLD + rank) * 4;
         q.seq = d->seq; q.epochs_per_step = m.n_layers; q.layer = layer; q.counter = d->seq + 8 + point;
         return q;
@@ -216,17 +216,17 @@ static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t 
             const GemvTpWait wh = wait_hook(TP_POINT_ATT, l); const GemvTpPush ph = push_hook(TP_POINT_X2, l, d->H_l);
             gemv_set_tp_hooks(&wh, &ph);
         }
-        rc = jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st);
+        rc = jllm_b200_gemv_quant_add(fused ? x2_full + (size_t)rank * d->H_l : d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st);
         gemv_set_tp_hooks(nullptr, nullptr);
         DCHK(rc);
         if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_X2, l); const GemvTpPush ph = push_hook(TP_POINT_SW, l, d->I_l); gemv_set_tp_hooks(&wh, &ph); }
         else DCHK(launch_tp_allgather(d->tp, d->x2, d->H_l * 2, d->tp_off[1], TP_POINT_X2, l, true, st));
-        rc = jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st);
+        rc = jllm_b200_norm_gemv_pair_swiglu(fused ? sw_full + (size_t)rank * d->I_l : d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st);
         gemv_set_tp_hooks(nullptr, nullptr);
         DCHK(rc);
         if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_SW, l); const GemvTpPush ph = push_hook(TP_POINT_X, l, d->H_l); gemv_set_tp_hooks(&wh, &ph); }
         else DCHK(launch_tp_allgather(d->tp, d->sw, d->I_l * 2, d->tp_off[2], TP_POINT_SW, l, true, st));
-        rc = jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st);
+        rc = jllm_b200_gemv_quant_add(fused ? x_full + (size_t)rank * d->H_l : d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st);
         gemv_set_tp_hooks(nullptr, nullptr);
         DCHK(rc);
         if (!fused) DCHK(launch_tp_allgather(d->tp, d->x, d->H_l * 2, d->tp_off[3], TP_POINT_X, l, true, st));

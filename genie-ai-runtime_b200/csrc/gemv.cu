@@ -417,14 +417,17 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
     pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
     pdl_wait();                  // x (and the residual) come from the kernel before us
     if (p.tp_wait_on) {          // ... and, tensor-parallel, partly from the other ranks: their flags must have reached this exchange's epoch
-        if (tid < p.tpw.world) {
+        if (tid == 0) {          // one poller per CTA: hundreds of CTAs look at the same few words
             const uint32_t epoch = p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u;
-            uint32_t v, i = 0;
-            for (;;) {
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.tpw.flags + tid) : "memory");
-                if (v >= epoch) break;
-                if (++i > (1u << 22)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
-                __nanosleep(32);
+            uint32_t i = 0;
+            for (int r = 0; r < p.tpw.world; ++r) {
+                for (;;) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.tpw.flags + r) : "memory");
+                    if (v >= epoch) break;
+                    if (++i > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
+                    __nanosleep(100);
+                }
             }
         }
         __syncthreads();
@@ -475,26 +478,6 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
             for (int r = 0; r < 4; ++r) gate_keep[r] = __shfl_sync(0xFFFFFFFFu, __half2float(__float2half_rn(mine)), r);
             continue;
         }
-        if (p.tp_push_on) {
-            if (lane < nrows) {
-                const int row = row0 + lane;
-                __half hv;
-                if (p.out_mode == 2) {
-                    const __half pr = __float2half_rn(mine);
-                    hv = __float2half_rn(__fadd_rn(__half2float(pr), __half2float(p.residual[row])));
-                } else if (p.out_mode == 3) {
-                    const float u = __half2float(__float2half_rn(mine));
-                    const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
-                    hv = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u));
-                } else {
-                    hv = __float2half_rn(mine);
-                }
-                #pragma unroll 1
-                for (int r = 0; r < p.tpp.world; ++r)
-                    reinterpret_cast<__half*>(p.tpp.peer[r] + p.tpp.buf_off)[p.tpp.row_off + row] = hv;
-            }
-            continue;
-        }
         if (lane < nrows) {
             const int row = row0 + lane;
             if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(mine);
@@ -511,17 +494,32 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
     }
     if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
     if (p.tp_push_on) {
-        // every store above must be visible on the peers before the flag: fence, count the CTA in, and let the last one signal
-        __threadfence_system();
+        // The rows went to this rank's own region (seg.y points into it).  The last CTA to finish copies the whole slice
+        // to the other ranks with 16-byte stores and then raises this rank's flag everywhere: one system-scope fence
+        // per launch instead of one per CTA.
+        __shared__ int is_last;
+        __threadfence();
         __syncthreads();
         if (tid == 0) {
             const unsigned int done = atomicAdd(p.tpp.counter, 1u);
-            if (done == gridDim.x - 1) {
-                *p.tpp.counter = 0u;
-                __threadfence_system();
+            is_last = done == gridDim.x - 1;
+            if (is_last) *p.tpp.counter = 0u;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            const int n16 = p.tpp.rows >> 3;                      // 8 halves per 16 bytes
+            const uint4* src = reinterpret_cast<const uint4*>(p.tpp.peer[p.tpp.rank] + p.tpp.buf_off) + (p.tpp.row_off >> 3);
+            for (int r = 0; r < p.tpp.world; ++r) {
+                if (r == p.tpp.rank) continue;
+                uint4* dst = reinterpret_cast<uint4*>(p.tpp.peer[r] + p.tpp.buf_off) + (p.tpp.row_off >> 3);
+                for (int i = tid; i < n16; i += GV_THREADS) dst[i] = __ldcg(src + i);
+            }
+            __threadfence_system();
+            __syncthreads();
+            if (tid < p.tpp.world) {
                 const uint32_t epoch = p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u;
-                for (int r = 0; r < p.tpp.world; ++r)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tpp.peer[r] + p.tpp.flag_off), "r"(epoch) : "memory");
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tpp.peer[tid] + p.tpp.flag_off), "r"(epoch) : "memory");
             }
         }
     }

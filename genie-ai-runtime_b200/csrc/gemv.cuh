@@ -28,11 +28,12 @@ struct GemvArgs {
 
 // Tensor-parallel hooks of one launch (csrc/tp.cu describes the exchange).  `wait`: before the activation vector is
 // read, flags[0..world) of this rank's own region must have reached the epoch seq[0]*epochs_per_step + layer + 1.
-// `push`: results are stored into the same slot of EVERY rank's region (row `row_off + row` of the fp16 vector at
-// buf_off) instead of seg.y, and the last CTA to finish raises this rank's flag in every region.
+// `push`: seg.y must point at rows [row_off, row_off + rows) of the fp16 vector at buf_off in this rank's OWN region;
+// the last CTA to finish copies that slice to the same place in every other region and raises this rank's flag in
+// every region.  rows and row_off must be multiples of 8 (16-byte copies).
 struct GemvTpWait { const uint32_t* flags; int world; const uint32_t* seq; int epochs_per_step; int layer; };
 struct GemvTpPush {
-    unsigned char* peer[8]; int world; int buf_off; int row_off; int flag_off;      // flag_off: byte offset of this rank's flag word
+    unsigned char* peer[8]; int world, rank; int buf_off; int row_off, rows; int flag_off;      // flag_off: byte offset of this rank's flag word
     const uint32_t* seq; int epochs_per_step; int layer; unsigned int* counter;     // counter: zeroed device word, one per exchange point
 };
 // The next launch_gemv on this thread takes the hooks (either may be null) and forgets them.
