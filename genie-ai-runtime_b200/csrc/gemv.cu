@@ -22,8 +22,8 @@
 
 namespace jb {
 
-constexpr int GV_WARPS   = 4;
-constexpr int GV_THREADS = GV_WARPS * 32;
+constexpr int GV_MAXWARPS = 16;                // one CTA per SM; 16, 8 or 4 warps depending on how large a row group is
+constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
 
 struct GvSegDev {
@@ -31,7 +31,7 @@ struct GvSegDev {
     int rb;          // row bytes
     int U;           // work items per row: 4 per super-block for both types
     int R;           // rows per warp pass ("row group")
-    int trc;         // rows per chunk = GV_WARPS * R
+    int trc;         // rows per chunk = warps * R
 };
 struct GvParams {
     GvSegDev seg[3]; int nseg;
@@ -39,7 +39,7 @@ struct GvParams {
     int out_mode; const __half* residual;
     int do_norm; const void* norm_w; int norm_w_fp32; float eps;
     int32_t* dbg_dots; int* status;
-    int slot_bytes, nslots, needA, needB, paired_rows;
+    int slot_bytes, nslots, needA, needB, paired_rows, nwarps;
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
     long long total_bytes;      // Σ over segments of (row groups x bytes per group)
     int tp_wait_on, tp_push_on;
@@ -63,12 +63,12 @@ void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
 // second plane with the low bytes follows at +K.
 template <int XM>
 __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = p.nwarps * 32;
     const int K = p.K;
     float rrms = 1.0f;
     if (p.do_norm) {   // reference: fused_rmsnorm_residual, src/kernels/fused_norm.cu:33-101
         float ss = 0.f;
-        for (int g8 = tid; g8 < K / 8; g8 += GV_THREADS) {
+        for (int g8 = tid; g8 < K / 8; g8 += nthreads) {
             const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * g8);
             const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
             #pragma unroll
@@ -78,103 +78,99 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         if (lane == 0) red[warp] = ss;
         __syncthreads();
         float tot = 0.f;
-        #pragma unroll
-        for (int w = 0; w < GV_WARPS; ++w) tot += red[w];
+        for (int w = 0; w < p.nwarps; ++w) tot += red[w];
         rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
     }
     uint8_t* xA = smem + p.off_xA; uint8_t* xB = smem + p.off_xB;
     float* xd = reinterpret_cast<float*>(smem + p.off_xd);
     float* xs = reinterpret_cast<float*>(smem + p.off_xs);
     int*   xsum = reinterpret_cast<int*>(smem + p.off_xsum);
-    // one thread per 32-element group: no shuffles, one pair of divisions per group
-    for (int gi = tid; gi < K / 32; gi += GV_THREADS) {
-        float v[32];
-        #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 32 * gi + 8 * q4);
+    // Four threads per 32-element group, eight elements each (one 16-byte load); the group's absmax and sums are
+    // combined with two xor-shuffles inside the quad.  K is a multiple of 256, so K/8 is a multiple of 32 and a warp is
+    // either entirely inside the loop or entirely outside: the shuffles are always between live lanes.
+    for (int it = tid; it < K / 8; it += nthreads) {
+        const int gi = it >> 2, q4 = it & 3;
+        float v[8];
+        {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * it);
             const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
             #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                v[8 * q4 + 2 * i] = a.x; v[8 * q4 + 2 * i + 1] = a.y;
+                v[2 * i] = a.x; v[2 * i + 1] = a.y;
             }
         }
         if (p.do_norm) {
-            float wn[32];
+            float wn[8];
             if (p.norm_w_fp32) {
                 #pragma unroll
-                for (int q4 = 0; q4 < 8; ++q4) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + 32 * gi + 4 * q4);
-                    wn[4 * q4] = w4.x; wn[4 * q4 + 1] = w4.y; wn[4 * q4 + 2] = w4.z; wn[4 * q4 + 3] = w4.w;
+                for (int h = 0; h < 2; ++h) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + 8 * it + 4 * h);
+                    wn[4 * h] = w4.x; wn[4 * h + 1] = w4.y; wn[4 * h + 2] = w4.z; wn[4 * h + 3] = w4.w;
                 }
             } else {
+                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.norm_w) + 8 * it);
+                const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
                 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.norm_w) + 32 * gi + 8 * q4);
-                    const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
-                    #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                        wn[8 * q4 + 2 * i] = a.x; wn[8 * q4 + 2 * i + 1] = a.y;
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                    wn[2 * i] = a.x; wn[2 * i + 1] = a.y;
                 }
             }
             #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i], rrms), wn[i])));
+            for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i], rrms), wn[i])));
         }
         float amax = 0.f;
         #pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
         const float lim = XM == 0 ? 127.0f : 32767.0f;
         const float d = __fdiv_rn(amax, lim);                      // q8_1: src/kernels/gemv_q4.cu:445-466
         const float id = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
-        uint32_t hi[8], lo[8];
-        int s16[2] = { 0, 0 };
-        float fsum = 0.f;
+        uint32_t hi[2] = { 0, 0 }, lo[2] = { 0, 0 };
+        int s8 = 0;
         #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            hi[w] = 0; lo[w] = 0;
+        for (int w = 0; w < 2; ++w) {
             #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float x = v[4 * w + i];
                 const int q = max(-(int)lim, min((int)lim, __float2int_rn(__fmul_rn(x, id))));
-                s16[w >> 2] += q;
+                s8 += q;
                 if (XM == 0) hi[w] |= (uint32_t)(q & 0xFF) << (8 * i);
                 else { hi[w] |= (uint32_t)((q >> 8) & 0xFF) << (8 * i); lo[w] |= (uint32_t)(q & 0xFF) << (8 * i); }
             }
         }
+        const int s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);          // code sum of this thread's 16-element half
+        const int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
+        float fsum = 0.f;
         if (XM == 1) {
             // fp32 sum of the group in the order of an 8-lane xor tree over 4-element partial sums
-            float ps[8];
-            #pragma unroll
-            for (int w = 0; w < 8; ++w) ps[w] = (v[4 * w] + v[4 * w + 1]) + (v[4 * w + 2] + v[4 * w + 3]);
-            fsum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+            const float t = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            const float t2 = t + __shfl_xor_sync(0xFFFFFFFFu, t, 1);
+            fsum = t2 + __shfl_xor_sync(0xFFFFFFFFu, t2, 2);
         }
-        const int blk = gi >> 3, j = gi & 7;
+        const int blk = gi >> 3, j = gi & 7, h = q4 >> 1, e8 = (q4 & 1) * 8;    // 16-element half h, byte offset inside its run
         if (p.needA) {
-            #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4));
-                *reinterpret_cast<uint4*>(xA + off) = make_uint4(hi[4 * h], hi[4 * h + 1], hi[4 * h + 2], hi[4 * h + 3]);
-                if (XM == 1) *reinterpret_cast<uint4*>(xA + K + off) = make_uint4(lo[4 * h], lo[4 * h + 1], lo[4 * h + 2], lo[4 * h + 3]);
-            }
+            const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4)) + e8;
+            *reinterpret_cast<uint2*>(xA + off) = make_uint2(hi[0], hi[1]);
+            if (XM == 1) *reinterpret_cast<uint2*>(xA + K + off) = make_uint2(lo[0], lo[1]);
         }
         if (p.needB) {
             const int n = j >> 2, k = j & 3;
-            #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int off = k * (K >> 2) + (blk * 4 + 2 * n + c) * 16;
-                *reinterpret_cast<uint4*>(xB + off) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-                if (XM == 1) *reinterpret_cast<uint4*>(xB + K + off) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-                xsum[2 * gi + c] = s16[c];
-            }
+            const int off = k * (K >> 2) + (blk * 4 + 2 * n + h) * 16 + e8;
+            *reinterpret_cast<uint2*>(xB + off) = make_uint2(hi[0], hi[1]);
+            if (XM == 1) *reinterpret_cast<uint2*>(xB + K + off) = make_uint2(lo[0], lo[1]);
+            if ((q4 & 1) == 0) xsum[2 * gi + h] = s16;
         }
-        if (XM == 0) {
-            xd[gi] = __half2float(__float2half_rn(d));
-            xs[gi] = __half2float(__float2half_rn(__fmul_rn(d, (float)(s16[0] + s16[1]))));
-        } else {
-            xd[gi] = d;
-            xs[gi] = fsum;
+        if (q4 == 0) {
+            if (XM == 0) {
+                xd[gi] = __half2float(__float2half_rn(d));
+                xs[gi] = __half2float(__float2half_rn(__fmul_rn(d, (float)s32)));
+            } else {
+                xd[gi] = d;
+                xs[gi] = fsum;
+            }
         }
     }
 }
@@ -339,10 +335,10 @@ __device__ __forceinline__ bool gv_task(const GvParams& p, const GvRange& rg, in
     int g;
     if (p.paired_rows) {               // (gate group, up group) of the same rows, back to back on one warp
         seg = u & 1;
-        g = rg.gf[0] + warp + GV_WARPS * (u >> 1);
+        g = rg.gf[0] + warp + p.nwarps * (u >> 1);
         if (g >= rg.gl[0]) return false;
     } else {
-        int t = warp + GV_WARPS * u;
+        int t = warp + p.nwarps * u;
         seg = -1;
         #pragma unroll
         for (int i = 0; i < 3; ++i) {
@@ -370,10 +366,10 @@ __device__ __forceinline__ void gv_issue(const GvParams& p, int seg, int row0, i
 }
 
 template <int XM, bool DBG>
-__global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GV_WARPS][GV_MAXSLOT];
-    __shared__ float red[GV_WARPS];
+    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
+    __shared__ float red[GV_MAXWARPS];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     // this CTA's row groups in every segment: an even split of all groups by bytes
@@ -513,7 +509,7 @@ __global__ void __launch_bounds__(GV_THREADS, 4) gemv_stream_kernel(const __grid
             for (int r = 0; r < p.tpp.world; ++r) {
                 if (r == p.tpp.rank) continue;
                 uint4* dst = reinterpret_cast<uint4*>(p.tpp.peer[r] + p.tpp.buf_off) + (p.tpp.row_off >> 3);
-                for (int i = tid; i < n16; i += GV_THREADS) dst[i] = __ldcg(src + i);
+                for (int i = tid; i < n16; i += (int)blockDim.x) dst[i] = __ldcg(src + i);
             }
             __threadfence_system();
             __syncthreads();
@@ -604,11 +600,10 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height and type");
     p.paired_rows = a.out_mode == 3;
     const int K = a.K, planes = a.xmode ? 2 : 1;
-    // Try 4, 2, then 1 CTA per SM: the shared-memory budget per CTA decides how large a row group each warp can stage.
-    const int smem_sm = cx->max_smem_optin + 1024;           // per-SM shared memory (per-CTA opt-in limit + 1 KB reserve)
-    for (int cps = 4; cps >= 1; cps >>= 1) {
-        int budget = smem_sm / cps - 1024 - 512;              // 1 KB system reserve per CTA, 512 B for static shared memory
-        if (budget > cx->max_smem_optin - 1024) budget = cx->max_smem_optin - 1024;
+    // One CTA per SM with 16, 8 or 4 warps: the activation vector is staged once per SM by all the CTA's threads, and
+    // what is left of the shared memory is split into one staging ring per warp; fewer warps mean larger rings.
+    const int budget = cx->max_smem_optin - 2048;             // opt-in limit minus this kernel's static shared memory
+    for (int nwarps = GV_MAXWARPS; nwarps >= 4; nwarps >>= 1) {
         uint32_t off = 0;
         p.off_xA = off; off += p.needA ? planes * K : 0;
         p.off_xB = off; off += p.needB ? planes * K : 0;
@@ -618,52 +613,59 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         p.off_gate = off;
         off = (off + 127) & ~127u;
         p.off_slots = off;
-        const int ring = (budget - (int)off) / GV_WARPS;      // bytes of staging ring per warp
+        const int ring = (budget - (int)off) / nwarps;        // bytes of staging ring per warp
         const int slot_cap = ring / 2;                        // at least two slots per warp
-        bool fits = slot_cap > 0;
+        if (slot_cap <= 0) continue;
+        int rb_max = 0;
+        for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
+        // rows per group: full lanes (items per group a multiple of 32) against enough groups to give every warp of
+        // every SM work; small matrices take fewer rows per group
+        const int U = nb * 4;
+        const double target = (double)cx->sm_count * nwarps * (a.out_mode == 3 ? 2 : 1);
+        int R = 0; double best = -1.0;
+        for (int cand = 4; cand >= 1; cand >>= 1) {
+            if ((long long)cand * rb_max + 16 > slot_cap) continue;
+            long long groups = 0;
+            for (int i = 0; i < a.nseg; ++i) groups += (a.seg[i].M + cand - 1) / cand;
+            const double fill = groups >= target ? 1.0 : groups / target;
+            const double score = lane_eff(cand, U) * fill;
+            if (score > best + 1e-9) { best = score; R = cand; }
+        }
+        if (!R) continue;
         int slot = 0;
         p.total_bytes = 0;
         long long groups_total = 0;
-        for (int i = 0; i < a.nseg && fits; ++i) {
+        for (int i = 0; i < a.nseg; ++i) {
             GvSegDev& d = p.seg[i];
             d.W = (const uint8_t*)a.seg[i].W; d.y = a.seg[i].y; d.M = a.seg[i].M; d.type = a.seg[i].type;
             d.rb = nb * block_bytes(d.type);
-            d.U = nb * 4;
-            int best = 0; double be = -1.0;
-            for (int R = 1; R <= 4; R *= 2) {
-                if ((long long)R * d.rb + 16 > slot_cap) break;
-                const double e = lane_eff(R, d.U);
-                if (e > be + 1e-9) { be = e; best = R; }
-            }
-            if (!best) { fits = false; break; }
-            d.R = best; d.trc = GV_WARPS * best;
+            d.U = U;
+            d.R = R; d.trc = nwarps * R;
             const int need = ((d.R * d.rb + 16 + 127) / 128) * 128;
             slot = need > slot ? need : slot;
             const long long groups = (d.M + d.R - 1) / d.R;
             p.total_bytes += groups * d.R * d.rb;
             groups_total += groups;
         }
-        if (!fits || ring / slot < 2) {
-            if (cps == 1) return set_error(JB_ERR_LIMIT, "gemv: one row group does not fit the staging ring (K=%d)", K);
-            continue;
-        }
+        if (ring / slot < 2) continue;
         p.slot_bytes = slot;
         p.nslots = ring / slot;
         if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
-        const size_t smem_bytes = (size_t)p.off_slots + (size_t)GV_WARPS * p.nslots * slot;
+        p.nwarps = nwarps;
+        const size_t smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
-        int grid = cx->sm_count * cps;
-        const long long ctas_useful = (groups_total + GV_WARPS - 1) / GV_WARPS;
+        int grid = cx->sm_count;
+        const long long ctas_useful = (groups_total + nwarps - 1) / nwarps;
         if (grid > ctas_useful) grid = (int)ctas_useful;
         if (grid < 1) grid = 1;
         auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
                                : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
         const int ki = (a.xmode ? 1 : 0) + (a.dbg_dots ? 2 : 0);
         if (!cx->gemv_attr[ki]) {
-            JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 1024));
+            JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
             cx->gemv_attr[ki] = true;
         }
-        JB_CUDA(launch_k(kern, dim3(grid), dim3(GV_THREADS), smem_bytes, st, pdl_enabled(), p));
+        JB_CUDA(launch_k(kern, dim3(grid), dim3(nwarps * 32), smem_bytes, st, pdl_enabled(), p));
         count_launch();
         return JB_OK;
     }
