@@ -165,44 +165,39 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
 }
 
 
-// One decode step of a tensor-parallel rank: the single-GPU sequence on this rank's rows and heads, with the four
-// gathers of a layer in between.  Full vectors live in this rank's exchange region.  tp_fused: the Wo, gate/up and
-// W_down kernels write their rows into this rank's region, their last CTA copies the slice to the peers and raises the flag, and
-// each consuming GEMV waits for the flags itself after it has started its weight prefetch, so an exchange costs no
-// launch and its latency hides behind the weight stream; only the attention output still goes through a push kernel.
+// One decode step of a tensor-parallel rank: the single-GPU sequence on this rank's rows and heads.  The Wo, gate/up
+// and W_down kernels send every finished row as a packet to all ranks from their epilogue, the attention output goes
+// out through one small push kernel, and each consuming GEMV polls the packets of its own region while it stages
+// its activation vector (after its weight prefetch is under way), so an exchange costs one one-way NVLink trip and,
+// but for the attention output, no launch.  Plain fp16 copies of this rank's own slices stay local for the residuals.
 static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
     const jllm_b200_model_desc& m = d->m;
     const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, I = m.intermediate_dim, hd = m.head_dim;
     const int QD_l = d->nh_l * hd, KVD_l = d->nkv_l * hd, rank = d->tp.rank, world = d->tp.world;
     unsigned char* mine = d->tp.peer[rank];
-    __half* att_full = (__half*)(mine + d->tp_off[0]); __half* x2_full = (__half*)(mine + d->tp_off[1]);
-    __half* sw_full = (__half*)(mine + d->tp_off[2]);  __half* x_full = (__half*)(mine + d->tp_off[3]);
+    const __half* att_pk = (const __half*)(mine + d->tp_off[0]); const __half* x2_pk = (const __half*)(mine + d->tp_off[1]);
+    const __half* sw_pk = (const __half*)(mine + d->tp_off[2]);  const __half* x_pk = (const __half*)(mine + d->tp_off[3]);
     const int* d_pos = d->state; const int* d_tok = d->state + 1;
     const float scale = 1.0f / sqrtf((float)hd);
     const long long l0 = jllm_b200_launch_count();
-    const bool fused = d->tp_fused;
-    auto wait_hook = [&](int point, int layer) {
-        GemvTpWait w;
-        w.flags = reinterpret_cast<const uint32_t*>(mine + d->tp.flags_off) + point * TP_MAX_WORLD;
-        w.world = world; w.seq = d->seq; w.epochs_per_step = m.n_layers; w.layer = layer;
-        return w;
-    };
+    auto wait_hook = [&](int layer) { GemvTpWait w; w.seq = d->seq; w.epochs_per_step = m.n_layers; w.layer = layer; return w; };
     auto push_hook = [&](int point, int layer, int rows_local) {
         GemvTpPush q;
         for (int r = 0; r < 8; ++r) q.peer[r] = r < world ? d->tp.peer[r] : nullptr;
-        q.world = world; q.rank = rank; q.buf_off = d->tp_off[point]; q.row_off = rank * rows_local; q.rows = rows_local;
-        q.flag_off = d->tp.flags_off + (point * TP_MAX_WORLD + rank) * 4;
-        q.seq = d->seq; q.epochs_per_step = m.n_layers; q.layer = layer; q.counter = d->seq + 8 + point;
+        q.world = world; q.buf_off = d->tp_off[point]; q.row_off = rank * rows_local;
+        q.seq = d->seq; q.epochs_per_step = m.n_layers; q.layer = layer;
         return q;
     };
-    DCHK(launch_embed_row(x_full, m.tok_embd, m.embd_type, 0, d_tok, H, st));
+    // d->normed holds the plain full x of layer 0 (the embedding row, computed by every rank); d->x / d->x2 hold this
+    // rank's own slices of x / x2
+    DCHK(launch_embed_row(d->normed, m.tok_embd, m.embd_type, 0, d_tok, H, st));
     for (int l = 0; l < m.n_layers; ++l) {
         const jllm_b200_layer_desc& w = d->layers[l];
         int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
         float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
-        if (fused && l > 0) { const GemvTpWait wh = wait_hook(TP_POINT_X, l - 1); gemv_set_tp_hooks(&wh, nullptr); }
+        if (l > 0) { const GemvTpWait wh = wait_hook(l - 1); gemv_set_tp_hooks(&wh, nullptr); }
         int rc = jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD_l, d->k, w.wk, w.type_wk, KVD_l, d->v, w.wv, w.type_wv, KVD_l,
-                                                  x_full, w.rms_attn, 1, m.rms_eps, H, st);
+                                                  l > 0 ? x_pk : d->normed, w.rms_attn, 1, m.rms_eps, H, st);
         gemv_set_tp_hooks(nullptr, nullptr);
         DCHK(rc);
         DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, d->nh_l, d->nkv_l, hd,
@@ -211,28 +206,32 @@ static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t 
         c.out = d->att; c.q = d->q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = d->nh_l; c.n_kv = d->nkv_l;
         c.hd = hd; c.chd = hd; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
         DCHK(launch_attention(c, st));
-        DCHK(launch_tp_allgather(d->tp, d->att, QD_l * 2, d->tp_off[0], TP_POINT_ATT, l, !fused, st));
-        if (fused) {
-            const GemvTpWait wh = wait_hook(TP_POINT_ATT, l); const GemvTpPush ph = push_hook(TP_POINT_X2, l, d->H_l);
+        DCHK(launch_tp_push(d->tp, d->att, QD_l, d->tp_off[0], rank * QD_l, l, st));
+        {
+            const GemvTpWait wh = wait_hook(l); const GemvTpPush ph = push_hook(TP_POINT_X2, l, d->H_l);
             gemv_set_tp_hooks(&wh, &ph);
+            const __half* resid = l > 0 ? d->x : d->normed + (size_t)rank * d->H_l;
+            rc = jllm_b200_gemv_quant_add(d->x2, w.wo, w.type_wo, att_pk, resid, d->H_l, QD, st);
+            gemv_set_tp_hooks(nullptr, nullptr);
+            DCHK(rc);
         }
-        rc = jllm_b200_gemv_quant_add(fused ? x2_full + (size_t)rank * d->H_l : d->x2, w.wo, w.type_wo, att_full, x_full + (size_t)rank * d->H_l, d->H_l, QD, st);
-        gemv_set_tp_hooks(nullptr, nullptr);
-        DCHK(rc);
-        if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_X2, l); const GemvTpPush ph = push_hook(TP_POINT_SW, l, d->I_l); gemv_set_tp_hooks(&wh, &ph); }
-        else DCHK(launch_tp_allgather(d->tp, d->x2, d->H_l * 2, d->tp_off[1], TP_POINT_X2, l, true, st));
-        rc = jllm_b200_norm_gemv_pair_swiglu(fused ? sw_full + (size_t)rank * d->I_l : d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_full, w.rms_ffn, 1, m.rms_eps, H, st);
-        gemv_set_tp_hooks(nullptr, nullptr);
-        DCHK(rc);
-        if (fused) { const GemvTpWait wh = wait_hook(TP_POINT_SW, l); const GemvTpPush ph = push_hook(TP_POINT_X, l, d->H_l); gemv_set_tp_hooks(&wh, &ph); }
-        else DCHK(launch_tp_allgather(d->tp, d->sw, d->I_l * 2, d->tp_off[2], TP_POINT_SW, l, true, st));
-        rc = jllm_b200_gemv_quant_add(fused ? x_full + (size_t)rank * d->H_l : d->x, w.w_down, w.type_w_down, sw_full, x2_full + (size_t)rank * d->H_l, d->H_l, I, st);
-        gemv_set_tp_hooks(nullptr, nullptr);
-        DCHK(rc);
-        if (!fused) DCHK(launch_tp_allgather(d->tp, d->x, d->H_l * 2, d->tp_off[3], TP_POINT_X, l, true, st));
+        {
+            const GemvTpWait wh = wait_hook(l); const GemvTpPush ph = push_hook(TP_POINT_SW, l, d->I_l);
+            gemv_set_tp_hooks(&wh, &ph);
+            rc = jllm_b200_norm_gemv_pair_swiglu(d->sw, w.w_gate, w.w_up, w.type_w_gate, d->I_l, x2_pk, w.rms_ffn, 1, m.rms_eps, H, st);
+            gemv_set_tp_hooks(nullptr, nullptr);
+            DCHK(rc);
+        }
+        {
+            const GemvTpWait wh = wait_hook(l); const GemvTpPush ph = push_hook(TP_POINT_X, l, d->H_l);
+            gemv_set_tp_hooks(&wh, &ph);
+            rc = jllm_b200_gemv_quant_add(d->x, w.w_down, w.type_w_down, sw_pk, d->x2, d->H_l, I, st);
+            gemv_set_tp_hooks(nullptr, nullptr);
+            DCHK(rc);
+        }
     }
-    if (fused) DCHK(launch_tp_allgather(d->tp, nullptr, 0, d->tp_off[3], TP_POINT_X, m.n_layers - 1, true, st));
-    DCHK(launch_rmsnorm(d->normed, x_full, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
+    DCHK(launch_tp_unpack(d->tp, d->gate, H, d->tp_off[3], m.n_layers - 1, st));          // d->gate: free scratch of at least H halves
+    DCHK(launch_rmsnorm(d->normed, d->gate, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
     DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, d->V_l, H, st));
     DCHK(launch_tp_argmax(d->tp, d->logits, d->V_l, d->state, d->out_tokens, d->out_cap, st));
     d->kernels_per_step = (int)(jllm_b200_launch_count() - l0);
@@ -288,8 +287,8 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
         ((model->n_heads / world) * hd * 2) % 16 || ((model->hidden_dim / world) * 2) % 16 || ((model->intermediate_dim / world) * 2) % 16) {
         set_error(JB_ERR_ARG, "decoder: heads, hidden, intermediate and vocabulary sizes must split evenly over %d ranks in 16-byte slices", world); return nullptr;
     }
-    if (model->hidden_dim % QK_K || model->intermediate_dim % QK_K || (model->n_heads * hd) % QK_K) {
-        set_error(JB_ERR_ARG, "decoder: hidden/intermediate/q dims must be multiples of 256"); return nullptr;
+    if (model->hidden_dim % QK_K || model->intermediate_dim % QK_K || (model->n_heads * hd) % QK_K || model->intermediate_dim < model->hidden_dim) {
+        set_error(JB_ERR_ARG, "decoder: hidden/intermediate/q dims must be multiples of 256, intermediate >= hidden"); return nullptr;
     }
     if (!ctx()) return nullptr;
     jllm_b200_decoder* d = new (std::nothrow) jllm_b200_decoder();
@@ -298,7 +297,7 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
     d->layers.assign(model->layers, model->layers + model->n_layers);
     d->m.layers = d->layers.data();
     d->fused = true; d->use_graph = (flags & 2) != 0;
-    d->tp_on = true; d->tp_fused = (flags & 4) == 0;      // bit 2: keep every gather in its own kernel (the unfused baseline)
+    d->tp_on = true;
     d->nh_l = model->n_heads / world; d->nkv_l = model->n_kv_heads / world; d->I_l = model->intermediate_dim / world;
     d->H_l = model->hidden_dim / world; d->V_l = model->vocab_size / world;
     tp_region_layout(model->hidden_dim, model->n_heads * hd, model->intermediate_dim, d->tp_off);

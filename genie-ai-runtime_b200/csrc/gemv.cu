@@ -61,18 +61,49 @@ void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
 // the 16-byte reads of eight neighbouring lanes (two blocks x four il) on different banks.  Layout B (Q6_K
 // items): plane k (= 32-wide quarter of a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a
 // second plane with the low bytes follows at +K.
+// Eight consecutive activations as floats: a 16-byte load of the plain fp16 vector, or, for a vector that arrives from
+// the other ranks, 64 bytes of packets polled (bounded) until every epoch word matches; the packets are read past L1.
+__device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epoch, float (&v)[8]) {
+    if (!p.tp_wait_on) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * it);
+        const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = a.x; v[2 * i + 1] = a.y;
+        }
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(p.x) + 4 * it;
+    uint4 q[4];
+    for (uint32_t tries = 0;; ++tries) {
+        bool ok = true;
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) { q[i] = __ldcv(src + i); ok = ok && q[i].y == epoch && q[i].w == epoch; }
+        if (ok) break;
+        if (tries > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
+        __nanosleep(20);
+    }
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i]     = __half2float(__ushort_as_half((unsigned short)(q[i].x & 0xFFFFu)));
+        v[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(q[i].z & 0xFFFFu)));
+    }
+}
+
 template <int XM>
 __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = p.nwarps * 32;
     const int K = p.K;
+    const uint32_t epoch = p.tp_wait_on ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
     float rrms = 1.0f;
     if (p.do_norm) {   // reference: fused_rmsnorm_residual, src/kernels/fused_norm.cu:33-101
         float ss = 0.f;
         for (int g8 = tid; g8 < K / 8; g8 += nthreads) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * g8);
-            const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+            float a[8];
+            gv_load8(p, g8, epoch, a);
             #pragma unroll
-            for (int i = 0; i < 4; ++i) { const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i])); ss += a.x * a.x + a.y * a.y; }
+            for (int i = 0; i < 4; ++i) ss += a[2 * i] * a[2 * i] + a[2 * i + 1] * a[2 * i + 1];
         }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
@@ -91,15 +122,7 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     for (int it = tid; it < K / 8; it += nthreads) {
         const int gi = it >> 2, q4 = it & 3;
         float v[8];
-        {
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * it);
-            const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
-            #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                v[2 * i] = a.x; v[2 * i + 1] = a.y;
-            }
-        }
+        gv_load8(p, it, epoch, v);
         if (p.do_norm) {
             float wn[8];
             if (p.norm_w_fp32) {
@@ -412,27 +435,12 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
     }
     pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
     pdl_wait();                  // x (and the residual) come from the kernel before us
-    if (p.tp_wait_on) {          // ... and, tensor-parallel, partly from the other ranks: their flags must have reached this exchange's epoch
-        if (tid == 0) {          // one poller per CTA: hundreds of CTAs look at the same few words
-            const uint32_t epoch = p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u;
-            uint32_t i = 0;
-            for (int r = 0; r < p.tpw.world; ++r) {
-                for (;;) {
-                    uint32_t v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.tpw.flags + r) : "memory");
-                    if (v >= epoch) break;
-                    if (++i > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
-                    __nanosleep(100);
-                }
-            }
-        }
-        __syncthreads();
-    }
     stage_x<XM>(p, smem, red);
     __syncthreads();
 
     const uint32_t sm0 = smem_u32(smem);
     const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K };
+    const uint32_t push_epoch = p.tp_push_on ? p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u : 0u;
     bool timed_out = false;
     float gate_keep[4] = { 0.f, 0.f, 0.f, 0.f };
     for (int u = 0;; ++u) {
@@ -486,39 +494,16 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
                 const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
                 reinterpret_cast<__half*>(p.seg[0].y)[row] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), hv));
             }
+            if (p.tp_push_on) {           // the value just stored, as a packet to every rank (this one included)
+                const unsigned short bits = __half_as_ushort(reinterpret_cast<const __half*>(p.out_mode == 3 ? p.seg[0].y : s.y)[row]);
+                const uint2 pkt = make_uint2((uint32_t)bits, push_epoch);
+                #pragma unroll 1
+                for (int r = 0; r < p.tpp.world; ++r)
+                    reinterpret_cast<uint2*>(p.tpp.peer[r] + p.tpp.buf_off)[p.tpp.row_off + row] = pkt;
+            }
         }
     }
     if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
-    if (p.tp_push_on) {
-        // The rows went to this rank's own region (seg.y points into it).  The last CTA to finish copies the whole slice
-        // to the other ranks with 16-byte stores and then raises this rank's flag everywhere: one system-scope fence
-        // per launch instead of one per CTA.
-        __shared__ int is_last;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned int done = atomicAdd(p.tpp.counter, 1u);
-            is_last = done == gridDim.x - 1;
-            if (is_last) *p.tpp.counter = 0u;
-        }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            const int n16 = p.tpp.rows >> 3;                      // 8 halves per 16 bytes
-            const uint4* src = reinterpret_cast<const uint4*>(p.tpp.peer[p.tpp.rank] + p.tpp.buf_off) + (p.tpp.row_off >> 3);
-            for (int r = 0; r < p.tpp.world; ++r) {
-                if (r == p.tpp.rank) continue;
-                uint4* dst = reinterpret_cast<uint4*>(p.tpp.peer[r] + p.tpp.buf_off) + (p.tpp.row_off >> 3);
-                for (int i = tid; i < n16; i += (int)blockDim.x) dst[i] = __ldcg(src + i);
-            }
-            __threadfence_system();
-            __syncthreads();
-            if (tid < p.tpp.world) {
-                const uint32_t epoch = p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tpp.peer[tid] + p.tpp.flag_off), "r"(epoch) : "memory");
-            }
-        }
-    }
 }
 
 // ── Q5_K (and nothing else): plain warp-per-row kernel with the reference's float

@@ -26,16 +26,17 @@ struct GemvArgs {
     int32_t* dbg_dots = nullptr;      // optional: integer accumulators of seg 0
 };
 
-// Tensor-parallel hooks of one launch (csrc/tp.cu describes the exchange).  `wait`: before the activation vector is
-// read, flags[0..world) of this rank's own region must have reached the epoch seq[0]*epochs_per_step + layer + 1.
-// `push`: seg.y must point at rows [row_off, row_off + rows) of the fp16 vector at buf_off in this rank's OWN region;
-// the last CTA to finish copies that slice to the same place in every other region and raises this rank's flag in
-// every region.  rows and row_off must be multiples of 8 (16-byte copies).
-struct GemvTpWait { const uint32_t* flags; int world; const uint32_t* seq; int epochs_per_step; int layer; };
-struct GemvTpPush {
-    unsigned char* peer[8]; int world, rank; int buf_off; int row_off, rows; int flag_off;      // flag_off: byte offset of this rank's flag word
-    const uint32_t* seq; int epochs_per_step; int layer; unsigned int* counter;     // counter: zeroed device word, one per exchange point
-};
+// Tensor-parallel hooks of one launch (csrc/tp.cu describes the exchange).  Exchanged vectors travel as 8-byte
+// packets {fp16 value in the low half of word 0, epoch in word 1}, one packet per element, written with single
+// 64-bit stores: a packet is valid exactly when its epoch word equals the epoch of this exchange
+// (seq[0]*epochs_per_step + layer + 1), so neither a fence nor a flag is needed and the transfer costs one
+// one-way trip over NVLink.
+// `wait`: GemvArgs.x points at a packet vector in this rank's own region; the staging pass polls every packet
+// (bounded) instead of waiting for the previous kernel only.
+// `push`: besides seg.y (this rank's plain fp16 slice, kept for the residual of a later kernel) every finished row
+// is sent as a packet to element row_off + row of the vector at buf_off in EVERY rank's region.
+struct GemvTpWait { const uint32_t* seq; int epochs_per_step; int layer; };
+struct GemvTpPush { unsigned char* peer[8]; int world; int buf_off; int row_off; const uint32_t* seq; int epochs_per_step; int layer; };
 // The next launch_gemv on this thread takes the hooks (either may be null) and forgets them.
 void gemv_set_tp_hooks(const GemvTpWait* wait, const GemvTpPush* push);
 

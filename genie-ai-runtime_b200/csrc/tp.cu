@@ -6,13 +6,15 @@
 // byte range; KV heads are independent in flash_attention_decode, src/kernels/attention.cu:626-760).
 //
 // Mechanism: every rank holds one exchange region (plain cudaMalloc memory, opened by the peers through CUDA
-// IPC).  A rank PUSHES its slice into the same offset of every peer's region with ordinary 16-byte stores over
-// NVLink, fences, and then raises its flag word in every peer's region to the epoch of this exchange; it then
-// waits until all flags in its OWN region have reached the epoch.  Remote data therefore always lands in local
-// HBM before it is read, by plain loads of the next kernel.  No TMA touches peer memory.
+// IPC) with one packet vector per exchange point.  A packet is 8 bytes, {fp16 value, epoch}, written with one 64-bit
+// store; a rank PUSHES each element it produces into the same slot of every rank's region over NVLink (from the
+// epilogue of the GEMV that computes it, or from tp_push_kernel for the attention output) and never waits.  A
+// consumer polls the packets of its OWN region while it stages its activation vector: an element is there exactly
+// when its epoch word matches.  No fence, no flag and no round trip are on the path, remote data always lands in
+// local HBM before it is read, and no TMA touches peer memory.  Only the sharded greedy argmax still uses flag words.
 //
-// Epochs come from a device-side step counter, so the same captured graph serves every step.  Flags only grow;
-// a region is reused one layer later, and a rank can only reach the next use of a buffer after every peer has
+// Epochs come from a device-side step counter (epoch = step * layers + layer + 1), so the same captured graph
+// serves every step.  A vector is rewritten one layer later, and a rank can only get there after every peer has
 // pushed a later exchange, i.e. after the peer's reader of the previous contents has finished.
 //
 // Every wait is bounded: when it runs out the kernel records JB_ERR_TIMEOUT in the status word and returns.
@@ -43,23 +45,30 @@ __device__ __forceinline__ bool tp_wait_flags(const TpDev& tp, int point, uint32
     return ok;
 }
 
-// all-gather of one slice: src (local, `bytes` long, a multiple of 16) -> offset buf_off + rank*bytes of every region.
-// bytes = 0: nothing to push (the producer kernel pushed from its epilogue); wait = 0: the consumer kernel waits itself.
-__global__ void __launch_bounds__(256) tp_allgather_kernel(TpDev tp, const uint4* src, int bytes, int buf_off, int point, int layer, int wait) {
+// fp16 slice -> packets in every rank's region (elements [elem_off, elem_off + n) of the vector at buf_off)
+__global__ void __launch_bounds__(256) tp_push_kernel(TpDev tp, const __half* src, int n, int buf_off, int elem_off, int layer) {
     pdl_wait();
-    const int tid = threadIdx.x, n16 = bytes >> 4;
     const uint32_t epoch = tp.seq[0] * (uint32_t)tp.epochs_per_step + (uint32_t)layer + 1u;
-    if (bytes > 0) {
-        for (int r = 0; r < tp.world; ++r) {
-            uint4* dst = reinterpret_cast<uint4*>(tp.peer[r] + buf_off + (size_t)tp.rank * bytes);
-            for (int i = tid; i < n16; i += blockDim.x) dst[i] = src[i];
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (tid < tp.world)
-            st_release_sys(reinterpret_cast<uint32_t*>(tp.peer[tid] + tp.flags_off) + point * TP_MAX_WORLD + tp.rank, epoch);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint2 pkt = make_uint2((uint32_t)__half_as_ushort(src[i]), epoch);
+        for (int r = 0; r < tp.world; ++r) reinterpret_cast<uint2*>(tp.peer[r] + buf_off)[elem_off + i] = pkt;
     }
-    if (wait && !tp_wait_flags(tp, point, epoch, tid)) atomicExch(tp.status, JB_ERR_TIMEOUT);
+}
+// packets of this rank's own region -> plain fp16 vector (bounded poll per element)
+__global__ void __launch_bounds__(256) tp_unpack_kernel(TpDev tp, __half* dst, int n, int buf_off, int layer) {
+    pdl_wait();
+    const uint32_t epoch = tp.seq[0] * (uint32_t)tp.epochs_per_step + (uint32_t)layer + 1u;
+    const uint2* src = reinterpret_cast<const uint2*>(tp.peer[tp.rank] + buf_off);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        uint2 q;
+        for (uint32_t tries = 0;; ++tries) {
+            q = __ldcv(src + i);
+            if (q.y == epoch) break;
+            if (tries > TP_WAIT_POLLS) { atomicExch(tp.status, JB_ERR_TIMEOUT); break; }
+            __nanosleep(32);
+        }
+        dst[i] = __ushort_as_half((unsigned short)(q.x & 0xFFFFu));
+    }
 }
 
 // Greedy sampling over sharded logits: local argmax (lowest index among equal maxima, non-finite skipped, as the
@@ -117,10 +126,14 @@ __global__ void __launch_bounds__(1024) tp_argmax_advance_kernel(TpDev tp, const
     }
 }
 
-int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, bool wait, cudaStream_t st) {
-    if (bytes < 0 || (bytes & 15) || ((uintptr_t)src & 15) || (buf_off & 15))
-        return set_error(JB_ERR_ARG, "tensor-parallel exchange: slice of %d bytes at offset %d is not 16-byte granular", bytes, buf_off);
-    JB_CUDA(launch_k(tp_allgather_kernel, dim3(1), dim3(256), 0, st, pdl_enabled(), tp, (const uint4*)src, bytes, buf_off, point, layer, (int)wait));
+int launch_tp_push(const TpDev& tp, const void* src, int n, int buf_off, int elem_off, int layer, cudaStream_t st) {
+    if (n <= 0) return JB_OK;
+    JB_CUDA(launch_k(tp_push_kernel, dim3((n + 255) / 256 > 8 ? 8 : (n + 255) / 256), dim3(256), 0, st, pdl_enabled(), tp, (const __half*)src, n, buf_off, elem_off, layer));
+    count_launch();
+    return JB_OK;
+}
+int launch_tp_unpack(const TpDev& tp, void* dst, int n, int buf_off, int layer, cudaStream_t st) {
+    JB_CUDA(launch_k(tp_unpack_kernel, dim3((n + 255) / 256 > 8 ? 8 : (n + 255) / 256), dim3(256), 0, st, pdl_enabled(), tp, (__half*)dst, n, buf_off, layer));
     count_launch();
     return JB_OK;
 }

@@ -19,24 +19,24 @@ struct TpDev {
     int* status;                             // device status word
 };
 
-// Region layout (all ranks identical): full-size fp16 vectors att [q_dim], x2 [hidden], sw [intermediate], x [hidden],
-// each 256-byte aligned, then TP_POINTS x TP_MAX_WORLD flag words, then the argmax slots (values, indices).
+// Region layout (all ranks identical): full-size packet vectors (8 bytes per element) att [q_dim], x2 [hidden],
+// sw [intermediate], x [hidden], each 256-byte aligned, then TP_POINTS x TP_MAX_WORLD flag words, then the argmax slots (values, indices).
 // Returns the region size; offs (optional) receives {att, x2, sw, x, flags, argmax}.
 inline size_t tp_region_layout(int hidden, int q_dim, int inter, int* offs) {
     auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
     size_t o = 0;
-    const size_t a = o; o += al((size_t)q_dim * 2);
-    const size_t b = o; o += al((size_t)hidden * 2);
-    const size_t c = o; o += al((size_t)inter * 2);
-    const size_t d = o; o += al((size_t)hidden * 2);
+    const size_t a = o; o += al((size_t)q_dim * 8);
+    const size_t b = o; o += al((size_t)hidden * 8);
+    const size_t c = o; o += al((size_t)inter * 8);
+    const size_t d = o; o += al((size_t)hidden * 8);
     const size_t f = o; o += al((size_t)TP_POINTS * TP_MAX_WORLD * 4);
     const size_t g = o; o += al((size_t)TP_MAX_WORLD * 8);
     if (offs) { offs[0] = (int)a; offs[1] = (int)b; offs[2] = (int)c; offs[3] = (int)d; offs[4] = (int)f; offs[5] = (int)g; }
     return o;
 }
 
-// push (bytes > 0) and/or wait; the fused path pushes from GEMV epilogues and waits in the consuming GEMV (gemv.cuh hooks)
-int launch_tp_allgather(const TpDev& tp, const void* src, int bytes, int buf_off, int point, int layer, bool wait, cudaStream_t st);
+int launch_tp_push(const TpDev& tp, const void* src, int n, int buf_off, int elem_off, int layer, cudaStream_t st);
+int launch_tp_unpack(const TpDev& tp, void* dst, int n, int buf_off, int layer, cudaStream_t st);
 int launch_tp_argmax(const TpDev& tp, const float* logits, int n_local, int* state, int* out, int out_cap, cudaStream_t st);
 
 }  // namespace jb

@@ -240,8 +240,7 @@ const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);
  * jllm_b200_tp_region_bytes() bytes.  All ranks must run the same steps in the same order; the greedy token is
  * reduced across ranks on the device, so every rank returns the same token.  jllm_b200_decoder_logits() gives the
  * rank's vocab_size/world slice.  Waits between ranks are bounded: a rank that never arrives shows up as
- * JLLM_B200_ERR_TIMEOUT in jllm_b200_device_status().  flags: bit 1 = CUDA graph as above; bit 2 = every gather in a
- * kernel of its own (baseline) instead of pushes from the GEMV epilogues and waits inside the consuming GEMV. */
+ * JLLM_B200_ERR_TIMEOUT in jllm_b200_device_status().  flags: bit 1 = CUDA graph as above. */
 jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model, int flags, int rank, int world, void* const* regions);
 size_t jllm_b200_tp_region_bytes(int hidden_dim, int q_dim, int intermediate_dim);
 void*  jllm_b200_tp_alloc(size_t bytes);                    /* zeroed device memory for an exchange region */
