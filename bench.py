@@ -342,7 +342,10 @@ def main():
             "kernels_per_step": dec.kernels_per_step(),
             "clocks": clk.summary(),
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<q8_1> (fused RMSNorm + gate/up Q4_K GEMV + SwiGLU)",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from the ncu
+                         # capture summarised in profiles/gemv_pair_swiglu_q4k_9728x2560.md (scaled by rows when sharded)
+                         "traffic": 28077824 // (world if tp_mode else 1),
                          "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "peak_source": peak_src},
             "step_hbm": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (dev_ms / K * 1e-3) / 1e9,
                          "frac_of_peak": wbytes / (dev_ms / K * 1e-3) / 1e9 / (peak * (world if tp_mode else 1))},

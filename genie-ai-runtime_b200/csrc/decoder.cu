@@ -18,12 +18,15 @@ namespace jb {
 
 // greedy argmax over fp32 logits; also advances the device-side step state:
 // state[0] = position, state[1] = current token, state[2] = number of tokens written to `out`.
-__global__ void argmax_advance_kernel(const float* logits, int n, int* state, int* out, int out_cap) {
+// Several CTAs scan slices of the vocabulary; each leaves its best (value, index) in scratch, and the last one to
+// finish (atomic ticket, no waiting) reduces them and advances the state.  scratch: [0] ticket, [32..32+G) values,
+// [32+G..32+2G) indices, G = gridDim.x <= 64.
+__global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* logits, int n, int* state, int* out, int out_cap, unsigned int* scratch) {
     pdl_wait();
-    __shared__ float sv[32]; __shared__ int si[32];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float sv[32]; __shared__ int si[32]; __shared__ int last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = gridDim.x;
     float best = -INFINITY; int bi = 0x7FFFFFFF;
-    for (int i = tid; i < n; i += blockDim.x) {
+    for (int i = blockIdx.x * blockDim.x + tid; i < n; i += G * blockDim.x) {
         const float v = logits[i];
         if (isfinite(v) && (v > best || (v == best && i < bi))) { best = v; bi = i; }
     }
@@ -37,13 +40,26 @@ __global__ void argmax_advance_kernel(const float* logits, int n, int* state, in
     if (tid == 0) {
         for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
             if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
-        if (bi == 0x7FFFFFFF) bi = 0;
-        const int k = state[2];
-        if (out && k < out_cap) out[k] = bi;
-        state[2] = k + 1;
-        state[1] = bi;
-        state[0] = state[0] + 1;
+        reinterpret_cast<float*>(scratch)[32 + blockIdx.x] = best;
+        reinterpret_cast<int*>(scratch)[32 + G + blockIdx.x] = bi;
+        __threadfence();
+        last = atomicAdd(scratch, 1u) == (unsigned)G - 1;
     }
+    __syncthreads();
+    if (!last || tid != 0) return;
+    __threadfence();
+    scratch[0] = 0u;
+    best = -INFINITY; bi = 0x7FFFFFFF;
+    for (int g = 0; g < G; ++g) {
+        const float v = reinterpret_cast<volatile float*>(scratch)[32 + g]; const int i = reinterpret_cast<volatile int*>(scratch)[32 + G + g];
+        if (i != 0x7FFFFFFF && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+    }
+    if (bi == 0x7FFFFFFF) bi = 0;
+    const int k = state[2];
+    if (out && k < out_cap) out[k] = bi;
+    state[2] = k + 1;
+    state[1] = bi;
+    state[0] = state[0] + 1;
 }
 
 __global__ void set_state_kernel(int* state, int pos, int token) {
@@ -88,7 +104,7 @@ static int dec_alloc(jllm_b200_decoder* d) {
     // (a tensor-parallel rank could do with slice-sized buffers; the full sizes are a few hundred KB)
     const size_t H = m.hidden_dim, QD = (size_t)m.n_heads * m.head_dim, KVD = (size_t)m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
     auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
-    const size_t total = 3 * al(H * 2) + 2 * al(QD * 2) + 2 * al(KVD * 2) + 3 * al(I * 2) + al((size_t)m.vocab_size * 4) + al(64) +
+    const size_t total = 3 * al(H * 2) + 2 * al(QD * 2) + 2 * al(KVD * 2) + 3 * al(I * 2) + al((size_t)m.vocab_size * 4) + al(1024) +
                          al((size_t)(m.max_context + 8) * 4) * 2;
     if (cudaMalloc(&d->slab, total) != cudaSuccess) { cudaGetLastError(); return set_error(JB_ERR_NOMEM, "decoder: %zu B of activations", total); }
     cudaMemset(d->slab, 0, total);
@@ -99,7 +115,7 @@ static int dec_alloc(jllm_b200_decoder* d) {
     d->k = (__half*)take(KVD * 2); d->v = (__half*)take(KVD * 2);
     d->gate = (__half*)take(I * 2); d->up = (__half*)take(I * 2); d->sw = (__half*)take(I * 2);
     d->logits = (float*)take((size_t)m.vocab_size * 4);
-    d->state = (int*)take(64);
+    d->state = (int*)take(1024);        // [0..3] step state, [32..] argmax scratch
     d->out_cap = m.max_context + 8; d->out_tokens = (int*)take((size_t)d->out_cap * 4);
     d->prompt_cap = m.max_context + 8; d->prompt_dev = (int*)take((size_t)d->prompt_cap * 4);
     return JB_OK;
@@ -157,8 +173,9 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
     }
     DCHK(launch_rmsnorm(d->normed, d->x, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
     DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, m.vocab_size, H, st));
-    JB_CUDA(launch_k(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, pdl_enabled(), (const float*)d->logits, m.vocab_size, d->state,
-                     d->out_tokens, d->out_cap));
+    const int ag = m.vocab_size >= 64 * 1024 ? 64 : (m.vocab_size + 1023) / 1024;
+    JB_CUDA(launch_k(argmax_advance_kernel, dim3(ag), dim3(1024), 0, st, pdl_enabled(), (const float*)d->logits, m.vocab_size, d->state,
+                     d->out_tokens, d->out_cap, (unsigned int*)(d->state + 32)));
     count_launch();
     d->kernels_per_step = (int)(jllm_b200_launch_count() - l0);
     return JB_OK;
