@@ -64,7 +64,7 @@ struct MappedRegion { const char* host; const char* dev; int64_t bytes; };
 static MappedRegion g_region = { nullptr, nullptr, 0 };
 static const void* g_ok_cache[64];
 
-static const void* resolve_weight(const void* W) {
+const void* resolve_weight(const void* W) {
     if (!W) return nullptr;
     if (g_region.host && g_region.dev) {
         const char* p = (const char*)W;
@@ -106,7 +106,7 @@ static int gemv_one(void* y, const void* W, int type, const __half* x, const __h
     return rc;
 }
 
-static bool triple_dp4a(int a, int b, int c) {          // gemv_q4.cu:1474-1489
+bool triple_dp4a(int a, int b, int c) {          // gemv_q4.cu:1474-1489
     return (a == 12 && b == 12 && c == 14) || (a == 12 && b == 12 && c == 12) || (a == 14 && b == 14 && c == 14) || (a == 14 && b == 12 && c == 12);
 }
 

@@ -79,10 +79,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `limit` polls (each poll may itself block for a
 // hardware-defined short interval) and reports false; callers set the status word
 // and return instead of spinning forever.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
+// Bounded in polls AND in time (2 s): a poll may itself block for a hardware-defined interval, so a poll count alone
+// does not bound the wait.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 4) __nanosleep(40);          // back off: waiting warps must not crowd the issue slots of working ones
+        if ((i & 63) == 63) {
+            const unsigned long long t = global_ns();
+            if (!t0) t0 = t; else if (t - t0 > 2000000000ull) return false;
+        }
     }
     return false;
 }

@@ -11,6 +11,7 @@
 #include "attention.cuh"
 #include "tp.cuh"
 #include <cfloat>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -80,7 +81,7 @@ struct jllm_b200_decoder {
     jllm_b200_model_desc m;
     std::vector<jllm_b200_layer_desc> layers;
     jllm::KVCachePool kv;
-    bool fused = true, use_graph = false;
+    bool fused = true, use_graph = false, chain = false;
     __half *x = nullptr, *x2 = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *gate = nullptr, *up = nullptr, *sw = nullptr;
     float* logits = nullptr;
     int* state = nullptr;       // [pos, token, n_out]
@@ -134,6 +135,45 @@ static int dec_enqueue_step(jllm_b200_decoder* d, int n_splits, cudaStream_t st)
     const float scale = 1.0f / sqrtf((float)m.head_dim);
     const long long l0 = jllm_b200_launch_count();
     DCHK(launch_embed_row(d->x, m.tok_embd, m.embd_type, 0, d_tok, H, st));
+    if (d->fused && d->chain) {
+        // Q/K/V of layer 0 alone, then per layer: QKV prep, attention, and ONE chained launch for Wo + residual ->
+        // norm + gate/up + SwiGLU -> W_down + residual -> norm + Q/K/V of the next layer
+        auto triple_args = [&](int l) {
+            const jllm_b200_layer_desc& w = d->layers[l];
+            GemvArgs a;
+            a.nseg = 3;
+            a.seg[0] = GemvSeg{ resolve_weight(w.wq), d->q, QD, w.type_wq };
+            a.seg[1] = GemvSeg{ resolve_weight(w.wk), d->k, KVD, w.type_wk };
+            a.seg[2] = GemvSeg{ resolve_weight(w.wv), d->v, KVD, w.type_wv };
+            a.x = d->x; a.K = H; a.xmode = triple_dp4a(w.type_wq, w.type_wk, w.type_wv) ? 0 : 1; a.out_mode = 0;
+            a.do_norm = 1; a.norm_w = w.rms_attn; a.norm_w_fp32 = 1; a.eps = m.rms_eps;
+            return a;
+        };
+        { const GemvArgs a0 = triple_args(0); DCHK(launch_gemv(a0, st)); }
+        for (int l = 0; l < m.n_layers; ++l) {
+            const jllm_b200_layer_desc& w = d->layers[l];
+            int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
+            float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
+            DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, m.n_heads, m.n_kv_heads, m.head_dim,
+                                 0, d_pos, m.rope_theta, m.rope_neox != 0, true, st));
+            AttnCall c;
+            c.out = d->att; c.q = d->q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads;
+            c.hd = m.head_dim; c.chd = m.head_dim; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
+            DCHK(launch_attention(c, st));
+            GemvArgs ph[4];
+            int n = 0;
+            ph[n].nseg = 1; ph[n].seg[0] = GemvSeg{ resolve_weight(w.wo), d->x2, H, w.type_wo };
+            ph[n].x = d->att; ph[n].K = QD; ph[n].xmode = 1; ph[n].out_mode = 2; ph[n].residual = d->x; ++n;
+            ph[n].nseg = 2; ph[n].seg[0] = GemvSeg{ resolve_weight(w.w_gate), d->sw, I, w.type_w_gate };
+            ph[n].seg[1] = GemvSeg{ resolve_weight(w.w_up), d->sw, I, w.type_w_up };
+            ph[n].x = d->x2; ph[n].K = H; ph[n].xmode = (w.type_w_gate == T_Q4K && w.type_w_up == T_Q4K) ? 0 : 1; ph[n].out_mode = 3;
+            ph[n].do_norm = 1; ph[n].norm_w = w.rms_ffn; ph[n].norm_w_fp32 = 1; ph[n].eps = m.rms_eps; ++n;
+            ph[n].nseg = 1; ph[n].seg[0] = GemvSeg{ resolve_weight(w.w_down), d->x, H, w.type_w_down };
+            ph[n].x = d->sw; ph[n].K = I; ph[n].xmode = 1; ph[n].out_mode = 2; ph[n].residual = d->x2; ++n;
+            if (l + 1 < m.n_layers) ph[n++] = triple_args(l + 1);
+            DCHK(launch_gemv_chain(ph, n, (unsigned int*)(d->state + 200), st));
+        }
+    } else
     for (int l = 0; l < m.n_layers; ++l) {
         const jllm_b200_layer_desc& w = d->layers[l];
         int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
@@ -212,11 +252,24 @@ static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t 
         const jllm_b200_layer_desc& w = d->layers[l];
         int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
         float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
-        if (l > 0) { const GemvTpWait wh = wait_hook(l - 1); gemv_set_tp_hooks(&wh, nullptr); }
-        int rc = jllm_b200_norm_gemv_quant_triple(d->q, w.wq, w.type_wq, QD_l, d->k, w.wk, w.type_wk, KVD_l, d->v, w.wv, w.type_wv, KVD_l,
-                                                  l > 0 ? x_pk : d->normed, w.rms_attn, 1, m.rms_eps, H, st);
-        gemv_set_tp_hooks(nullptr, nullptr);
-        DCHK(rc);
+        auto triple_args = [&](int ll, const GemvTpWait* wh) {
+            const jllm_b200_layer_desc& ww = d->layers[ll];
+            GemvArgs a;
+            a.nseg = 3;
+            a.seg[0] = GemvSeg{ resolve_weight(ww.wq), d->q, QD_l, ww.type_wq };
+            a.seg[1] = GemvSeg{ resolve_weight(ww.wk), d->k, KVD_l, ww.type_wk };
+            a.seg[2] = GemvSeg{ resolve_weight(ww.wv), d->v, KVD_l, ww.type_wv };
+            a.x = ll > 0 ? x_pk : d->normed; a.K = H; a.xmode = triple_dp4a(ww.type_wq, ww.type_wk, ww.type_wv) ? 0 : 1; a.out_mode = 0;
+            a.do_norm = 1; a.norm_w = ww.rms_attn; a.norm_w_fp32 = 1; a.eps = m.rms_eps;
+            a.tp_wait = ll > 0 ? wh : nullptr;
+            return a;
+        };
+        int rc = 0;
+        if (l == 0 || !d->chain) {
+            const GemvTpWait wh = wait_hook(l - 1);
+            const GemvArgs a0 = triple_args(l, &wh);
+            DCHK(launch_gemv(a0, st));
+        }
         DCHK(launch_qkv_prep(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, d->nh_l, d->nkv_l, hd,
                              0, d_pos, m.rope_theta, m.rope_neox != 0, true, st));
         AttnCall c;
@@ -224,6 +277,27 @@ static int dec_enqueue_step_tp(jllm_b200_decoder* d, int n_splits, cudaStream_t 
         c.hd = hd; c.chd = hd; c.d_pos = d_pos; c.scale = scale; c.kv_int8 = 1; c.n_splits = n_splits; c.max_seq = m.max_context;
         DCHK(launch_attention(c, st));
         DCHK(launch_tp_push(d->tp, d->att, QD_l, d->tp_off[0], rank * QD_l, l, st));
+        if (d->chain) {
+            // Wo -> gate/up -> W_down -> next layer's Q/K/V in one launch; no grid barrier: every input of a later phase
+            // (activation vector and residual rows) is read as packets, which carry their own arrival mark
+            const GemvTpWait wh = wait_hook(l);
+            const GemvTpPush p_x2 = push_hook(TP_POINT_X2, l, d->H_l), p_sw = push_hook(TP_POINT_SW, l, d->I_l), p_x = push_hook(TP_POINT_X, l, d->H_l);
+            GemvArgs ph[4];
+            int n = 0;
+            ph[n].nseg = 1; ph[n].seg[0] = GemvSeg{ resolve_weight(w.wo), d->x2, d->H_l, w.type_wo };
+            ph[n].x = att_pk; ph[n].K = QD; ph[n].xmode = 1; ph[n].out_mode = 2;
+            ph[n].residual = l > 0 ? d->x : d->normed + (size_t)rank * d->H_l; ph[n].tp_wait = &wh; ph[n].tp_push = &p_x2; ++n;
+            ph[n].nseg = 2; ph[n].seg[0] = GemvSeg{ resolve_weight(w.w_gate), d->sw, d->I_l, w.type_w_gate };
+            ph[n].seg[1] = GemvSeg{ resolve_weight(w.w_up), d->sw, d->I_l, w.type_w_up };
+            ph[n].x = x2_pk; ph[n].K = H; ph[n].xmode = (w.type_w_gate == T_Q4K && w.type_w_up == T_Q4K) ? 0 : 1; ph[n].out_mode = 3;
+            ph[n].do_norm = 1; ph[n].norm_w = w.rms_ffn; ph[n].norm_w_fp32 = 1; ph[n].eps = m.rms_eps; ph[n].tp_wait = &wh; ph[n].tp_push = &p_sw; ++n;
+            ph[n].nseg = 1; ph[n].seg[0] = GemvSeg{ resolve_weight(w.w_down), d->x, d->H_l, w.type_w_down };
+            ph[n].x = sw_pk; ph[n].K = I; ph[n].xmode = 1; ph[n].out_mode = 2;
+            ph[n].residual_pk = reinterpret_cast<const uint2*>(x2_pk) + (size_t)rank * d->H_l; ph[n].tp_wait = &wh; ph[n].tp_push = &p_x; ++n;
+            if (l + 1 < m.n_layers) ph[n++] = triple_args(l + 1, &wh);
+            DCHK(launch_gemv_chain(ph, n, nullptr, st));
+            continue;
+        }
         {
             const GemvTpWait wh = wait_hook(l); const GemvTpPush ph = push_hook(TP_POINT_X2, l, d->H_l);
             gemv_set_tp_hooks(&wh, &ph);
@@ -287,7 +361,7 @@ jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, i
     d->m = *model;
     d->layers.assign(model->layers, model->layers + model->n_layers);
     d->m.layers = d->layers.data();
-    d->fused = (flags & 1) != 0; d->use_graph = (flags & 2) != 0;
+    d->fused = (flags & 1) != 0; d->use_graph = (flags & 2) != 0; d->chain = (flags & 8) != 0;
     jllm::KVCachePool::Config c = { model->n_layers, model->n_kv_heads, model->head_dim, model->max_context, 0, 1 };
     if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); delete d; return nullptr; }
     if (dec_alloc(d)) { d->kv.destroy(); delete d; return nullptr; }
@@ -313,7 +387,7 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
     d->m = *model;
     d->layers.assign(model->layers, model->layers + model->n_layers);
     d->m.layers = d->layers.data();
-    d->fused = true; d->use_graph = (flags & 2) != 0;
+    d->fused = true; d->use_graph = (flags & 2) != 0; d->chain = (flags & 8) != 0;
     d->tp_on = true;
     d->nh_l = model->n_heads / world; d->nkv_l = model->n_kv_heads / world; d->I_l = model->intermediate_dim / world;
     d->H_l = model->hidden_dim / world; d->V_l = model->vocab_size / world;

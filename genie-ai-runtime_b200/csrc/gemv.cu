@@ -37,12 +37,15 @@ struct GvParams {
     GvSegDev seg[3]; int nseg;
     const __half* x; int K;
     int out_mode; const __half* residual;
+    const uint2* residual_pk;   // residual as packets of this rank's own region (tensor-parallel chain), else null
     int do_norm; const void* norm_w; int norm_w_fp32; float eps;
     int32_t* dbg_dots; int* status;
     int slot_bytes, nslots, needA, needB, paired_rows, nwarps;
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
     long long total_bytes;      // Σ over segments of (row groups x bytes per group)
     int tp_wait_on, tp_push_on;
+    int xmode;                  // 0 q8_1 activations, 1 16-bit activations
+    int chained;                // phase of a chain kernel: activations may have been written by other SMs in this launch
     GemvTpWait tpw;
     GemvTpPush tpp;
 };
@@ -65,7 +68,8 @@ void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
 // the other ranks, 64 bytes of packets polled (bounded) until every epoch word matches; the packets are read past L1.
 __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epoch, float (&v)[8]) {
     if (!p.tp_wait_on) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + 8 * it);
+        // inside a chain the vector was written earlier in this launch: read it past L1, which may hold older lines
+        const uint4 raw = p.chained ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
         const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
         #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -93,7 +97,7 @@ __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epo
 
 template <int XM>
 __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = p.nwarps * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nw_cta = blockDim.x >> 5;
     const int K = p.K;
     const uint32_t epoch = p.tp_wait_on ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
     float rrms = 1.0f;
@@ -109,7 +113,7 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         if (lane == 0) red[warp] = ss;
         __syncthreads();
         float tot = 0.f;
-        for (int w = 0; w < p.nwarps; ++w) tot += red[w];
+        for (int w = 0; w < nw_cta; ++w) tot += red[w];
         rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
     }
     uint8_t* xA = smem + p.off_xA; uint8_t* xB = smem + p.off_xB;
@@ -388,55 +392,31 @@ __device__ __forceinline__ void gv_issue(const GvParams& p, int seg, int row0, i
     bulk_g2s(slot, (const void*)a0, bytes, bar);
 }
 
-template <int XM, bool DBG>
-__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __grid_constant__ GvParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
-    __shared__ float red[GV_MAXWARPS];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    // this CTA's row groups in every segment: an even split of all groups by bytes
-    GvRange rg;
-    {
-        const long long G = gridDim.x, b = blockIdx.x;
-        if (p.paired_rows) {      // out_mode 3: the same groups of both matrices
-            const int R = p.seg[0].R, groups = (p.seg[0].M + R - 1) / R;
-            rg.gf[0] = rg.gf[1] = (int)((long long)groups * b / G);
-            rg.gl[0] = rg.gl[1] = (int)((long long)groups * (b + 1) / G);
-            rg.gf[2] = rg.gl[2] = 0;
-        } else {
-            const long long lo = p.total_bytes * b / G, hi = p.total_bytes * (b + 1) / G;
-            long long cum = 0;
-            #pragma unroll
-            for (int i = 0; i < 3; ++i) {
-                rg.gf[i] = rg.gl[i] = 0;
-                if (i < p.nseg) {
-                    const long long R = p.seg[i].R, gb = R * p.seg[i].rb, groups = (p.seg[i].M + R - 1) / R;
-                    long long f = lo - cum <= 0 ? 0 : (lo - cum + gb - 1) / gb;
-                    long long l = hi - cum <= 0 ? 0 : (hi - cum + gb - 1) / gb;
-                    rg.gf[i] = (int)(f > groups ? groups : f); rg.gl[i] = (int)(l > groups ? groups : l);
-                    cum += gb * groups;
-                }
-            }
-        }
-    }
+// first tasks of a phase: start the bulk copies of this warp's first row groups.  The slot barriers are created once
+// per kernel and live through all phases of a chain; `later` = not the first phase of the launch.
+__device__ __forceinline__ void gv_prefetch(const GvParams& p, const GvRange& rg, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], int warp, int lane, bool later) {
+    if (warp >= p.nwarps) return;
     uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
     if (lane == 0) {
-        for (int s = 0; s < p.nslots; ++s) mbar_init(&full[warp][s], 1);
-        fence_mbar_init();
-    }
-    __syncwarp();
-    if (lane == 0) {              // weights do not depend on the previous kernel: start fetching at once
+        if (later) fence_proxy_async();       // the slots were read with ordinary loads in the phase before
         for (int u = 0; u < p.nslots; ++u) {
             int seg, row0, nrows;
             if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
             gv_issue(p, seg, row0, nrows, ring + (unsigned)u * (unsigned)p.slot_bytes, &full[warp][u]);
         }
     }
-    pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
-    pdl_wait();                  // x (and the residual) come from the kernel before us
+    __syncwarp();
+}
+
+// one GEMV launch, or one phase of a chain (then the caller has prefetched and synchronised the grid)
+template <int XM, bool DBG>
+__device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], float* red, const GvRange& rg, uint32_t& par) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
     stage_x<XM>(p, smem, red);
     __syncthreads();
+    if (warp >= p.nwarps) return;            // chain phases may use fewer warps than the CTA has (larger staging rings)
 
     const uint32_t sm0 = smem_u32(smem);
     const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K };
@@ -447,8 +427,10 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
         int seg, row0, nrows;
         if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
         const int slot = u % p.nslots;
-        // a wait that runs out is recorded and the loop carries on; later waits are skipped
-        if (!timed_out && !mbar_wait_bounded(&full[warp][slot], (u / p.nslots) & 1)) timed_out = true;
+        // a wait that runs out is recorded and the loop carries on; later waits are skipped.  `par` holds, per slot
+        // barrier, the parity of the phase its next copy completes (barriers live across the phases of a chain).
+        if (!timed_out && !mbar_wait_bounded(&full[warp][slot], (par >> slot) & 1u)) timed_out = true;
+        par ^= 1u << slot;
         const GvSegDev& s = p.seg[seg];
         const uintptr_t g0 = (uintptr_t)s.W + (size_t)row0 * s.rb;
         uint8_t* rows = ring + (unsigned)slot * (unsigned)p.slot_bytes + (unsigned)(g0 & 15);
@@ -488,7 +470,20 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
             else if (p.out_mode == 1) reinterpret_cast<float*>(s.y)[row] = mine;
             else if (p.out_mode == 2) {   // src/kernels/gemv_q4.cu:996-999
                 const __half pr = __float2half_rn(mine);
-                reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), __half2float(p.residual[row])));
+                float res;
+                if (p.residual_pk) {          // written earlier in this launch by another CTA of this rank: valid once its epoch matches
+                    uint2 q;
+                    for (uint32_t tries = 0;; ++tries) {
+                        q = __ldcv(p.residual_pk + row);
+                        if (q.y == push_epoch) break;
+                        if (tries > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
+                        __nanosleep(20);
+                    }
+                    res = __half2float(__ushort_as_half((unsigned short)(q.x & 0xFFFFu)));
+                } else {
+                    res = __half2float(p.chained ? __ldcg(p.residual + row) : p.residual[row]);
+                }
+                reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), res));
             } else {                      // fused SwiGLU of the gate/up pair (src/kernels/convert.cu:85-104)
                 const float hv = __half2float(__float2half_rn(mine));
                 const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
@@ -504,6 +499,113 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
         }
     }
     if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
+}
+
+
+// this CTA's row groups in every segment: an even split of all groups by bytes
+__device__ __forceinline__ GvRange gv_range(const GvParams& p) {
+    GvRange rg;
+    const long long G = gridDim.x, b = blockIdx.x;
+    if (p.paired_rows) {      // out_mode 3: the same groups of both matrices
+        const int R = p.seg[0].R, groups = (p.seg[0].M + R - 1) / R;
+        rg.gf[0] = rg.gf[1] = (int)((long long)groups * b / G);
+        rg.gl[0] = rg.gl[1] = (int)((long long)groups * (b + 1) / G);
+        rg.gf[2] = rg.gl[2] = 0;
+    } else {
+        const long long lo = p.total_bytes * b / G, hi = p.total_bytes * (b + 1) / G;
+        long long cum = 0;
+        #pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            rg.gf[i] = rg.gl[i] = 0;
+            if (i < p.nseg) {
+                const long long R = p.seg[i].R, gb = R * p.seg[i].rb, groups = (p.seg[i].M + R - 1) / R;
+                long long f = lo - cum <= 0 ? 0 : (lo - cum + gb - 1) / gb;
+                long long l = hi - cum <= 0 ? 0 : (hi - cum + gb - 1) / gb;
+                rg.gf[i] = (int)(f > groups ? groups : f); rg.gl[i] = (int)(l > groups ? groups : l);
+                cum += gb * groups;
+            }
+        }
+    }
+    return rg;
+}
+
+template <int XM, bool DBG>
+__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
+    __shared__ float red[GV_MAXWARPS];
+    const GvRange rg = gv_range(p);
+    if ((threadIdx.x & 31) == 0) {
+        for (int s = 0; s < p.nslots; ++s) mbar_init(&full[threadIdx.x >> 5][s], 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    gv_prefetch(p, rg, smem, full, threadIdx.x >> 5, threadIdx.x & 31, false);   // weights do not depend on the previous kernel
+    pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
+    pdl_wait();                  // x (and the residual) come from the kernel before us
+    uint32_t par = 0;
+    gv_phase<XM, DBG>(p, smem, full, red, rg, par);
+}
+
+// ── chain: up to four GEMVs that feed one another (Wo -> gate/up -> W_down -> next layer's Q/K/V) in ONE launch ──
+// One persistent CTA per SM runs the phases in order with a grid-wide barrier between them.  Against separate
+// launches this removes the kernel boundary (drain, launch, first bulk-copy round trip) three times per layer: the
+// first weight copies of the next phase are issued before the CTA enters the barrier, so they fly while it waits.
+// The barrier is a ticket counter plus a generation word in global memory; the wait is bounded and a timeout is
+// recorded in the status word (the phase then runs on whatever has arrived).  All CTAs must be resident at the same
+// time: the grid never exceeds the number of SMs and a CTA takes a whole SM.
+struct GvChain { int n; unsigned int* bar; GvParams ph[4]; };
+
+__device__ __forceinline__ void gv_grid_barrier(unsigned int* bar, int* status) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int gen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(bar + 1) : "memory");
+        const unsigned int ticket = atomicAdd(bar, 1u);
+        if (ticket == gridDim.x - 1) {
+            *bar = 0u;
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen + 1u) : "memory");
+        } else {
+            unsigned int g, i = 0;
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(bar + 1) : "memory");
+                if (g != gen) break;
+                if (++i > (1u << 22)) { atomicExch(status, JB_ERR_TIMEOUT); break; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_chain_kernel(const __grid_constant__ GvChain c) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
+    __shared__ float red[GV_MAXWARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {                          // slot barriers of every warp, for all phases
+        for (int s = 0; s < GV_MAXSLOT; ++s) mbar_init(&full[warp][s], 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    uint32_t par = 0;                         // per slot barrier: parity of the phase its next copy completes
+    GvRange rg = gv_range(c.ph[0]);
+    gv_prefetch(c.ph[0], rg, smem, full, warp, lane, false);
+    pdl_launch();
+    pdl_wait();
+    for (int i = 0; i < c.n; ++i) {
+        const GvParams& p = c.ph[i];
+        if (i > 0) {
+            __syncthreads();                  // every warp of this CTA is done with the rings of the phase before
+            rg = gv_range(p);
+            gv_prefetch(p, rg, smem, full, warp, lane, true);
+            if (c.bar) gv_grid_barrier(c.bar, p.status); // ... and every CTA with its rows: the next activation vector is complete
+            // (no barrier when every input of the phase arrives as packets: each element carries its own arrival mark)
+        }
+        if (p.xmode) gv_phase<1, false>(p, smem, full, red, rg, par);
+        else         gv_phase<0, false>(p, smem, full, red, rg, par);
+    }
 }
 
 // ── Q5_K (and nothing else): plain warp-per-row kernel with the reference's float
@@ -550,21 +652,22 @@ int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const
 // rows per warp pass: the count of 32-byte items of a row group should fill whole warps
 static double lane_eff(int R, int U) { const int items = R * U, iters = (items + 31) / 32; return (double)items / (32.0 * iters); }
 
-int launch_gemv(const GemvArgs& a, cudaStream_t st) {
-    if (a.nseg < 1 || a.nseg > 3) return set_error(JB_ERR_ARG, "gemv: nseg=%d", a.nseg);
-    if (a.K <= 0 || a.K % QK_K) return set_error(JB_ERR_ARG, "gemv: K=%d is not a positive multiple of 256", a.K);
-    if (a.K > 32768) return set_error(JB_ERR_LIMIT, "gemv: K=%d exceeds the supported 32768", a.K);
-    if (!a.x) return set_error(JB_ERR_PTR, "gemv: null activation pointer");
+// Fills the device-side argument block for one GEMV.  max_warps caps the warps per CTA (a chain runs all its phases
+// with one block size); on return smem_bytes / grid hold what this GEMV wants.
+static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& smem_bytes, int& grid, bool& empty) {
     DeviceCtx* cx = ctx();
     if (!cx) return JB_ERR_CUDA;
-    GvParams p = {};
-    p.nseg = a.nseg; p.x = a.x; p.K = a.K; p.out_mode = a.out_mode; p.residual = a.residual;
+    empty = false;
+    if (a.nseg < 1 || a.nseg > 3) return set_error(JB_ERR_ARG, "gemv: %d matrices", a.nseg);
+    if (a.K <= 0 || a.K % QK_K) return set_error(JB_ERR_ARG, "gemv: K=%d is not a positive multiple of 256", a.K);
+    if (!a.x) return set_error(JB_ERR_PTR, "gemv: null activation pointer");
+    p = GvParams{};
+    p.nseg = a.nseg; p.x = a.x; p.K = a.K; p.out_mode = a.out_mode; p.residual = a.residual; p.residual_pk = (const uint2*)a.residual_pk;
     p.do_norm = a.do_norm; p.norm_w = a.norm_w; p.norm_w_fp32 = a.norm_w_fp32; p.eps = a.eps;
-    p.dbg_dots = a.dbg_dots; p.status = cx->d_status;
-    p.tp_wait_on = g_tp_wait_set; p.tp_push_on = g_tp_push_set;
-    if (g_tp_wait_set) p.tpw = g_tp_wait;
-    if (g_tp_push_set) p.tpp = g_tp_push;
-    g_tp_wait_set = g_tp_push_set = false;
+    p.dbg_dots = a.dbg_dots; p.status = cx->d_status; p.xmode = a.xmode ? 1 : 0;
+    p.tp_wait_on = a.tp_wait != nullptr; p.tp_push_on = a.tp_push != nullptr;
+    if (a.tp_wait) p.tpw = *a.tp_wait;
+    if (a.tp_push) p.tpp = *a.tp_push;
     if (p.tp_push_on && (a.out_mode == 1 || a.nseg > 2 || (a.nseg == 2 && a.out_mode != 3)))
         return set_error(JB_ERR_ARG, "gemv: a pushed result must be one fp16 vector");
     const int nb = a.K / QK_K;
@@ -579,8 +682,9 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         if (s.type == T_Q4K) p.needA = 1; else p.needB = 1;
         total_rows += s.M;
     }
-    if (total_rows == 0) return JB_OK;
-    if (a.out_mode == 2 && (a.nseg != 1 || !a.residual)) return set_error(JB_ERR_ARG, "gemv: residual epilogue needs one matrix and a residual");
+    if (total_rows == 0) { empty = true; return JB_OK; }
+    if (a.residual_pk && !a.tp_push) return set_error(JB_ERR_ARG, "gemv: a packet residual needs the push epoch");
+    if (a.out_mode == 2 && (a.nseg != 1 || (!a.residual && !a.residual_pk))) return set_error(JB_ERR_ARG, "gemv: residual epilogue needs one matrix and a residual");
     if (a.out_mode == 3 && (a.nseg != 2 || a.seg[0].M != a.seg[1].M || a.seg[0].type != a.seg[1].type))
         return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height and type");
     p.paired_rows = a.out_mode == 3;
@@ -588,7 +692,7 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
     // One CTA per SM with 16, 8 or 4 warps: the activation vector is staged once per SM by all the CTA's threads, and
     // what is left of the shared memory is split into one staging ring per warp; fewer warps mean larger rings.
     const int budget = cx->max_smem_optin - 2048;             // opt-in limit minus this kernel's static shared memory
-    for (int nwarps = GV_MAXWARPS; nwarps >= 4; nwarps >>= 1) {
+    for (int nwarps = max_warps; nwarps >= 4; nwarps >>= 1) {
         uint32_t off = 0;
         p.off_xA = off; off += p.needA ? planes * K : 0;
         p.off_xB = off; off += p.needB ? planes * K : 0;
@@ -637,24 +741,70 @@ int launch_gemv(const GemvArgs& a, cudaStream_t st) {
         p.nslots = ring / slot;
         if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
         p.nwarps = nwarps;
-        const size_t smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
+        smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
-        int grid = cx->sm_count;
+        grid = cx->sm_count;
         const long long ctas_useful = (groups_total + nwarps - 1) / nwarps;
         if (grid > ctas_useful) grid = (int)ctas_useful;
         if (grid < 1) grid = 1;
-        auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
-                               : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
-        const int ki = (a.xmode ? 1 : 0) + (a.dbg_dots ? 2 : 0);
-        if (!cx->gemv_attr[ki]) {
-            JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
-            cx->gemv_attr[ki] = true;
-        }
-        JB_CUDA(launch_k(kern, dim3(grid), dim3(nwarps * 32), smem_bytes, st, pdl_enabled(), p));
-        count_launch();
         return JB_OK;
     }
     return set_error(JB_ERR_LIMIT, "gemv: no launch configuration fits (K=%d)", K);
+}
+
+int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
+    DeviceCtx* cx = ctx();
+    if (!cx) return JB_ERR_CUDA;
+    GemvArgs a = a0;
+    if (g_tp_wait_set && !a.tp_wait) a.tp_wait = &g_tp_wait;
+    if (g_tp_push_set && !a.tp_push) a.tp_push = &g_tp_push;
+    g_tp_wait_set = g_tp_push_set = false;
+    GvParams p;
+    size_t smem_bytes = 0; int grid = 0; bool empty = false;
+    const int rc = gv_configure(a, p, GV_MAXWARPS, smem_bytes, grid, empty);
+    if (rc || empty) return rc;
+    auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
+                           : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
+    const int ki = (a.xmode ? 1 : 0) + (a.dbg_dots ? 2 : 0);
+    if (!cx->gemv_attr[ki]) {
+        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 2048));
+        cx->gemv_attr[ki] = true;
+    }
+    JB_CUDA(launch_k(kern, dim3(grid), dim3(p.nwarps * 32), smem_bytes, st, pdl_enabled(), p));
+    count_launch();
+    return JB_OK;
+}
+
+// Up to four GEMVs, each reading what the one before wrote, in one launch (gemv_chain_kernel).  `bar` = two zeroed
+// device words owned by the caller and used by one chain at a time.
+int launch_gemv_chain(const GemvArgs* args, int n, unsigned int* bar, cudaStream_t st) {
+    DeviceCtx* cx = ctx();
+    if (!cx) return JB_ERR_CUDA;
+    if (n < 1 || n > 4) return set_error(JB_ERR_ARG, "gemv chain: %d phases", n);
+    for (int i = 1; i < n && !bar; ++i)
+        if (!args[i].tp_wait || (args[i].out_mode == 2 && !args[i].residual_pk))
+            return set_error(JB_ERR_ARG, "gemv chain: without a grid barrier every input of a later phase must arrive as packets");
+    static GvChain c;                     // 1 KB of parameters: built in place
+    c.n = n; c.bar = bar;
+    size_t smem_max = 0;
+    for (int i = 0; i < n; ++i) {
+        if (args[i].dbg_dots) return set_error(JB_ERR_ARG, "gemv chain: no debug output");
+        size_t smem_bytes = 0; int grid = 0; bool empty = false;
+        const int rc = gv_configure(args[i], c.ph[i], GV_MAXWARPS, smem_bytes, grid, empty);
+        if (rc) return rc;
+        if (empty) return set_error(JB_ERR_ARG, "gemv chain: empty phase");
+        c.ph[i].chained = 1;
+        smem_max = smem_bytes > smem_max ? smem_bytes : smem_max;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        JB_CUDA(cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 2048));
+        attr_done = true;
+    }
+    // every phase splits its rows over the same grid: one CTA per SM, all resident together
+    JB_CUDA(launch_k(gemv_chain_kernel, dim3(cx->sm_count), dim3(GV_MAXTHREADS), smem_max, st, pdl_enabled(), c));
+    count_launch();
+    return JB_OK;
 }
 
 }  // namespace jb

@@ -20,10 +20,13 @@ struct GemvArgs {
     int xmode = 0;
     int out_mode = 0;                 // 0 half, 1 float, 2 half(half(acc)+residual), 3 silu(seg0)*seg1 -> seg0.y
     const __half* residual = nullptr; // out_mode 2
+    const void* residual_pk = nullptr; // out_mode 2, tensor-parallel chain: the residual rows as packets in this rank's own region
     // optional fused input RMSNorm: x := half((x [+ norm_res]) * rrms * w) before quantising
     int do_norm = 0;
     const void* norm_w = nullptr; int norm_w_fp32 = 1; float eps = 0.f;
     int32_t* dbg_dots = nullptr;      // optional: integer accumulators of seg 0
+    const struct GemvTpWait* tp_wait = nullptr;   // tensor-parallel hooks (see below); null on one GPU
+    const struct GemvTpPush* tp_push = nullptr;
 };
 
 // Tensor-parallel hooks of one launch (csrc/tp.cu describes the exchange).  Exchanged vectors travel as 8-byte
@@ -40,7 +43,14 @@ struct GemvTpPush { unsigned char* peer[8]; int world; int buf_off; int row_off;
 // The next launch_gemv on this thread takes the hooks (either may be null) and forgets them.
 void gemv_set_tp_hooks(const GemvTpWait* wait, const GemvTpPush* push);
 
+// dispatch helpers shared with the decoder's chained launches (csrc/api.cu)
+const void* resolve_weight(const void* W);          // device pointer of a weight tensor (registered host ranges are mapped)
+bool triple_dp4a(int t0, int t1, int t2);            // type mixes the reference runs on its q8_1 + dp4a path
+
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
+// n <= 4 GEMVs that feed one another, in one launch with grid-wide barriers between them; bar: two zeroed device words,
+// or null when every later phase takes all its inputs as packets (tensor-parallel): packets carry their own arrival mark
+int launch_gemv_chain(const GemvArgs* args, int n, unsigned int* bar, cudaStream_t st);
 int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const __half* residual,
                     int M, int K, cudaStream_t st);
 

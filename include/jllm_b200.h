@@ -210,7 +210,9 @@ typedef struct {
 } jllm_b200_model_desc;
 typedef struct jllm_b200_decoder jllm_b200_decoder;
 /* flags: bit 0 = fused kernels (norm+GEMV, SwiGLU epilogue, one QKV-prep launch) instead of the reference's
- * launch-for-launch sequence (both give identical bits); bit 1 = replay a captured CUDA graph per step. */
+ * launch-for-launch sequence (both give identical bits); bit 1 = replay a captured CUDA graph per step;
+ * bit 3 = with bit 0, run Wo / gate-up / W_down / next Q-K-V as ONE chained launch with grid-wide barriers instead of
+ * four launches (same bits; measured slower on B200, where dependent launches overlap per SM, so it is off by default). */
 jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, int flags);
 void   jllm_b200_decoder_destroy(jllm_b200_decoder* d);
 int    jllm_b200_decoder_reset(jllm_b200_decoder* d);

@@ -37,11 +37,14 @@ def test_greedy_stream_matches_oracle(small_model):
     want = od.generate(prompt, n_new)
     assert np.all(np.isfinite(od.logits)) and len(set(want)) > 1      # a live model, not an overflowed one
     streams = {}
-    for flags in (0, jb.decoder.FUSED, jb.decoder.FUSED | jb.decoder.GRAPH):
+    CHAIN = 8         # fused kernels with the four GEMVs between two attentions in one chained launch
+    for flags in (0, jb.decoder.FUSED, jb.decoder.FUSED | jb.decoder.GRAPH, jb.decoder.FUSED | CHAIN, jb.decoder.FUSED | jb.decoder.GRAPH | CHAIN):
         d = jb.decoder.Decoder(m["cfg"], w, ctx, flags)
         streams[flags] = list(d.generate(prompt, n_new))
+        streams[(flags, 2)] = list(d.generate(prompt, n_new))       # again through the same session (barrier words, KV reset)
         d.close()
-    assert streams[0] == streams[1] == streams[3], "fused / graph paths changed the stream"
+        assert jb.device_status() == 0
+    assert all(v == streams[0] for v in streams.values()), "fused / chained / graph paths changed the stream"
     got = streams[3]
     if got != want:
         s = next(i for i in range(n_new) if got[i] != want[i])
@@ -65,13 +68,16 @@ def test_logits_match_oracle_and_fused_equals_unfused(small_model):
     o = orc.Decoder(m, ctx)
     a = jb.decoder.Decoder(m["cfg"], w, ctx, 0)
     b = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED)
+    c = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED | 8)
     toks = [5, 77, 1234, 2999, 0, 13]
     for pos, t in enumerate(toks):
         nt_o = o.step(t, pos)
         nt_a = a.step(t, pos)
         nt_b = b.step(t, pos)
+        c.step(t, pos)
         la, lb = a.logits(), b.logits()
         assert torch.equal(la, lb)                                    # same bits, fewer launches
+        assert torch.equal(la, c.logits())
         want = o.logits
         got = la.cpu().numpy()
         assert np.all(np.isfinite(want)) and np.all(np.isfinite(got))
@@ -81,8 +87,8 @@ def test_logits_match_oracle_and_fused_equals_unfused(small_model):
         assert nt_a == nt_b
         if nt_a != nt_o:                                              # only acceptable at a near tie of the two top logits
             assert abs(want[nt_a] - want[nt_o]) <= NOISE * rms
-    assert b.kernels_per_step() < a.kernels_per_step()
-    a.close(); b.close()
+    assert c.kernels_per_step() < b.kernels_per_step() < a.kernels_per_step()
+    a.close(); b.close(); c.close()
 
 
 def test_decoder_argument_errors(small_model):

@@ -100,7 +100,7 @@ def main():
         local = decmod.upload(tp.shard_model(model, world, rank))
         st = torch.cuda.Stream()
         res = {}
-        for name, flags in (("graph", 3), ("nograph", 1)):
+        for name, flags in (("graph", 3), ("nograph", 1), ("chain", 11)):
             d = tp.TPDecoder(model["cfg"], local, 64, rank, world, flags=flags)
             res[name] = d.generate(PROMPT, N_NEW, st)
             res[name + "2"] = d.generate(PROMPT, N_NEW, st)          # a second run through the same exchange regions
