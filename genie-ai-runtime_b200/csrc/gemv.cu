@@ -692,7 +692,8 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
     // One CTA per SM with 16, 8 or 4 warps: the activation vector is staged once per SM by all the CTA's threads, and
     // what is left of the shared memory is split into one staging ring per warp; fewer warps mean larger rings.
     const int budget = cx->max_smem_optin - 2048;             // opt-in limit minus this kernel's static shared memory
-    for (int nwarps = max_warps; nwarps >= 4; nwarps >>= 1) {
+    // 16, 12, 8, 6, 4 warps: the most that still leaves every warp a ring of two row groups
+    for (int nwarps = max_warps; nwarps >= 4; nwarps = (nwarps & (nwarps - 1)) ? (nwarps / 3) * 2 : (nwarps / 4) * 3) {
         uint32_t off = 0;
         p.off_xA = off; off += p.needA ? planes * K : 0;
         p.off_xB = off; off += p.needB ? planes * K : 0;
