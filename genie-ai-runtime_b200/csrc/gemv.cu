@@ -22,7 +22,7 @@
 
 namespace jb {
 
-constexpr int GV_MAXWARPS = 16;                // one CTA per SM; 16, 8 or 4 warps depending on how large a row group is
+constexpr int GV_MAXWARPS = 18;                // one CTA per SM; 4 to 18 warps, chosen per launch (gv_configure)
 constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
 
@@ -650,7 +650,6 @@ int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const
 }
 
 // rows per warp pass: the count of 32-byte items of a row group should fill whole warps
-static double lane_eff(int R, int U) { const int items = R * U, iters = (items + 31) / 32; return (double)items / (32.0 * iters); }
 
 // Fills the device-side argument block for one GEMV.  max_warps caps the warps per CTA (a chain runs all its phases
 // with one block size); on return smem_bytes / grid hold what this GEMV wants.
@@ -689,39 +688,43 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
         return set_error(JB_ERR_ARG, "gemv: SwiGLU epilogue needs two matrices of equal height and type");
     p.paired_rows = a.out_mode == 3;
     const int K = a.K, planes = a.xmode ? 2 : 1;
-    // One CTA per SM with 16, 8 or 4 warps: the activation vector is staged once per SM by all the CTA's threads, and
-    // what is left of the shared memory is split into one staging ring per warp; fewer warps mean larger rings.
+    // One CTA per SM.  The activation vector is staged once per SM by all the CTA's threads; what is left of the shared
+    // memory is split into one staging ring per warp.  Warps per CTA and rows per group are chosen together to
+    // minimise the longest chain of work any warp has to run: (row groups of its CTA / warps, rounded up) x
+    // (32-lane rounds a group takes, plus half a round of per-group overhead).  Ties go to more warps, larger groups.
     const int budget = cx->max_smem_optin - 2048;             // opt-in limit minus this kernel's static shared memory
-    // 16, 12, 8, 6, 4 warps: the most that still leaves every warp a ring of two row groups
-    for (int nwarps = max_warps; nwarps >= 4; nwarps = (nwarps & (nwarps - 1)) ? (nwarps / 3) * 2 : (nwarps / 4) * 3) {
-        uint32_t off = 0;
-        p.off_xA = off; off += p.needA ? planes * K : 0;
-        p.off_xB = off; off += p.needB ? planes * K : 0;
-        p.off_xd = off; off += (K / 32) * 4;
-        p.off_xs = off; off += (K / 32) * 4;
-        p.off_xsum = off; off += p.needB ? (K / 16) * 4 : 0;
-        p.off_gate = off;
-        off = (off + 127) & ~127u;
-        p.off_slots = off;
+    const int U = nb * 4;
+    int rb_max = 0;
+    for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
+    uint32_t off = 0;
+    p.off_xA = off; off += p.needA ? planes * K : 0;
+    p.off_xB = off; off += p.needB ? planes * K : 0;
+    p.off_xd = off; off += (K / 32) * 4;
+    p.off_xs = off; off += (K / 32) * 4;
+    p.off_xsum = off; off += p.needB ? (K / 16) * 4 : 0;
+    p.off_gate = off;
+    off = (off + 127) & ~127u;
+    p.off_slots = off;
+    static const int warp_choices[] = { 18, 17, 16, 14, 12, 10, 8, 6, 4 };
+    int best_w = 0, best_R = 0; double best_cost = 1e30;
+    for (int nwarps : warp_choices) {
+        if (nwarps > max_warps) continue;
         const int ring = (budget - (int)off) / nwarps;        // bytes of staging ring per warp
         const int slot_cap = ring / 2;                        // at least two slots per warp
-        if (slot_cap <= 0) continue;
-        int rb_max = 0;
-        for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
-        // rows per group: full lanes (items per group a multiple of 32) against enough groups to give every warp of
-        // every SM work; small matrices take fewer rows per group
-        const int U = nb * 4;
-        const double target = (double)cx->sm_count * nwarps * (a.out_mode == 3 ? 2 : 1);
-        int R = 0; double best = -1.0;
-        for (int cand = 4; cand >= 1; cand >>= 1) {
-            if ((long long)cand * rb_max + 16 > slot_cap) continue;
-            long long groups = 0;
-            for (int i = 0; i < a.nseg; ++i) groups += (a.seg[i].M + cand - 1) / cand;
-            const double fill = groups >= target ? 1.0 : groups / target;
-            const double score = lane_eff(cand, U) * fill;
-            if (score > best + 1e-9) { best = score; R = cand; }
+        for (int cand = 4; cand >= 1; --cand) {
+            if ((long long)cand * rb_max + 16 + 127 > slot_cap) continue;
+            long long groups = 0;       // units a warp takes one at a time: row groups, or (gate, up) pairs of groups
+            for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg); ++i) groups += (a.seg[i].M + cand - 1) / cand;
+            const long long per_cta = (groups + cx->sm_count - 1) / cx->sm_count;
+            const long long chain = (per_cta + nwarps - 1) / nwarps;
+            const double cost = (double)chain * ((cand * U + 31) / 32 + 0.5) * (a.out_mode == 3 ? 2 : 1);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best_w = nwarps; best_R = cand; }
         }
-        if (!R) continue;
+    }
+    if (!best_w) return set_error(JB_ERR_LIMIT, "gemv: one row group does not fit the staging ring (K=%d)", K);
+    {
+        const int nwarps = best_w, R = best_R;
+        const int ring = (budget - (int)off) / nwarps;
         int slot = 0;
         p.total_bytes = 0;
         long long groups_total = 0;
@@ -737,7 +740,7 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
             p.total_bytes += groups * d.R * d.rb;
             groups_total += groups;
         }
-        if (ring / slot < 2) continue;
+        if (ring / slot < 2) return set_error(JB_ERR_LIMIT, "gemv: staging ring too small (K=%d)", K);
         p.slot_bytes = slot;
         p.nslots = ring / slot;
         if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
@@ -750,7 +753,6 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
         if (grid < 1) grid = 1;
         return JB_OK;
     }
-    return set_error(JB_ERR_LIMIT, "gemv: no launch configuration fits (K=%d)", K);
 }
 
 int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
