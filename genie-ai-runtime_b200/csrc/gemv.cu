@@ -22,7 +22,7 @@
 
 namespace jb {
 
-constexpr int GV_MAXWARPS = 18;                // one CTA per SM; 4 to 18 warps, chosen per launch (gv_configure)
+constexpr int GV_MAXWARPS = 20;                // one CTA per SM; 4 to 18 warps, chosen per launch (gv_configure)
 constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
 
@@ -705,7 +705,7 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
     p.off_gate = off;
     off = (off + 127) & ~127u;
     p.off_slots = off;
-    static const int warp_choices[] = { 18, 17, 16, 14, 12, 10, 8, 6, 4 };
+    static const int warp_choices[] = { 20, 19, 18, 17, 16, 14, 12, 10, 8, 6, 4 };
     int best_w = 0, best_R = 0; double best_cost = 1e30;
     for (int nwarps : warp_choices) {
         if (nwarps > max_warps) continue;
