@@ -747,9 +747,8 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
         p.nwarps = nwarps;
         smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
-        grid = cx->sm_count;
-        const long long ctas_useful = (groups_total + nwarps - 1) / nwarps;
-        if (grid > ctas_useful) grid = (int)ctas_useful;
+        grid = cx->sm_count;                                   // every SM streams its share, however few groups that is
+        if (grid > groups_total) grid = (int)groups_total;
         if (grid < 1) grid = 1;
         return JB_OK;
     }
