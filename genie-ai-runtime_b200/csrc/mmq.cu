@@ -111,7 +111,7 @@ int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N
     // JLLM_B200_MMQ=cuda keeps the CUDA-core kernel (the one that can also export the integer accumulators)
     static const bool tc_off = [] { const char* e = getenv("JLLM_B200_MMQ"); return e && !strcmp(e, "cuda"); }();
     if (!dbg && !tc_off && mmq_tc_applies(W, type, M, N, K)) {
-        const size_t need_tc = mmq_tc_scratch_bytes(type, N, K);
+        const size_t need_tc = mmq_tc_scratch_bytes(type, M, N, K);
         __half* xq = (__half*)mmq_scratch(need_tc, !capturing(st));
         if (!xq) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_tc);
         return launch_mmq_tc(y, W, type, x, xq, M, N, K, st);

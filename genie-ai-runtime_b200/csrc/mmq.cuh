@@ -12,7 +12,7 @@ int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N
 size_t mmq_scratch_bytes(int N, int K);
 // tensor-core path (mmq_tc.cu): tcgen05.mma over fp16 operands built from the same quantised values
 bool   mmq_tc_applies(const void* W, int type, int M, int N, int K);
-size_t mmq_tc_scratch_bytes(int type, int N, int K);
+size_t mmq_tc_scratch_bytes(int type, int M, int N, int K);
 int    launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* xq, int M, int N, int K, cudaStream_t st);
 void*  mmq_scratch(size_t bytes, bool may_alloc);
 

@@ -44,6 +44,8 @@ struct TcArgs {
     __half* y; const uint8_t* W; int type; int M, N, K;
     int n_main, n_min;        // K tiles of weights, K tiles of the min and centring terms (Q4_K)
     int* status;
+    int ksplit;               // K ranges per output tile (1: results go straight to y; >1: fp32 partials, summed by a second kernel)
+    float* part;              // [ksplit][N][M] fp32
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -271,8 +273,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
     uint8_t* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (a.N + n_tile - 1) / n_tile, tiles_m = (a.M + TC_M - 1) / TC_M;
-    const int n_work = tiles_n * tiles_m;
+    const int n_work = tiles_n * tiles_m * a.ksplit;
     const int n_tiles = a.n_main + a.n_min;
+    // work item w = (output tile, K range): main K tiles [t0, t1) (whole fetch groups), and the extra tiles on the last range
+    constexpr int GTILES = TYPE == T_Q4K ? 4 : 2;
+    auto k_range = [&](int w, int& t0, int& t1, bool& extra) {
+        const int sp = w % a.ksplit, ng = a.n_main / GTILES;
+        t0 = (int)((long long)ng * sp / a.ksplit) * GTILES;
+        t1 = (int)((long long)ng * (sp + 1) / a.ksplit) * GTILES;
+        extra = sp == a.ksplit - 1;
+    };
     const uint32_t b_bytes = (uint32_t)n_tile * TC_K * 2;
 
     if (threadIdx.x == 0) {
@@ -297,8 +307,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             for (int w = blockIdx.x; w < n_work && !fail; w += gridDim.x) {
-                const int n0 = (w % tiles_n) * n_tile;
-                for (int t = 0; t < n_tiles; ++t, ++it) {
+                const int n0 = ((w / a.ksplit) % tiles_n) * n_tile;
+                int t0, t1; bool extra;
+                k_range(w, t0, t1, extra);
+                for (int t = t0; t < n_tiles; ++t, ++it) {
+                    if (t == t1) { if (!extra) break; t = a.n_main; if (t >= n_tiles) break; }
                     const int s = it % TC_STAGES;
                     if (!tc_wait(&empty[s], ((it / TC_STAGES) & 1) ^ 1) || fail) { tc_fail(&fail, a.status); break; }
                     mbar_expect_tx(&full[s], b_bytes);
@@ -317,7 +330,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                 const uint32_t d_tmem = tmem + (j & 1) * 256u;
                 if (!tc_wait(&acc_empty[j & 1], ((j >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
-                for (int t = 0; t < n_tiles; ++t, ++it) {
+                int t0, t1; bool extra;
+                k_range(w, t0, t1, extra);
+                const int count = (t1 - t0) + (extra ? a.n_min : 0);
+                for (int t = 0; t < count; ++t, ++it) {
                     const uint32_t s = it % TC_STAGES;
                     if (!tc_wait(&full[s], (it / TC_STAGES) & 1)) { ok = false; break; }
                     tc_fence_after();
@@ -340,8 +356,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         const int pw = warp - 2, rl = (pw & 3) * 32 + lane, h = pw >> 2;
         const int nb = a.K / QK_K;
         constexpr int BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
-        constexpr int GT = TYPE == T_Q4K ? 4 : 2;               // K tiles per fetched group
-        const int n_groups = a.n_main / GT;
+        constexpr int GT = GTILES;                              // K tiles per fetched group
         typename std::conditional<TYPE == T_Q4K, RawQ4, RawQ6>::type cur, nxt;
         uint32_t it = 0;
         bool ok = true;
@@ -356,16 +371,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&full[it_ % TC_STAGES]);
         };
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-            const int row = (w / tiles_n) * TC_M + rl;
+            const int row = ((w / a.ksplit) / tiles_n) * TC_M + rl;
             const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
+            int kt0, kt1; bool extra;
+            k_range(w, kt0, kt1, extra);
+            const int g_first = kt0 / GT, g_last = kt1 / GT;
             auto fetch = [&](decltype(cur)& r, int g) {
-                if (!rowp || g >= n_groups) return;
+                if (!rowp || g >= g_last) return;
                 if constexpr (TYPE == T_Q4K) tc_load_q4k(r, rowp + (size_t)g * Q4K_BYTES, h);
                 else                         tc_load_q6k(r, rowp + (size_t)(g >> 1) * Q6K_BYTES, g & 1, h);
             };
-            fetch(cur, 0);
-            int t = 0;
-            for (int g = 0; g < n_groups && ok; ++g) {
+            fetch(cur, g_first);
+            int t = kt0;
+            for (int g = g_first; g < g_last && ok; ++g) {
                 fetch(nxt, g + 1);
                 #pragma unroll
                 for (int u = 0; u < GT; ++u, ++t, ++it) {
@@ -383,7 +401,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                 }
                 cur = nxt;
             }
-            for (; t < n_tiles && ok; ++t, ++it) {                  // Q4_K: the min-term and centring tiles
+            for (t = a.n_main; extra && t < n_tiles && ok; ++t, ++it) {   // Q4_K: the min-term and centring tiles
                 if (!stage_free(it)) { ok = false; break; }
                 tc_dequant_q4k_extra(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
                 stage_done(it);
@@ -398,7 +416,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         uint32_t j = 0;
         for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++j) {
             const uint32_t acc = j & 1;
-            const int n0 = (w % tiles_n) * n_tile, row = (w / tiles_n) * TC_M + rl;
+            const int n0 = ((w / a.ksplit) % tiles_n) * n_tile, row = ((w / a.ksplit) / tiles_n) * TC_M + rl;
+            float* part = a.ksplit > 1 ? a.part + (size_t)(w % a.ksplit) * a.N * a.M : nullptr;
             if (dw == 0 && lane == 0) {
                 const bool good = tc_wait(&acc_full[acc], (j >> 1) & 1) && !fail;
                 if (!good) tc_fail(&fail, a.status);
@@ -414,7 +433,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                     #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int tok = n0 + cb + c;
-                        if (tok < a.N) a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[c]));
+                        if (tok < a.N) {
+                            if (part) part[(size_t)tok * a.M + row] = __uint_as_float(r[c]);
+                            else a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[c]));
+                        }
                     }
                 }
             }
@@ -430,6 +452,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
+}
+
+// sum of the K-range partials in a fixed order, rounded once to fp16
+__global__ void mmq_tc_reduce_kernel(__half* y, const float* part, long long n, int ksplit) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = part[i];
+    for (int k = 1; k < ksplit; ++k) s += part[(long long)k * n + i];
+    y[i] = __float2half_rn(s);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -451,9 +483,35 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-size_t mmq_tc_scratch_bytes(int type, int N, int K) {
+// Token-tile width and K ranges per output tile, chosen together.  Cost of a choice = rounds of the persistent grid x
+// (tile width / 256, floored at 0.65 for the MMA-issue and dequantisation floor of a K tile) / K ranges.  K is split
+// only when the output tiles alone leave SMs idle (the partial sums cost N x M x 8 bytes of traffic per range) and
+// every range keeps at least four fetch groups.
+static void tc_pick(int M, int N, int n_main_groups, int sm_count, int& n_tile, int& ksplit) {
+    const int tiles_m = (M + TC_M - 1) / TC_M;
+    float best = 1e30f;
+    n_tile = 256; ksplit = 1;
+    for (int cand = 256; cand >= 32; cand >>= 1) {
+        if (cand < 256 && cand >= 2 * N) continue;
+        const int tiles = tiles_m * ((N + cand - 1) / cand);
+        const float w = cand / 256.f, wt = w > 0.65f ? w : 0.65f;
+        for (int ks = 1; ks <= 8; ++ks) {
+            if (ks > 1 && (tiles * ks > sm_count || n_main_groups / ks < 4)) break;
+            const int rounds = (tiles * ks + sm_count - 1) / sm_count;
+            const float cost = rounds * wt / ks + 0.03f * (ks - 1);
+            if (cost < best - 1e-6f) { best = cost; n_tile = cand; ksplit = ks; }
+        }
+    }
+}
+size_t mmq_tc_scratch_bytes(int type, int M, int N, int K) {
+    DeviceCtx* c = ctx();
+    const int sm = c ? c->sm_count : 148;
     const int n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
-    return (size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half) + 256;
+    size_t b = (((size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half)) + 255) & ~(size_t)255;
+    int n_tile, ks;
+    tc_pick(M, N, (K / TC_K) / (type == T_Q4K ? 4 : 2), sm, n_tile, ks);
+    if (ks > 1) b += (size_t)ks * N * M * sizeof(float);
+    return b + 256;
 }
 
 bool mmq_tc_applies(const void* W, int type, int M, int N, int K) {
@@ -472,20 +530,10 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     a.n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     a.status = c->d_status;
     const int Kp = (a.n_main + a.n_min) * TC_K;
-    // token-tile width: the widest tile amortises the dequantisation best, a narrower one can fill the last round of
-    // the persistent grid better; cost model = rounds x max(width/256, 0.65) (0.65: MMA issue and dequantisation floor of a K tile)
-    int n_tile = 256;
-    {
-        const int tiles_m = (M + TC_M - 1) / TC_M;
-        float best = 1e30f;
-        for (int cand = 256; cand >= 32; cand >>= 1) {
-            if (cand < 256 && cand >= 2 * N) continue;
-            const int work = tiles_m * ((N + cand - 1) / cand);
-            const int rounds = (work + c->sm_count - 1) / c->sm_count;
-            const float w = cand / 256.f, cost = rounds * (w > 0.65f ? w : 0.65f);
-            if (cost < best - 1e-6f) { best = cost; n_tile = cand; }
-        }
-    }
+    int n_tile;
+    tc_pick(M, N, a.n_main / (type == T_Q4K ? 4 : 2), c->sm_count, n_tile, a.ksplit);
+    const int tiles = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    a.part = a.ksplit > 1 ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xq) + ((((size_t)N * Kp * sizeof(__half)) + 255) & ~(size_t)255)) : nullptr;
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)Kp, (cuuint64_t)N};
@@ -506,11 +554,16 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     const long long groups = (long long)N * (K / 32);
     JB_CUDA(launch_k(mmq_tc_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xq, N, K, Kp, (int)(type == T_Q4K)));
     count_launch();
-    const int n_work = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    const int n_work = tiles * a.ksplit;
     const dim3 grid(n_work < c->sm_count ? n_work : c->sm_count);
     if (ti == 0) JB_CUDA(launch_k(mmq_tc_kernel<T_Q4K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     else         JB_CUDA(launch_k(mmq_tc_kernel<T_Q6K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     count_launch();
+    if (a.ksplit > 1) {
+        const long long n = (long long)N * M;
+        JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)a.part, n, a.ksplit));
+        count_launch();
+    }
     return JB_OK;
 }
 

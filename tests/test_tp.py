@@ -76,10 +76,11 @@ def test_slices_are_views_of_contiguous_byte_ranges():
     assert s.base is not None and s.size == 6 * 2 * 210 and np.array_equal(s, W.reshape(-1)[3 * 420:9 * 420])
 
 
-def test_gloo_two_ranks_match_single_rank_oracle(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_ranks_match_single_rank_oracle(tmp_path, world):
     model, want_tokens, want_logits = _single_rank_reference()
-    res = _run_ranks("cpu", 2, tmp_path, 600)
-    V_l = tp_worker.SMALL["vocab"] // 2
+    res = _run_ranks("cpu", world, tmp_path, 600)
+    V_l = tp_worker.SMALL["vocab"] // world
     for r, z in enumerate(res):
         assert np.array_equal(z["tokens"], want_tokens), (r, z["tokens"], want_tokens)
         assert np.array_equal(z["logits"], want_logits[r * V_l:(r + 1) * V_l])
