@@ -288,10 +288,12 @@ int launch_fp16_to_int8(int8_t* dst, float* scale_out, const __half* src, int ro
 }
 
 // ── one embedding row -> fp16 (gemv_q4.cu:793-864) ─────────────────────────
+// blockIdx.y = row of a batch: token d_token[y], destination dst + y * hidden
 __global__ void embed_row_kernel(__half* dst, const uint8_t* W, int type, const int* d_token, int token, int hidden) {
     pdl_wait();
     const int b = blockIdx.x, i = threadIdx.x, nb = hidden / QK_K;
-    const int tok = d_token ? *d_token : token;
+    const int tok = d_token ? d_token[blockIdx.y] : token;
+    dst += (size_t)blockIdx.y * hidden;
     float val;
     if (type == T_Q4K) {
         const uint8_t* blk = W + ((size_t)tok * nb + b) * Q4K_BYTES;
@@ -311,6 +313,15 @@ __global__ void embed_row_kernel(__half* dst, const uint8_t* W, int type, const 
         val = __fmul_rn(__fmul_rn(d, (float)(int8_t)blk[192 + (i >> 4)]), (float)(q - 32));
     }
     dst[b * QK_K + i] = __float2half_rn(val);
+}
+int launch_embed_rows(__half* dst, const void* W, int type, const int* d_tokens, int rows, int hidden, cudaStream_t st) {
+    if (rows <= 0) return JB_OK;
+    if (hidden <= 0 || hidden % QK_K) return set_error(JB_ERR_ARG, "embedding rows: hidden=%d is not a multiple of 256", hidden);
+    if (type != T_Q4K && type != T_Q6K) return set_error(JB_ERR_TYPE, "embedding rows: ggml type %d", type);
+    if (!dst || !W || !d_tokens) return set_error(JB_ERR_PTR, "embedding rows: null pointer");
+    JB_CUDA(launch_k(embed_row_kernel, dim3(hidden / QK_K, rows), dim3(QK_K), 0, st, pdl_enabled(), dst, (const uint8_t*)W, type, d_tokens, 0, hidden));
+    count_launch();
+    return JB_OK;
 }
 int launch_embed_row(__half* dst, const void* W, int type, int token, const int* d_token, int hidden, cudaStream_t st) {
     if (hidden <= 0 || hidden % QK_K) return set_error(JB_ERR_ARG, "embedding row: hidden=%d is not a multiple of 256", hidden);
@@ -354,6 +365,9 @@ struct QkvPrepArgs {
     const float* q_norm; const float* k_norm; float eps;
     int8_t* k_cache; int8_t* v_cache; float* k_scales; float* v_scales;   // layer bases, position 0
     int n_heads, n_kv, hd, pos; const int* d_pos; int neox; int do_rope;
+    // batch of independent streams at the same position (blockIdx.y = stream): activations q/k/v + y * stride, caches from lists
+    int q_stride, kv_stride;
+    int8_t* const* k_list; int8_t* const* v_list; float* const* ks_list; float* const* vs_list;
 };
 __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ RopeFreq fr) {
     pdl_wait();
@@ -361,11 +375,16 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
     const int hd = a.hd, h2 = hd / 2;
     const int pos = a.d_pos ? *a.d_pos : a.pos;
     if (w >= a.n_heads + 2 * a.n_kv) return;
+    const int sq = blockIdx.y;
+    __half* qb = a.q + (size_t)sq * a.q_stride;
+    const __half* kb = a.k + (size_t)sq * a.kv_stride; const __half* vb = a.v + (size_t)sq * a.kv_stride;
+    int8_t* kcache = a.k_list ? a.k_list[sq] : a.k_cache; int8_t* vcache = a.k_list ? a.v_list[sq] : a.v_cache;
+    float* kscales = a.k_list ? a.ks_list[sq] : a.k_scales; float* vscales = a.k_list ? a.vs_list[sq] : a.v_scales;
     extern __shared__ float sh[];
     float* buf = sh + (size_t)threadIdx.y * hd;
     const bool is_q = w < a.n_heads, is_k = !is_q && w < a.n_heads + a.n_kv;
     const int head = is_q ? w : (is_k ? w - a.n_heads : w - a.n_heads - a.n_kv);
-    const __half* src = is_q ? a.q + (size_t)head * hd : (is_k ? a.k : a.v) + (size_t)head * hd;
+    const __half* src = is_q ? qb + (size_t)head * hd : (is_k ? kb : vb) + (size_t)head * hd;
     if (is_q || is_k) {
         const float* nw = is_q ? a.q_norm : a.k_norm;
         float ss = 0.f;
@@ -389,7 +408,7 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
             buf[i0] = r0; buf[i1] = r1;
         }
         __syncwarp();
-        if (is_q) { for (int i = lane; i < hd; i += 32) a.q[(size_t)head * hd + i] = __float2half_rn(buf[i]); return; }
+        if (is_q) { for (int i = lane; i < hd; i += 32) qb[(size_t)head * hd + i] = __float2half_rn(buf[i]); return; }
     } else {
         for (int i = lane; i < hd; i += 32) buf[i] = __half2float(src[i]);
         __syncwarp();
@@ -399,8 +418,8 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
     for (int i = lane; i < hd; i += 32) mx = fmaxf(mx, fabsf(buf[i]));
     mx = warp_max(mx);
     const float scale = __fdiv_rn(mx, 127.0f), inv = scale > 0.f ? __fdiv_rn(127.0f, mx) : 0.f;
-    int8_t* dst = (is_k ? a.k_cache : a.v_cache) + ((size_t)pos * a.n_kv + head) * hd;
-    float* sc = (is_k ? a.k_scales : a.v_scales) + (size_t)pos * a.n_kv + head;
+    int8_t* dst = (is_k ? kcache : vcache) + ((size_t)pos * a.n_kv + head) * hd;
+    float* sc = (is_k ? kscales : vscales) + (size_t)pos * a.n_kv + head;
     if (lane == 0) *sc = scale;
     for (int i = lane; i < hd; i += 32) dst[i] = (int8_t)max(-127, min(127, __float2int_rn(__fmul_rn(buf[i], inv))));
 }
@@ -409,9 +428,38 @@ int launch_qkv_prep(__half* q, const __half* k, const __half* v, const float* q_
                     int pos, const int* d_pos, float theta, bool neox, bool do_rope, cudaStream_t st) {
     if (!q || !k || !v || !k_cache || !v_cache || !k_scales || !v_scales) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
     if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
-    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, pos, d_pos, (int)neox, (int)do_rope };
+    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, pos, d_pos, (int)neox, (int)do_rope,
+                      0, 0, nullptr, nullptr, nullptr, nullptr };
     const int warps = n_heads + 2 * n_kv;
     JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
+    count_launch();
+    return JB_OK;
+}
+
+// the same for `batch` independent streams at one position: q [batch][n_heads*hd], k/v [batch][n_kv*hd], caches by list
+int launch_qkv_prep_batched(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
+                            int8_t* const* k_list, int8_t* const* v_list, float* const* ks_list, float* const* vs_list, int batch,
+                            int n_heads, int n_kv, int hd, const int* d_pos, float theta, bool neox, cudaStream_t st) {
+    if (batch <= 0) return JB_OK;
+    if (!q || !k || !v || !k_list || !v_list || !ks_list || !vs_list || !d_pos) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
+    if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
+    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, nullptr, nullptr, nullptr, nullptr, n_heads, n_kv, hd, 0, d_pos, (int)neox, 1,
+                      n_heads * hd, n_kv * hd, k_list, v_list, ks_list, vs_list };
+    const int warps = n_heads + 2 * n_kv;
+    JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4, batch), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
+    count_launch();
+    return JB_OK;
+}
+
+// out = half(float(a) + float(b)), element-wise (the residual exit of a batched layer)
+__global__ void add_half_kernel(__half* out, const __half* a, const __half* b, long long n) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(__fadd_rn(__half2float(a[i]), __half2float(b[i])));
+}
+int launch_add_half(__half* out, const __half* a, const __half* b, long long n, cudaStream_t st) {
+    if (n <= 0) return JB_OK;
+    JB_CUDA(launch_k(add_half_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), out, a, b, n));
     count_launch();
     return JB_OK;
 }

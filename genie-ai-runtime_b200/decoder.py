@@ -91,6 +91,64 @@ class Decoder:
         return int(lib.jllm_b200_decoder_kernels_per_step(C.c_void_p(self._h)))
 
 
+class BatchDecoder:
+    """n_streams requests decoded in lock step through the batched kernels (jllm_b200_batch_decoder_*)."""
+
+    def __init__(self, cfg, weights, max_context, n_streams):
+        self._keep = weights
+        L = cfg["n_layers"]
+        self._layers = (LayerDesc * L)()
+        names = dict(wq="wq", wk="wk", wv="wv", wo="wo", w_gate="gate", w_up="up", w_down="down")
+        for i, lw in enumerate(weights["layers"]):
+            for f, k in names.items():
+                setattr(self._layers[i], f, lw[k][0].data_ptr())
+                setattr(self._layers[i], "type_" + f, lw[k][1])
+            for k in ("rms_attn", "rms_ffn", "q_norm", "k_norm"):
+                setattr(self._layers[i], k, lw[k].data_ptr() if lw.get(k) is not None else None)
+        m = ModelDesc()
+        m.n_layers, m.hidden_dim, m.n_heads, m.n_kv_heads = L, cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
+        m.head_dim, m.intermediate_dim, m.vocab_size, m.max_context = cfg["head_dim"], cfg["ffn"], cfg["vocab"], max_context
+        m.rope_theta, m.rms_eps, m.rope_neox = cfg["rope_theta"], cfg["eps"], 1
+        m.tok_embd, m.embd_type = weights["tok_embd"][0].data_ptr(), weights["tok_embd"][1]
+        m.output, m.output_type = weights["output"][0].data_ptr(), weights["output"][1]
+        m.output_norm = weights["out_norm"].data_ptr()
+        m.layers = self._layers
+        self.cfg, self.n_streams = cfg, n_streams
+        lib.jllm_b200_batch_decoder_create.restype = C.c_void_p
+        lib.jllm_b200_batch_decoder_logits.restype = C.c_void_p
+        self._h = lib.jllm_b200_batch_decoder_create(C.byref(m), C.c_int(n_streams))
+        if not self._h:
+            raise JllmError(-1, last_error())
+
+    def close(self):
+        if self._h:
+            lib.jllm_b200_batch_decoder_destroy(C.c_void_p(self._h))
+            self._h = None
+
+    def generate(self, prompts, n_new, stream=None):
+        """prompts: int array [n_streams][n_prompt]; returns [n_new][n_streams]."""
+        p = np.ascontiguousarray(prompts, np.int32)
+        assert p.ndim == 2 and p.shape[0] == self.n_streams
+        out = np.zeros((max(n_new, 1), self.n_streams), np.int32)
+        check(lib.jllm_b200_batch_decoder_generate(C.c_void_p(self._h), p.ctypes.data_as(C.c_void_p), C.c_int(p.shape[1]), C.c_int(n_new),
+                                                   out.ctypes.data_as(C.c_void_p), _stream(stream)))
+        return out[:n_new]
+
+    def step_device(self, stream):
+        check(lib.jllm_b200_batch_decoder_step_device(C.c_void_p(self._h), _stream(stream)))
+
+    def logits(self):
+        import torch
+        ptr = lib.jllm_b200_batch_decoder_logits(C.c_void_p(self._h))
+        out = torch.empty((self.n_streams, self.cfg["vocab"]), dtype=torch.float16, device="cuda")
+        torch.cuda.synchronize()
+        C.CDLL("libcudart.so").cudaMemcpy(C.c_void_p(out.data_ptr()), C.c_void_p(ptr), C.c_size_t(out.numel() * 2), 3)
+        return out
+
+    def kernels_per_step(self):
+        return int(lib.jllm_b200_batch_decoder_kernels_per_step(C.c_void_p(self._h)))
+
+
 def upload(model):
     """oracle.gen_model()-style numpy weights -> the same structure with torch CUDA tensors."""
     import torch

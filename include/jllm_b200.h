@@ -251,6 +251,20 @@ int    jllm_b200_tp_export(void* region, void* handle64);   /* 64-byte CUDA IPC 
 void*  jllm_b200_tp_open(const void* handle64);             /* maps a peer's region, enabling peer access */
 int    jllm_b200_tp_close(void* mapped);
 
+/* ── lock-step batch decoder session (extension) ────────────────────────────────────────────────
+ * n_streams independent requests, all at the same position, one token each per step: per layer the n_streams hidden
+ * vectors go through the batched kernels above (RMSNorm over rows, jllm_b200_gemm_quant_batched with N = n_streams,
+ * per-stream QK-norm + RoPE + INT8 KV store, ragged-batch decode attention, SwiGLU, residual adds), so the weights are
+ * read once per step for all streams; greedy argmax per stream on the device.  host_prompts is [n_streams][n_prompt]
+ * (equal prompt lengths), host_out receives [n_new][n_streams] token ids. */
+typedef struct jllm_b200_batch_decoder jllm_b200_batch_decoder;
+jllm_b200_batch_decoder* jllm_b200_batch_decoder_create(const jllm_b200_model_desc* model, int n_streams);
+void   jllm_b200_batch_decoder_destroy(jllm_b200_batch_decoder* d);
+int    jllm_b200_batch_decoder_generate(jllm_b200_batch_decoder* d, const int* host_prompts, int n_prompt, int n_new, int* host_out, void* stream);
+int    jllm_b200_batch_decoder_step_device(jllm_b200_batch_decoder* d, void* stream);   /* one more step from the device-side state */
+const void* jllm_b200_batch_decoder_logits(jllm_b200_batch_decoder* d);                /* device, fp16 [n_streams][vocab_size] of the last step */
+int    jllm_b200_batch_decoder_kernels_per_step(jllm_b200_batch_decoder* d);
+
 /* ── allocation-free decode attention (no counterpart in the reference) ─────────────────────────
  * For hosts that cannot let the library allocate device memory: an engine whose own pools already hold
  * all of the GPU's free memory, a request loop that must avoid driver calls which can stall the device,
