@@ -181,6 +181,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--streams", type=int, default=64, help="N = 1: also time this many concurrent streams (0/1: skip)")
     ap.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
                     help="N > 1: one request decoded tensor-parallel over the N GPUs (default), or N independent replicas")
     a = ap.parse_args()
@@ -351,6 +352,28 @@ def main():
                          "frac_of_peak": wbytes / (dev_ms / K * 1e-3) / 1e9 / (peak * (world if tp_mode else 1))},
             "device_status": status,
         }
+        # second workload of the same configuration: 64 concurrent streams decoded in lock step (N = 1 only)
+        if world == 1 and a.streams > 1:
+            try:
+                bd = jb.decoder.BatchDecoder(CFG, weights, MAX_CTX, a.streams)
+                bp = np.random.Generator(np.random.PCG64(SEED + 1)).integers(0, CFG["vocab"], (a.streams, N_PROMPT)).astype(np.int32)
+                with torch.cuda.stream(stream):
+                    bd.generate(bp, 4, stream)
+                    for _ in range(3):
+                        bd.step_device(stream)
+                    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    b0.record(stream)
+                    for _ in range(8):
+                        bd.step_device(stream)
+                    b1.record(stream)
+                    torch.cuda.synchronize()
+                bms = b0.elapsed_time(b1) / 8
+                line["batch_streams"] = {"streams": a.streams, "value": a.streams / (bms * 1e-3), "unit": "tok/s", "ms_per_step": bms,
+                                         "kernels_per_step": bd.kernels_per_step(), "steps": 8}
+                bd.close()
+            except Exception as e:          # the headline line must not depend on the side measurement
+                line["batch_streams"] = {"error": str(e)[:200]}
         # CPU baseline on a bounded sample (rank 0, N = 1 only)
         if world == 1 and a.cpu_steps > 0:
             host = model_to_host(weights)
