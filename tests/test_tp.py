@@ -109,3 +109,66 @@ def test_gpu_ranks_match_single_gpu(tmp_path, world):
         # every exchange but the attention output rides in a GEMV epilogue; the chained variant also folds the four
         # GEMVs between two attentions into one launch
         assert int(z["chain_kernels"]) < int(z["graph_kernels"])
+
+
+@pytest.mark.gpu
+def test_rank_that_never_arrives_is_reported_not_waited_for_forever():
+    """Failure detection without a fault: rank 0 of a two-rank group whose peer region is a buffer that nothing ever writes.
+    Every wait for the peer's packets runs out after its bound, the kernels return, the step completes with
+    JLLM_B200_ERR_TIMEOUT in the device status word, and the context stays usable."""
+    import ctypes as C
+    import importlib
+    import time
+    import torch
+    from gpu_util import pkg
+    jb = pkg()
+    decmod = importlib.import_module(jb.__name__ + ".decoder")
+    tp = importlib.import_module(jb.__name__ + ".tp")
+    small = dict(tp_worker.SMALL, n_layers=1)
+    model = orc.gen_model(7, **small)
+    cfg = model["cfg"]
+    local = decmod.upload(tp.shard_model(model, 2, 0))
+    lib = jb.lib
+    lib.jllm_b200_tp_alloc.restype = C.c_void_p
+    lib.jllm_b200_tp_region_bytes.restype = C.c_size_t
+    lib.jllm_b200_decoder_create_tp.restype = C.c_void_p
+    nbytes = lib.jllm_b200_tp_region_bytes(cfg["hidden"], cfg["n_heads"] * cfg["head_dim"], cfg["ffn"])
+    mine, silent = lib.jllm_b200_tp_alloc(C.c_size_t(nbytes)), lib.jllm_b200_tp_alloc(C.c_size_t(nbytes))
+    assert mine and silent
+    regions = (C.c_void_p * 2)(mine, silent)
+    layers = (decmod.LayerDesc * 1)()
+    names = dict(wq="wq", wk="wk", wv="wv", wo="wo", w_gate="gate", w_up="up", w_down="down")
+    for f, k in names.items():
+        setattr(layers[0], f, local["layers"][0][k][0].data_ptr())
+        setattr(layers[0], "type_" + f, local["layers"][0][k][1])
+    for k in ("rms_attn", "rms_ffn", "q_norm", "k_norm"):
+        setattr(layers[0], k, local["layers"][0][k].data_ptr())
+    m = decmod.ModelDesc()
+    m.n_layers, m.hidden_dim, m.n_heads, m.n_kv_heads = 1, cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
+    m.head_dim, m.intermediate_dim, m.vocab_size, m.max_context = cfg["head_dim"], cfg["ffn"], cfg["vocab"], 16
+    m.rope_theta, m.rms_eps, m.rope_neox = cfg["rope_theta"], cfg["eps"], 1
+    m.tok_embd, m.embd_type = local["tok_embd"][0].data_ptr(), local["tok_embd"][1]
+    m.output, m.output_type = local["output"][0].data_ptr(), local["output"][1]
+    m.output_norm = local["out_norm"].data_ptr()
+    m.layers = layers
+    h = lib.jllm_b200_decoder_create_tp(C.byref(m), C.c_int(1), C.c_int(0), C.c_int(2), regions)
+    assert h, jb.last_error()
+    st = torch.cuda.Stream()
+    t0 = time.time()
+    rc = lib.jllm_b200_decoder_step(C.c_void_p(h), 5, 0, C.c_void_p(st.cuda_stream))
+    assert rc == 0                                       # the step was enqueued; the failure shows on the device
+    status = jb.device_status(st)
+    took = time.time() - t0
+    assert status == 7, status                           # JLLM_B200_ERR_TIMEOUT
+    assert took < 120, took
+    assert jb.device_status(st) == 0                     # reading the status clears it
+    # the context is still usable: an ordinary GEMV gives the oracle's result
+    rng = np.random.Generator(np.random.PCG64(3))
+    W = orc.gen_weight(rng, 12, 64, 512); x = orc.gen_act(rng, 512)
+    y = torch.zeros(64, dtype=torch.float16, device="cuda")
+    from gpu_util import dev, close
+    jb.gemv_quant(y, dev(W), 12, dev(x), 64, 512)
+    ok, md = close(y.float().cpu().numpy(), orc.entry_gemv_quant(W, 12, x, 64, 512).astype(np.float32))
+    assert ok, md
+    lib.jllm_b200_decoder_destroy(C.c_void_p(h))
+    lib.jllm_b200_tp_free(C.c_void_p(mine)); lib.jllm_b200_tp_free(C.c_void_p(silent))
