@@ -4,20 +4,22 @@
 // :1245-1616 dispatch).  The GGUF super-block layout is read unchanged from HBM.
 //
 // Shape of the kernel
-//   * grid = 2 CTAs per SM; every CTA owns one contiguous byte range of the (up to three)
-//     weight matrices, split evenly by bytes, so all SMs stream the same amount.
-//   * weights travel HBM -> shared memory with 1-D TMA bulk copies (cp.async.bulk +
-//     mbarrier complete_tx) through a ring of slots, several copies in flight per CTA;
-//     Q6_K rows (210-byte blocks, 2-byte aligned) are copied as the enclosing 16-byte
-//     aligned span and re-aligned with funnel shifts when read from shared memory.
-//   * the activation vector is quantised by every CTA itself into shared memory (q8_1
-//     codes, or 16-bit fixed point for the entry points whose reference path keeps fp16
-//     activations), optionally after a fused RMSNorm, laid out so that the 16-byte runs
-//     the lanes read are bank-conflict free.
-//   * each lane takes one 16-byte run of quants per step, dots it with dp4a, and a warp
-//     reduces the rows it owns with shuffles; outputs are deterministic.
-//   * launched with programmatic dependent launch: weight copies are issued before
-//     griddepcontrol.wait, so they overlap the tail of the kernel that produces x.
+//   * grid = one CTA per SM with 4 to 20 warps; every CTA owns one contiguous range of row groups of the (up to
+//     three) weight matrices, split evenly by bytes, so all SMs stream the same amount.  Warps per CTA and rows per
+//     group are chosen per launch so that the longest chain of work any warp runs is shortest (gv_configure).
+//   * weights travel HBM -> shared memory with 1-D TMA bulk copies (cp.async.bulk + mbarrier complete_tx); every
+//     warp runs its own ring of slots with one mbarrier per slot, no CTA-wide barrier in the loop; Q6_K rows
+//     (210-byte blocks, 2-byte aligned) are copied as the enclosing 16-byte aligned span and re-aligned with funnel
+//     shifts when read from shared memory.
+//   * the activation vector is quantised once per SM by all threads of the CTA (four threads per 32-element group)
+//     into shared memory (q8_1 codes, or 16-bit fixed point for the entry points whose reference path keeps fp16
+//     activations), optionally after a fused RMSNorm, laid out so that the 16-byte runs the lanes read are
+//     bank-conflict free.
+//   * each lane takes one 32-byte run of quants per step, dots it with dp4a, and a warp reduces the rows it owns
+//     with shuffles; outputs are deterministic.
+//   * launched with programmatic dependent launch: weight copies are issued before griddepcontrol.wait.
+//   * the same body runs as one phase of an optional chained launch (gemv_chain_kernel), and carries the
+//     tensor-parallel hooks: activations polled as {value, epoch} packets, results pushed as packets to every rank.
 #include "gemv.cuh"
 
 namespace jb {
