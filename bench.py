@@ -9,21 +9,31 @@ weights (Q4_K everywhere, Q6_K for attn_v, ffn_down and output), INT8 KV cache, 
 random-id prompt is decoded first (untimed), then W warm-up steps, then K timed greedy decode steps; one
 step = one token through all 36 layers, the logits GEMV and the device-side argmax.
 
-One JSON line is printed (rank 0).  `value` times the steps on the device with every input resident
-(CUDA-graph replay, no host synchronisation inside the timed region); `e2e` times the user-facing per-token
-call, which copies {position, token} host->device and the sampled token device->host and waits for it.
-`roofline` times the dominant kernel (fused norm + gate/up GEMV + SwiGLU, 28 MB of Q4_K weights per launch)
-over the 36 layers' distinct weights with CUDA events on its own stream.  `cpu_baseline` runs the CPU oracle
-(oracle/, the reference's golden arithmetic restated in C with OpenMP) on a bounded sample of the same steps.
+One JSON line is printed (rank 0).
+  value        the K steps timed on the device with every input resident (CUDA-graph replay, no host synchronisation
+               inside the timed region); the K steps are repeated `--repeats` times, `value` is the median repeat and
+               `repeats` lists every repeat.
+  e2e          the user-facing per-token call: copies {position, token} host->device and the sampled token device->host
+               and waits for it.
+  tokens_match the e2e loop and the device-resident loop must produce the same greedy tokens at the same positions, and
+               the tokens predicted at the prompt positions are compared with the CPU oracle's.
+  roofline     the dominant kernel (fused norm + gate/up GEMV + SwiGLU, 28 MB of Q4_K weights per launch) over the 36
+               layers' distinct weights, CUDA events on its own stream.
+  kernels      (N = 1) the per-kernel items of the metric: configuration 0 / 1 GEMV GB/s, configuration 2 decode
+               attention GB/s per call at 1024..32768 keys and for 64 ragged sequences, configuration 3 TFLOP/s.
+  cpu_baseline the CPU oracle (oracle/, the reference's golden arithmetic restated in C with OpenMP) on a bounded
+               sample of the same steps.
 
-N > 1 (torchrun): the same single request is decoded tensor-parallel — weight rows and KV heads sharded over the N
-GPUs, slices gathered after each sharded product by the library's own NVLink push kernels — so `value` is the
-tok/s of that one stream (strong scaling).  --parallelism replicas runs N independent copies of the 1-GPU
-engine instead (weak scaling, no data-path collective).  Times are reduced with MAX over ranks.
+N > 1 (torchrun): every rank draws the same model; the single request is decoded tensor-parallel — weight rows and KV
+heads sharded over the N GPUs, slices gathered after each sharded product by the library's own NVLink push kernels —
+so `value` is the tok/s of that one stream (strong scaling at every N).  The same run also times the single-GPU engine
+on every rank: `tp_tokens_match` compares the tensor-parallel stream with the single-GPU one and `replicas` reports N
+independent engines (weak scaling, no data-path collective).  --parallelism replicas makes the replicas the headline.
+Times are reduced with MAX over ranks.
 
---impl reference: times the CPU oracle port of the reference's arithmetic on the host cores (the reference has
-no CPU implementation of INT8-KV attention, src/kernels/attention.cu:1078-1082, and its CPU GEMV golden is
-single-threaded and reachable only behind a CUDA copy), same metric and configuration.
+--impl reference: times the CPU oracle port of the reference's arithmetic on all host cores (the reference has no CPU
+implementation of INT8-KV attention, src/kernels/attention.cu:1078-1082, and its CPU GEMV golden is single-threaded
+and reachable only behind a CUDA copy), same metric and configuration.
 """
 import argparse
 import json
@@ -66,29 +76,24 @@ def gen_blocks_gpu(gen, ggml_type, rows, K, dev):
     return img.reshape(rows, -1).contiguous()
 
 
-def gen_model_gpu(dev, cfg=CFG, seed=SEED, shard=None):
-    """Whole model, or with shard=(rank, world) the row slices of one tensor-parallel rank: sharded matrices hold
-    rows/world rows drawn from a per-rank generator, replicated tensors (embedding, norms) come from the shared one."""
+def gen_model_gpu(dev, cfg=CFG, seed=SEED):
+    """The whole model on `dev`.  Every rank of a multi-GPU run draws the same model from the same seed and takes its
+    own row slices of it (views), so the tensor-parallel stream can be checked against the single-GPU one."""
     import torch
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
-    gl, div = g, 1
-    if shard is not None:
-        gl = torch.Generator(device=dev)
-        gl.manual_seed(seed * 1000 + shard[0])
-        div = shard[1]
     H, QD, KVD, I, V = cfg["hidden"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["ffn"], cfg["vocab"]
     nrm = lambda n: (1.0 + 0.02 * torch.randn(n, device=dev, generator=g)).float()
-    w = dict(layers=[])
+    w = dict(cfg=dict(cfg), layers=[])
     for _ in range(cfg["n_layers"]):
         w["layers"].append(dict(
-            wq=(gen_blocks_gpu(gl, Q4_K, QD // div, H, dev), Q4_K), wk=(gen_blocks_gpu(gl, Q4_K, KVD // div, H, dev), Q4_K),
-            wv=(gen_blocks_gpu(gl, Q6_K, KVD // div, H, dev), Q6_K), wo=(gen_blocks_gpu(gl, Q4_K, H // div, QD, dev), Q4_K),
-            gate=(gen_blocks_gpu(gl, Q4_K, I // div, H, dev), Q4_K), up=(gen_blocks_gpu(gl, Q4_K, I // div, H, dev), Q4_K),
-            down=(gen_blocks_gpu(gl, Q6_K, H // div, I, dev), Q6_K),
+            wq=(gen_blocks_gpu(g, Q4_K, QD, H, dev), Q4_K), wk=(gen_blocks_gpu(g, Q4_K, KVD, H, dev), Q4_K),
+            wv=(gen_blocks_gpu(g, Q6_K, KVD, H, dev), Q6_K), wo=(gen_blocks_gpu(g, Q4_K, H, QD, dev), Q4_K),
+            gate=(gen_blocks_gpu(g, Q4_K, I, H, dev), Q4_K), up=(gen_blocks_gpu(g, Q4_K, I, H, dev), Q4_K),
+            down=(gen_blocks_gpu(g, Q6_K, H, I, dev), Q6_K),
             rms_attn=nrm(H), rms_ffn=nrm(H), q_norm=nrm(cfg["head_dim"]), k_norm=nrm(cfg["head_dim"])))
     w["tok_embd"] = (gen_blocks_gpu(g, Q4_K, V, H, dev), Q4_K)
-    w["output"] = (gen_blocks_gpu(gl, Q6_K, V // div, H, dev), Q6_K)
+    w["output"] = (gen_blocks_gpu(g, Q6_K, V, H, dev), Q6_K)
     w["out_norm"] = nrm(H)
     return w
 
@@ -167,102 +172,53 @@ def cpu_decode_sample(host_model, prompt, n_steps, threads=None):
         orc.lib().orc_set_threads(int(threads))
     dec = orc.Decoder(host_model, MAX_CTX)
     tok = int(prompt[0])
+    pred = []
     t0 = time.perf_counter()
     for pos in range(n_steps):
         tok = dec.step(tok if pos >= len(prompt) else int(prompt[pos]), pos)
+        pred.append(tok)
     dt = time.perf_counter() - t0
-    return n_steps / dt, int(orc.lib().orc_num_threads())
+    return n_steps / dt, int(orc.lib().orc_num_threads()), pred
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200")
-    ap.add_argument("--cpu-steps", type=int, default=3)
-    ap.add_argument("--streams", type=int, default=64, help="N = 1: also time this many concurrent streams (0/1: skip)")
-    ap.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
-                    help="N > 1: one request decoded tensor-parallel over the N GPUs (default), or N independent replicas")
-    a = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    W = max(a.warmup, 3)
-    K = a.steps
-    config = {"workload": "qwen3-4b-shape decoder, Q4_K_M mix (Q6_K attn_v/ffn_down/output), INT8 KV, greedy decode after a "
-                          f"{N_PROMPT}-token random-id prompt, batch 1",
-              "n_prompt": N_PROMPT,
-              "parallelism": "single" if int(os.environ.get("WORLD_SIZE", "1")) == 1 else
-                             (f"tp{os.environ.get('WORLD_SIZE')} (weight rows and KV heads sharded, push gathers over NVLink)" if a.parallelism == "tp"
-                              else f"{os.environ.get('WORLD_SIZE')} independent replicas"),
-              "l2": "2.6 GB of weights are streamed per step (>> 126 MB L2); no explicit flush"}
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
+
+def profile_traffic(name):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu summary profiles/<name>.json."""
+    try:
+        with open(os.path.join(ROOT, "profiles", name + ".json")) as f:
+            d = json.load(f)
+        return int(d["dram_bytes_read"]) + int(d["dram_bytes_write"])
+    except Exception:
+        return None
+
+
+# ── measurements on one decoder session ─────────────────────────────────────
+def time_decoder(jb, dec, prompt, W, K, R, stream, barrier, local_rank):
+    """e2e loop (per-token host round trip), then R repeats of K device-resident steps (graph replays, no host
+    synchronisation inside a repeat).  Returns times, the tokens both loops produced at the same positions, the
+    tokens predicted at the prompt positions, launches counted inside the timed region and the clock samples."""
     import torch
-
-    if a.impl == "reference":
-        if rank != 0:
-            return
-        if not torch.cuda.is_available():
-            print(json.dumps({"impl": "reference", "unavailable": "needs the GPU box to draw the synthetic weights"}))
-            return
-        dev = torch.device("cuda", local_rank)
-        torch.cuda.set_device(dev)
-        host = model_to_host(gen_model_gpu(dev))
-        prompt = np.random.Generator(np.random.PCG64(SEED)).integers(0, CFG["vocab"], N_PROMPT)
-        n = max(1, min(K, 4))
-        for _ in range(min(W, 1)):
-            cpu_decode_sample(host, prompt, 1)
-        v, cores = cpu_decode_sample(host, prompt, n)
-        line = {"metric": "decode_tok_s", "value": v, "unit": "tok/s", "n_gpus": 0, "steps": n, "warmup": min(W, 1), "ms_per_step": 1e3 / v,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xq4/q6 dots, fp32 accumulate, fp16 activations",
-                "data": "synthetic", "config": config, "impl": "reference",
-                "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
-                                 "sample": f"{n} decode steps of the full model at positions 0..{n - 1}"},
-                "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
-        return
-
-    from __graft_entry__ import load_package
-    jb = load_package()
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    tp_mode = world > 1 and a.parallelism == "tp"
-    prompt = np.random.Generator(np.random.PCG64(SEED)).integers(0, CFG["vocab"], N_PROMPT).astype(np.int32)
-    if tp_mode:
-        import importlib
-        tpm = importlib.import_module(jb.__name__ + ".tp")
-        weights = gen_model_gpu(dev, shard=(rank, world))
-        dec = tpm.TPDecoder(CFG, weights, MAX_CTX, rank, world)
-    else:
-        weights = gen_model_gpu(dev)
-        dec = jb.decoder.Decoder(CFG, weights, MAX_CTX, jb.decoder.FUSED | jb.decoder.GRAPH)
-    streams = 1 if (tp_mode or world == 1) else world        # requests decoded at the same time
-    stream = torch.cuda.Stream(device=dev)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    # ── e2e: per-token user call, host boundary inside ──
     pos_tok = torch.zeros(2, dtype=torch.int32).pin_memory()
     nxt = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     def run_prompt():
-        tok = None
+        toks = []
         for p in range(N_PROMPT):
             pos_tok[0], pos_tok[1] = p, int(prompt[p])
             dec.step_sync(pos_tok, nxt, stream)
-            tok = int(nxt[0])
-        return tok
+            toks.append(int(nxt[0]))
+        return toks
 
     with torch.cuda.stream(stream):
-        tok = run_prompt()
+        dec.reset()
+        prompt_pred = run_prompt()
+        tok = prompt_pred[-1]
         for i in range(W):
             pos_tok[0], pos_tok[1] = N_PROMPT + i, tok
             dec.step_sync(pos_tok, nxt, stream)
@@ -278,46 +234,186 @@ def main():
         barrier()
         e2e_s = time.perf_counter() - t0
 
-    # ── device-resident timing: prompt + warm-up + K steps enqueued without host synchronisation ──
-    import ctypes as C
-    lib = jb.lib
-    h = C.c_void_p(dec._h)
-    sp = C.c_void_p(stream.cuda_stream)
-    out_host = np.zeros(N_PROMPT + W + K + 1, np.int32)
-    # generate() = prompt steps + new tokens in one enqueue; to time only the K decode steps we enqueue the first part,
-    # record an event, enqueue K more graph replays, record again.
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        tok = run_prompt()
+        # device-resident: the prompt and W warm-up steps, then R x K self-feeding steps
+        dec.reset()
+        tok = run_prompt()[-1]
         pos_tok[0], pos_tok[1] = N_PROMPT, tok
         dec.step_sync(pos_tok, nxt, stream)                  # leaves position/token on the device; later steps self-feed
         for _ in range(W - 1):
-            jb.check(lib.jllm_b200_decoder_step_device(h, sp))
+            dec.step_device(stream)
         barrier()
+        base, _ = dec.recorded_tokens(0, 0, stream)          # index of the first timed token in the device-side record
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(R + 1)]
         l0 = jb.launch_count()
         with ClockSampler(local_rank) as clk:
-            ev0.record(stream)
-            for _ in range(K):
-                jb.check(lib.jllm_b200_decoder_step_device(h, sp))
-            ev1.record(stream)
+            evs[0].record(stream)
+            for r in range(R):
+                for _ in range(K):
+                    dec.step_device(stream)
+                evs[r + 1].record(stream)
             barrier()
         launches = jb.launch_count() - l0
-    dev_ms = ev0.elapsed_time(ev1)
-    status = jb.device_status(stream)
+        _, dev_tokens = dec.recorded_tokens(base, R * K, stream)
+    rep_ms = [evs[r].elapsed_time(evs[r + 1]) for r in range(R)]
+    return dict(e2e_s=e2e_s, rep_ms=rep_ms, e2e_tokens=e2e_tokens, dev_tokens=[int(t) for t in dev_tokens], prompt_pred=prompt_pred,
+                launches=launches // R, clocks=clk.summary(), status=jb.device_status(stream))
+
+
+def kernel_records(jb, peak_gbs, peaks):
+    """The per-kernel items of the metric, each timed as a CUDA graph of launches over operand copies rotated past the L2
+    cache (time per CALL: an attention call includes its reduce pass; a batched product includes its activation
+    quantiser): configuration 0 and 1 GEMV GB/s, configuration 2 decode attention GB/s, configuration 3 TFLOP/s."""
+    import importlib
+    mb = importlib.import_module(jb.__name__ + ".microbench")
+    tf_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    out = {}
+
+    def hbm(name, argv):
+        try:
+            r = mb.measure(jb, argv)
+            out[name] = {"bytes": int(r["algorithmic_bytes"]), "us": round(r["us_per_launch"], 3), "GBps": round(r["GBps"], 1),
+                         "frac": round(r["GBps"] / peak_gbs, 4), "bound": "hbm"}
+        except Exception as e:
+            out[name] = {"error": str(e)[:160]}
+
+    def tensor(name, argv, M, N, K):
+        try:
+            r = mb.measure(jb, argv)
+            out[name] = {"flops": 2.0 * M * N * K, "us": round(r["us_per_launch"], 2), "TFLOPs": round(r["TFLOPs"], 1),
+                         "frac": round(r["TFLOPs"] / tf_peak, 4), "bound": "tensor (fp16 tcgen05 contraction; of bf16_tflops_sustained)"}
+        except Exception as e:
+            out[name] = {"error": str(e)[:160]}
+
+    hbm("config0_gemv_q4k_9728x2560", ["gemv", "--type", 12, "--M", 9728, "--K", 2560])
+    hbm("config1_gemv_q6k_2560x9728_b1", ["gemv", "--type", 14, "--M", 2560, "--K", 9728])
+    hbm("config1_gemv_q6k_2560x9728_b8", ["mmq", "--type", 14, "--M", 2560, "--K", 9728, "--N", 8])
+    for L in (1024, 4096, 8192, 32768):
+        hbm(f"config2_attn_int8_L{L}", ["attn", "--L", L])
+    hbm("config2_attn_int8_64_ragged", ["attn", "--batch", 64, "--iters", 50])
+    for N in (512, 2048, 8192):
+        tensor(f"config3_mmq_q4k_9728x2560_N{N}", ["mmq", "--type", 12, "--M", 9728, "--K", 2560, "--N", N, "--iters", 20], 9728, N, 2560)
+    tensor("config3_mmq_q6k_2560x9728_N2048", ["mmq", "--type", 14, "--M", 2560, "--K", 9728, "--N", 2048, "--iters", 20], 2560, 2048, 9728)
+    return out
+
+
+def reference_arm(a, rank, local_rank, config, W, K):
+    """The reference's arithmetic on the host cores (CPU oracle port, OpenMP over all the cores this process may use)."""
+    import torch
+    if rank != 0:
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "needs the GPU box to draw the synthetic weights"}))
+        return
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    host = model_to_host(gen_model_gpu(dev))
+    prompt = np.random.Generator(np.random.PCG64(SEED)).integers(0, CFG["vocab"], N_PROMPT)
+    threads = host_threads()                                  # torchrun sets OMP_NUM_THREADS=1 for its ranks: override it
+    n = max(1, min(K, 8))
+    for _ in range(min(W, 1)):
+        cpu_decode_sample(host, prompt, 1, threads)
+    v, cores, _ = cpu_decode_sample(host, prompt, n, threads)
+    line = {"metric": "decode_tok_s", "value": v, "unit": "tok/s", "n_gpus": 0, "steps": n, "warmup": min(W, 1), "ms_per_step": 1e3 / v,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8xq4/q6 dots, fp32 accumulate, fp16 activations",
+            "data": "synthetic", "config": config, "impl": "reference",
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
+                             "sample": f"{n} decode steps of the full model at positions 0..{n - 1}"},
+            "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--repeats", type=int, default=5, help="the K timed steps are repeated this many times; value = the median repeat")
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--cpu-steps", type=int, default=32, help="N = 1: decode steps of the CPU oracle (timed baseline and token check)")
+    ap.add_argument("--streams", type=int, default=64, help="N = 1: also time this many concurrent streams (0/1: skip)")
+    ap.add_argument("--no-kernels", action="store_true", help="N = 1: skip the per-kernel records")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
+                    help="N > 1: one request decoded tensor-parallel over the N GPUs (default), or N independent replicas")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    W = max(a.warmup, 3)
+    K = a.steps
+    R = max(1, a.repeats)
+    max_ctx = max(512, ((N_PROMPT + W + R * K + 8 + 127) // 128) * 128)
+    tp_mode = world > 1 and a.parallelism == "tp"
+    config = {"workload": "qwen3-4b-shape decoder, Q4_K_M mix (Q6_K attn_v/ffn_down/output), INT8 KV, greedy decode after a "
+                          f"{N_PROMPT}-token random-id prompt, batch 1",
+              "n_prompt": N_PROMPT,
+              "parallelism": "single" if world == 1 else
+                             (f"tp{world} (weight rows and KV heads sharded, push gathers over NVLink)" if tp_mode else f"{world} independent replicas"),
+              "l2": "2.6 GB of weights are streamed per step (>> 126 MB L2); no explicit flush"}
+
+    if a.impl == "reference":
+        reference_arm(a, rank, local_rank, config, W, K)
+        return
+
+    import torch
+    from __graft_entry__ import load_package
+    jb = load_package()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    prompt = np.random.Generator(np.random.PCG64(SEED)).integers(0, CFG["vocab"], N_PROMPT).astype(np.int32)
+    weights = gen_model_gpu(dev)                              # the same model on every rank
+    stream = torch.cuda.Stream(device=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def reduce_max(vals):
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    # the single-GPU engine: the headline at N = 1; at N > 1 the checker of the tensor-parallel stream and the replicas record
+    dec1 = jb.decoder.Decoder(CFG, weights, max_ctx, jb.decoder.FUSED | jb.decoder.GRAPH)
+    m1 = time_decoder(jb, dec1, prompt, W, K, R, stream, barrier, local_rank)
+    kernels_per_step = dec1.kernels_per_step()
+    dec1.close()
+    head, streams = m1, (world if world > 1 and not tp_mode else 1)
+    side = {}
+    if tp_mode:
+        import importlib
+        tpm = importlib.import_module(jb.__name__ + ".tp")
+        dect = tpm.TPDecoder(CFG, tpm.shard_model(weights, world, rank), max_ctx, rank, world)
+        head = time_decoder(jb, dect, prompt, W, K, R, stream, barrier, local_rank)
+        kernels_per_step = dect.kernels_per_step()
+        dect.close()
+        rep1 = reduce_max([float(np.median(m1["rep_ms"]))])[0]
+        side["replicas"] = {"value": world * K / (rep1 * 1e-3), "unit": "tok/s", "ms_per_step": rep1 / K, "scaling": "weak",
+                            "what": f"{world} independent single-GPU engines, one request each, run at the same time (no data-path collective)"}
+        side["tp_tokens_match"] = bool(head["dev_tokens"] == m1["dev_tokens"] and head["e2e_tokens"] == m1["e2e_tokens"])
+        side["single_gpu_tok_s_same_run"] = K / (float(np.median(m1["rep_ms"])) * 1e-3)
 
     # ── roofline of the dominant kernel: fused norm + gate/up GEMV + SwiGLU over the 36 layers' weights ──
     H, I = CFG["hidden"], CFG["ffn"] // (world if tp_mode else 1)
     x = (torch.randn(H, device=dev) * 1.0).to(torch.float16)
     sw = torch.zeros(I, dtype=torch.float16, device=dev)
     reps = 5
+    import importlib
+    tpm_ = importlib.import_module(jb.__name__ + ".tp")
+    lws = weights["layers"] if not tp_mode else tpm_.shard_model(weights, world, rank)["layers"]
     with torch.cuda.stream(stream):
-        for lw in weights["layers"][:4]:
+        for lw in lws[:4]:
             jb.norm_gemv_pair_swiglu(sw, lw["gate"][0], lw["up"][0], Q4_K, I, x, lw["rms_ffn"], True, 1e-6, H, stream)
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         k0.record(stream)
         for _ in range(reps):
-            for lw in weights["layers"]:
+            for lw in lws:
                 jb.norm_gemv_pair_swiglu(sw, lw["gate"][0], lw["up"][0], Q4_K, I, x, lw["rms_ffn"], True, 1e-6, H, stream)
         k1.record(stream)
         torch.cuda.synchronize()
@@ -326,36 +422,45 @@ def main():
     peak, peak_src = measured_peaks()
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
 
-    # MAX over ranks
-    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    rep = reduce_max(head["rep_ms"] + [head["e2e_s"] * 1e3])           # MAX over ranks, repeat by repeat
+    rep_ms, e2e_ms = rep[:-1], rep[-1]
+    dev_ms = float(np.median(rep_ms))
 
     if rank == 0:
         wbytes = weight_bytes_per_token()
+        traffic = profile_traffic("gemv_pair_swiglu_q4k_9728x2560")
         line = {
             "metric": "decode_tok_s", "value": streams * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if tp_mode else "weak", "vs_baseline": None,
+            "ms_per_step": dev_ms / K, "higher_is_better": True,
+            # the default multi-GPU mode shards ONE request (strong scaling), so the label is the same at every N; replicas are weak scaling
+            "scaling": "weak" if (world > 1 and not tp_mode) else "strong", "vs_baseline": None,
             "dtype": "int8xq4/q6 dots, fp32 accumulate, fp16 activations", "data": "synthetic", "config": config,
+            "repeats": {"n": R, "ms_per_step": [round(v / K, 5) for v in rep_ms], "value": "median repeat",
+                        "spread": round((max(rep_ms) - min(rep_ms)) / dev_ms, 4)},
             "e2e": {"value": streams * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": int(launches),
-            "kernels_per_step": dec.kernels_per_step(),
-            "clocks": clk.summary(),
+            "gpu_launches": int(head["launches"]),
+            "kernels_per_step": kernels_per_step,
+            "clocks": head["clocks"],
+            "tokens_match": {"e2e_vs_device_loop": bool(head["e2e_tokens"] == head["dev_tokens"][:K]), "compared": K},
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<q8_1> (fused RMSNorm + gate/up Q4_K GEMV + SwiGLU)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape, from the ncu
-                         # capture summarised in profiles/gemv_pair_swiglu_q4k_9728x2560.md (scaled by rows when sharded)
-                         "traffic": 28077824 // (world if tp_mode else 1),
+                         "traffic": (traffic // (world if tp_mode else 1)) if traffic else None,
                          "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3, "peak_source": peak_src},
             "step_hbm": {"weight_bytes_per_step": wbytes, "achieved_gbs": wbytes / (dev_ms / K * 1e-3) / 1e9,
                          "frac_of_peak": wbytes / (dev_ms / K * 1e-3) / 1e9 / (peak * (world if tp_mode else 1))},
-            "device_status": status,
+            "device_status": head["status"],
         }
+        line.update(side)
+        if world == 1 and not a.no_kernels:
+            try:
+                peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            except Exception:
+                peaks = {}
+            line["kernels"] = kernel_records(jb, peak, peaks)
         # second workload of the same configuration: 64 concurrent streams decoded in lock step (N = 1 only)
         if world == 1 and a.streams > 1:
             try:
-                bd = jb.decoder.BatchDecoder(CFG, weights, MAX_CTX, a.streams)
+                bd = jb.decoder.BatchDecoder(CFG, weights, max_ctx, a.streams)
                 bp = np.random.Generator(np.random.PCG64(SEED + 1)).integers(0, CFG["vocab"], (a.streams, N_PROMPT)).astype(np.int32)
                 with torch.cuda.stream(stream):
                     bd.generate(bp, 4, stream)
@@ -370,19 +475,23 @@ def main():
                     torch.cuda.synchronize()
                 bms = b0.elapsed_time(b1) / 8
                 line["batch_streams"] = {"streams": a.streams, "value": a.streams / (bms * 1e-3), "unit": "tok/s", "ms_per_step": bms,
-                                         "kernels_per_step": bd.kernels_per_step(), "steps": 8}
+                                         "kernels_per_step": bd.kernels_per_step(), "steps": 8,
+                                         "frac_of_hbm_peak": wbytes / (bms * 1e-3) / 1e9 / peak}
                 bd.close()
             except Exception as e:          # the headline line must not depend on the side measurement
                 line["batch_streams"] = {"error": str(e)[:200]}
-        # CPU baseline on a bounded sample (rank 0, N = 1 only)
+        # CPU baseline on a bounded sample (rank 0, N = 1 only), and the token check against it
         if world == 1 and a.cpu_steps > 0:
+            n_cpu = min(a.cpu_steps, N_PROMPT)
             host = model_to_host(weights)
-            v, cores = cpu_decode_sample(host, prompt, a.cpu_steps)
+            v, cores, cpu_pred = cpu_decode_sample(host, prompt, n_cpu, host_threads())
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": f"{a.cpu_steps} decode steps of the full model at positions 0..{a.cpu_steps - 1}"}
+                                    "sample": f"{n_cpu} decode steps of the full model at positions 0..{n_cpu - 1}"}
+            eq = sum(int(x == y) for x, y in zip(cpu_pred, head["prompt_pred"][:n_cpu]))
+            line["tokens_match"]["oracle_vs_gpu_at_prompt_positions"] = {"compared": n_cpu, "equal": eq}
         print(json.dumps(line))
-    dec.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

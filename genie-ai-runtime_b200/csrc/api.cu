@@ -48,6 +48,9 @@ DeviceCtx* ctx() {
     if (pr.major != 10) { set_error(JB_ERR_STATE, "device %d is sm_%d%d; this library is built for sm_100a only", dev, pr.major, pr.minor); return nullptr; }
     c->sm_count = pr.multiProcessorCount;
     c->max_smem_optin = (int)pr.sharedMemPerBlockOptin;
+    // two CTAs per SM: half the SM's shared memory each, minus the per-CTA system reservation and 2 KB of static arrays
+    c->gemv_smem_budget = (int)(pr.sharedMemPerMultiprocessor / 2 - pr.reservedSharedMemPerBlock) - 2048;
+    c->gemv_smem_budget &= ~127;
     if (cudaMalloc(&c->d_status, 256) != cudaSuccess) { cuda_error(cudaGetLastError(), "cudaMalloc(status)"); return nullptr; }
     cudaMemset(c->d_status, 0, 256);
     c->device = dev;
@@ -191,6 +194,7 @@ int jllm_b200_device_status(void* stream) {
 }
 long long jllm_b200_launch_count(void) { return g_launches.load(); }
 void jllm_b200_set_pdl(int on) { g_pdl.store(on ? 1 : 0); }
+void jllm_b200_debug_gemv_trace(unsigned long long* device_buf) { gemv_set_trace(device_buf); }
 
 const void* jllm_b200_resolve_mapped_weight_device_ptr(const void* p) {
     if (!p || !g_region.host || !g_region.dev) return nullptr;

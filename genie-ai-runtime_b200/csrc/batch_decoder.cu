@@ -80,6 +80,7 @@ struct jllm_b200_batch_decoder {
     void* slab = nullptr;
     int kernels_per_step = 0;
     cudaGraphExec_t graph_exec = nullptr;   // one decode step from the device-side state
+    int host_pos = -1;                      // host mirror of the device-side position (-1 until generate has run): the bound of step_device
 };
 
 #define BCHK(call) do { const int rc__ = (call); if (rc__) return rc__; } while (0)
@@ -203,7 +204,9 @@ int jllm_b200_batch_decoder_generate(jllm_b200_batch_decoder* d, const int* host
     JB_CUDA(cudaMemsetAsync(d->state, 0, 64, st));
     for (auto& p : d->kv) p.clear();
     const int total_steps = n_prompt + (n_new > 0 ? n_new - 1 : 0);
+    d->host_pos = -1;
     for (int s = 0; s < total_steps; ++s) BCHK(bdec_enqueue_step(d, d->prompt_dev, n_prompt, st));
+    d->host_pos = total_steps;              // every step advances the device-side position by one
     if (n_new > 0 && host_out)
         JB_CUDA(cudaMemcpyAsync(host_out, d->out_tokens + (size_t)(n_prompt - 1) * B, (size_t)n_new * B * sizeof(int), cudaMemcpyDeviceToHost, st));
     JB_CUDA(cudaStreamSynchronize(st));
@@ -212,6 +215,10 @@ int jllm_b200_batch_decoder_generate(jllm_b200_batch_decoder* d, const int* host
 /* one more step from the device-side state (after generate): no host copy, no wait */
 int jllm_b200_batch_decoder_step_device(jllm_b200_batch_decoder* d, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
+    // The position lives on the device; the host mirror keeps a step from writing K/V rows past the per-stream pools.
+    if (d->host_pos < 0) return set_error(JB_ERR_STATE, "batch decoder: step_device before generate");
+    if (d->host_pos >= d->m.max_context) return set_error(JB_ERR_LIMIT, "batch decoder: position %d is outside the context of %d", d->host_pos, d->m.max_context);
+    ++d->host_pos;
     if (st == nullptr || st == cudaStreamLegacy) return bdec_enqueue_step(d, nullptr, 0, st);   // the default stream cannot be captured
     if (!d->graph_exec) {
         cudaGraph_t g = nullptr;

@@ -46,6 +46,8 @@ struct DeviceCtx {
     void*  mmq_act = nullptr; size_t mmq_act_bytes = 0;
     RopeTable rope[8]; int n_rope = 0;
     bool gemv_attr[4] = { false, false, false, false };
+    bool gemv_chain_attr = false;
+    int  gemv_smem_budget = 0;          // dynamic shared memory of a GEMV CTA that shares its SM with one other CTA
 };
 DeviceCtx* ctx();                        // context of the current device (created on first use)
 
@@ -96,6 +98,31 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
     return false;
 }
+// Guard of a polling loop on memory that another rank (or CTA) writes.  The wait is given up — and JB_ERR_TIMEOUT
+// recorded in the status word — after `max_polls` polls or `max_ns` nanoseconds, whichever comes first.  A wait that
+// starts when the status word already holds a timeout gives up at its first miss: once one wait of a step has run
+// out, the later waits of that step (every element, kernel and layer behind it) must not each spin their full bound
+// again, so a dead peer costs one bound per step, not one per wait.
+struct PollGuard {
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    bool dead;
+    __device__ __forceinline__ explicit PollGuard(const int* status) {
+        dead = *reinterpret_cast<const volatile int*>(status) == JB_ERR_TIMEOUT;
+    }
+    // call after a miss; false = stop waiting and use whatever is there
+    __device__ __forceinline__ bool again(int* status, uint32_t sleep_ns = 20, uint32_t max_polls = (1u << 21), unsigned long long max_ns = 500000000ull) {
+        if (dead) return false;
+        if ((++polls & 63u) == 0u) {
+            const unsigned long long t = global_ns();
+            if (!t0) t0 = t;
+            else if (t - t0 > max_ns) polls = max_polls;
+        }
+        if (polls >= max_polls) { atomicExch(status, JB_ERR_TIMEOUT); dead = true; return false; }
+        __nanosleep(sleep_ns);
+        return true;
+    }
+};
 // 1-D bulk copy global -> shared through the TMA unit; both addresses 16-byte aligned,
 // size a multiple of 16 bytes; completion is signalled on `bar` by byte count.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {

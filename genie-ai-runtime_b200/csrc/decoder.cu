@@ -514,6 +514,19 @@ int jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream) {
     return h[1];
 }
 int jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d) { return d->kernels_per_step; }
+int jllm_b200_decoder_recorded_tokens(jllm_b200_decoder* d, int first, int n, int* host_out, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    int h[3] = { 0, 0, 0 };
+    if (cudaMemcpyAsync(h, d->state, sizeof h, cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+    const int have = h[2] < d->out_cap ? h[2] : d->out_cap;
+    if (host_out && n > 0 && first >= 0 && first < have) {
+        const int m = first + n <= have ? n : have - first;
+        if (cudaMemcpyAsync(host_out, d->out_tokens + first, (size_t)m * sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+        cudaStreamSynchronize(st);
+    }
+    return h[2];
+}
 const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which) {
     switch (which) {
         case 0: return d->x;   case 1: return d->x2; case 2: return d->q;  case 3: return d->k; case 4: return d->v;

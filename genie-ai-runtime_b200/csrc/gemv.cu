@@ -21,12 +21,21 @@
 //   * the same body runs as one phase of an optional chained launch (gemv_chain_kernel), and carries the
 //     tensor-parallel hooks: activations polled as {value, epoch} packets, results pushed as packets to every rank.
 #include "gemv.cuh"
+#include <cstdio>
+#include <cstdlib>
 
 namespace jb {
 
-constexpr int GV_MAXWARPS = 20;                // one CTA per SM; 4 to 18 warps, chosen per launch (gv_configure)
+// Stream kernel: a CTA takes HALF an SM (at most 14 warps at 72 registers, half the shared memory), and a launch puts
+// one CTA on every SM.  The other half is where the CTAs of the NEXT kernel in the stream become resident as soon as
+// this one has issued griddepcontrol.launch_dependents: they set up their barriers and start the bulk copies of their
+// first row groups while this kernel is still computing, so HBM keeps streaming across kernel boundaries.
+constexpr int GV_MAXWARPS = 14;
 constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
+constexpr int GV_CHAINWARPS = 20;              // the chain kernel keeps a whole SM per CTA (its phases overlap inside one launch)
+constexpr int GV_CHAINTHREADS = GV_CHAINWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
+constexpr int GV_NTRACE = 8;                   // time stamps per CTA of a traced launch
 
 struct GvSegDev {
     const uint8_t* W; void* y; int M; int type;
@@ -42,7 +51,9 @@ struct GvParams {
     const uint2* residual_pk;   // residual as packets of this rank's own region (tensor-parallel chain), else null
     int do_norm; const void* norm_w; int norm_w_fp32; float eps;
     int32_t* dbg_dots; int* status;
+    unsigned long long* trace;  // diagnostic launches only: GV_NTRACE time stamps per CTA
     int slot_bytes, nslots, needA, needB, paired_rows, nwarps;
+    int nchunk, chunk_blocks;   // a row group is streamed as nchunk tasks of chunk_blocks super-blocks per row (nchunk > 1 only with R = 1)
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
     long long total_bytes;      // Σ over segments of (row groups x bytes per group)
     int tp_wait_on, tp_push_on;
@@ -52,6 +63,8 @@ struct GvParams {
     GemvTpPush tpp;
 };
 
+static thread_local unsigned long long* g_trace = nullptr;    // diagnostic: time stamps of the next launch (gemv_set_trace)
+void gemv_set_trace(unsigned long long* t) { g_trace = t; }
 static thread_local bool g_tp_wait_set = false, g_tp_push_set = false;
 static thread_local GemvTpWait g_tp_wait;
 static thread_local GemvTpPush g_tp_push;
@@ -82,13 +95,12 @@ __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epo
     }
     const uint4* src = reinterpret_cast<const uint4*>(p.x) + 4 * it;
     uint4 q[4];
-    for (uint32_t tries = 0;; ++tries) {
+    PollGuard guard(p.status);
+    for (;;) {
         bool ok = true;
         #pragma unroll
         for (int i = 0; i < 4; ++i) { q[i] = __ldcv(src + i); ok = ok && q[i].y == epoch && q[i].w == epoch; }
-        if (ok) break;
-        if (tries > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
-        __nanosleep(20);
+        if (ok || !guard.again(p.status)) break;
     }
     #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -97,8 +109,29 @@ __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epo
     }
 }
 
+// The eight norm weights of staging item `it` (eight consecutive activations).
+__device__ __forceinline__ void gv_norm_w8(const GvParams& p, int it, float (&wn)[8]) {
+    if (p.norm_w_fp32) {
+        #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + 8 * it + 4 * h);
+            wn[4 * h] = w4.x; wn[4 * h + 1] = w4.y; wn[4 * h + 2] = w4.z; wn[4 * h + 3] = w4.w;
+        }
+    } else {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.norm_w) + 8 * it);
+        const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            wn[2 * i] = a.x; wn[2 * i + 1] = a.y;
+        }
+    }
+}
+
+// `wpre`: the norm weights of this thread's first staging item, loaded by the caller before it waited for the
+// producer kernel (they do not depend on it), so their trip to L2 is off the critical path; have_pre = false: none.
 template <int XM>
-__device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red) {
+__device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red, const float (&wpre)[8], bool have_pre) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nw_cta = blockDim.x >> 5;
     const int K = p.K;
     const uint32_t epoch = p.tp_wait_on ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
@@ -131,20 +164,11 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         gv_load8(p, it, epoch, v);
         if (p.do_norm) {
             float wn[8];
-            if (p.norm_w_fp32) {
+            if (have_pre && it == tid) {
                 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + 8 * it + 4 * h);
-                    wn[4 * h] = w4.x; wn[4 * h + 1] = w4.y; wn[4 * h + 2] = w4.z; wn[4 * h + 3] = w4.w;
-                }
+                for (int i = 0; i < 8; ++i) wn[i] = wpre[i];
             } else {
-                const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.norm_w) + 8 * it);
-                const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
-                #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                    wn[2 * i] = a.x; wn[2 * i + 1] = a.y;
-                }
+                gv_norm_w8(p, it, wn);
             }
             #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i], rrms), wn[i])));
@@ -321,8 +345,10 @@ __device__ __forceinline__ float q6k_item(uint32_t sb, int n, int c, int kblk, c
 // (4 per super-block), each lane adds its terms into the accumulator of the row the item belongs to.
 // Item i of the group is (row i / U, block (i % U) / 4, sub-item i % 4); 32 and U are multiples of 4, so a
 // lane's sub-item never changes.
+// `rb_` = bytes between consecutive rows in shared memory, `U_` = items per row held there (a chunk of the row when the
+// row is streamed in several tasks: its first super-block is kb0), `Ufull` = items of a whole row.
 template <int XM, int TYPE, bool DBG>
-__device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, int U_, int lane, const GvX& X,
+__device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, int U_, int kb0, int Ufull, int lane, const GvX& X,
                                              float (&acc)[4], int32_t* dbg) {
     const unsigned rb = (unsigned)rb_, U = (unsigned)U_, total = (unsigned)nrw * U;
     constexpr unsigned BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
@@ -337,13 +363,13 @@ __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, in
         float term;
         if (TYPE == T_Q4K) {
             int d0, d1;
-            term = q4k_item<XM>(sb, sub, (int)blk, X, d0, d1);
-            if (DBG && dbg && valid) { int32_t* o = dbg + (size_t)rl * (2 * U) + blk * 8 + 2 * sub; o[0] = d0; o[1] = d1; }
+            term = q4k_item<XM>(sb, sub, kb0 + (int)blk, X, d0, d1);
+            if (DBG && dbg && valid) { int32_t* o = dbg + (size_t)rl * (2 * Ufull) + (kb0 + blk) * 8 + 2 * sub; o[0] = d0; o[1] = d1; }
         } else {
             int dots[4];
-            term = q6k_item<XM>(sb, sub >> 1, sub & 1, (int)blk, X, dots);
+            term = q6k_item<XM>(sb, sub >> 1, sub & 1, kb0 + (int)blk, X, dots);
             if (DBG && dbg && valid) {
-                int32_t* o = dbg + (size_t)rl * (4 * U) + blk * 16 + 8 * (sub >> 1) + (sub & 1);
+                int32_t* o = dbg + (size_t)rl * (4 * Ufull) + (kb0 + blk) * 16 + 8 * (sub >> 1) + (sub & 1);
                 o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
             }
         }
@@ -360,19 +386,25 @@ __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, in
 struct GvRange { int gf[3], gl[3]; };   // row groups [gf, gl) of each segment owned by this CTA
 
 // task `u` of warp `warp` -> segment, first row, number of rows
-__device__ __forceinline__ bool gv_task(const GvParams& p, const GvRange& rg, int warp, int u, int& seg, int& row0, int& nrows) {
+struct GvTask { int seg, row0, nrows, kb0, kb1; bool last; };   // rows [row0, row0+nrows) x super-blocks [kb0, kb1); last chunk of the rows
+
+__device__ __forceinline__ bool gv_task(const GvParams& p, const GvRange& rg, int warp, int u_, GvTask& t) {
     int g;
+    int& seg = t.seg; int& row0 = t.row0; int& nrows = t.nrows;
+    const int c = p.nchunk > 1 ? u_ % p.nchunk : 0, u = p.nchunk > 1 ? u_ / p.nchunk : u_;
+    const int nb = p.K / QK_K;
+    t.kb0 = c * p.chunk_blocks; t.kb1 = min(nb, t.kb0 + p.chunk_blocks); t.last = c == p.nchunk - 1;
     if (p.paired_rows) {               // (gate group, up group) of the same rows, back to back on one warp
         seg = u & 1;
         g = rg.gf[0] + warp + p.nwarps * (u >> 1);
         if (g >= rg.gl[0]) return false;
     } else {
-        int t = warp + p.nwarps * u;
+        int k = warp + p.nwarps * u;
         seg = -1;
         #pragma unroll
         for (int i = 0; i < 3; ++i) {
             const int cnt = rg.gl[i] - rg.gf[i];
-            if (seg < 0 && i < p.nseg) { if (t < cnt) { seg = i; g = rg.gf[i] + t; } else t -= cnt; }
+            if (seg < 0 && i < p.nseg) { if (k < cnt) { seg = i; g = rg.gf[i] + k; } else k -= cnt; }
         }
         if (seg < 0) return false;
     }
@@ -382,9 +414,18 @@ __device__ __forceinline__ bool gv_task(const GvParams& p, const GvRange& rg, in
     return nrows > 0;
 }
 
-__device__ __forceinline__ void gv_issue(const GvParams& p, int seg, int row0, int nrows, uint8_t* slot, uint64_t* bar) {
-    const GvSegDev& s = p.seg[seg];
-    const uintptr_t g0 = (uintptr_t)s.W + (size_t)row0 * s.rb, g1 = g0 + (size_t)nrows * s.rb;
+// global byte range of a task: whole rows, or (one row only) the super-blocks [kb0, kb1) of it
+__device__ __forceinline__ void gv_span(const GvParams& p, const GvTask& t, uintptr_t& g0, uintptr_t& g1) {
+    const GvSegDev& s = p.seg[t.seg];
+    const int bb = s.type == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    g0 = (uintptr_t)s.W + (size_t)t.row0 * s.rb + (size_t)(p.nchunk > 1 ? t.kb0 * bb : 0);
+    g1 = p.nchunk > 1 ? g0 + (size_t)(t.kb1 - t.kb0) * bb : g0 + (size_t)t.nrows * s.rb;
+}
+
+__device__ __forceinline__ void gv_issue(const GvParams& p, const GvTask& t, uint8_t* slot, uint64_t* bar) {
+    const GvSegDev& s = p.seg[t.seg];
+    uintptr_t g0, g1;
+    gv_span(p, t, g0, g1);
     const uintptr_t a0 = g0 & ~(uintptr_t)15;
     const uintptr_t endw = ((uintptr_t)s.W + (size_t)s.M * s.rb) & ~(uintptr_t)15;
     uintptr_t a1 = (g1 + 15) & ~(uintptr_t)15;
@@ -402,22 +443,28 @@ __device__ __forceinline__ void gv_prefetch(const GvParams& p, const GvRange& rg
     if (lane == 0) {
         if (later) fence_proxy_async();       // the slots were read with ordinary loads in the phase before
         for (int u = 0; u < p.nslots; ++u) {
-            int seg, row0, nrows;
-            if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
-            gv_issue(p, seg, row0, nrows, ring + (unsigned)u * (unsigned)p.slot_bytes, &full[warp][u]);
+            GvTask t;
+            if (!gv_task(p, rg, warp, u, t)) break;
+            gv_issue(p, t, ring + (unsigned)u * (unsigned)p.slot_bytes, &full[warp][u]);
         }
     }
     __syncwarp();
 }
 
 // one GEMV launch, or one phase of a chain (then the caller has prefetched and synchronised the grid)
+__device__ __forceinline__ void gv_stamp(const GvParams& p, int k) {
+    p.trace[(size_t)blockIdx.x * GV_NTRACE + k] = global_ns();
+}
+
 template <int XM, bool DBG>
-__device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], float* red, const GvRange& rg, uint32_t& par) {
+__device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], float* red, const GvRange& rg, uint32_t& par,
+                                         const float (&wpre)[8], bool have_pre) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
-    stage_x<XM>(p, smem, red);
+    stage_x<XM>(p, smem, red, wpre, have_pre);
     __syncthreads();
+    if (DBG && p.trace && tid == 0) gv_stamp(p, 3);
     if (warp >= p.nwarps) return;            // chain phases may use fewer warps than the CTA has (larger staging rings)
 
     const uint32_t sm0 = smem_u32(smem);
@@ -425,19 +472,22 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
     const uint32_t push_epoch = p.tp_push_on ? p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u : 0u;
     bool timed_out = false;
     float gate_keep[4] = { 0.f, 0.f, 0.f, 0.f };
+    float acc[4] = { 0.f, 0.f, 0.f, 0.f };       // lives across the chunks of a row
     for (int u = 0;; ++u) {
-        int seg, row0, nrows;
-        if (!gv_task(p, rg, warp, u, seg, row0, nrows)) break;
+        GvTask t;
+        if (!gv_task(p, rg, warp, u, t)) break;
+        const int seg = t.seg, row0 = t.row0, nrows = t.nrows;
         const int slot = u % p.nslots;
         // a wait that runs out is recorded and the loop carries on; later waits are skipped.  `par` holds, per slot
         // barrier, the parity of the phase its next copy completes (barriers live across the phases of a chain).
         if (!timed_out && !mbar_wait_bounded(&full[warp][slot], (par >> slot) & 1u)) timed_out = true;
         par ^= 1u << slot;
+        if (DBG && p.trace && tid == 0 && u == 0) gv_stamp(p, 4);
         const GvSegDev& s = p.seg[seg];
-        const uintptr_t g0 = (uintptr_t)s.W + (size_t)row0 * s.rb;
+        uintptr_t g0, g1;
+        gv_span(p, t, g0, g1);
         uint8_t* rows = ring + (unsigned)slot * (unsigned)p.slot_bytes + (unsigned)(g0 & 15);
         {   // bytes between the last 16-byte boundary inside the tensor and its end
-            const uintptr_t g1 = g0 + (size_t)nrows * s.rb;
             const uintptr_t endw = ((uintptr_t)s.W + (size_t)s.M * s.rb) & ~(uintptr_t)15;
             if (g1 > endw) {     // warp-uniform
                 const int tail = (int)(g1 - endw);
@@ -445,22 +495,23 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
                 __syncwarp();
             }
         }
-        float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-        int32_t* dbg = (DBG && seg == 0) ? p.dbg_dots + (size_t)row0 * (s.type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
-        if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, s.U, lane, X, acc, dbg);
-        else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, s.U, lane, X, acc, dbg);
+        int32_t* dbg = (DBG && seg == 0 && p.dbg_dots) ? p.dbg_dots + (size_t)row0 * (s.type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
+        const int Uc = p.nchunk > 1 ? 4 * (t.kb1 - t.kb0) : s.U, kb0 = p.nchunk > 1 ? t.kb0 : 0;
+        if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
+        else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
         __syncwarp();                            // the warp is done reading this slot
         if (lane == 0) {
-            int seg2, row2, nrows2;
-            if (gv_task(p, rg, warp, u + p.nslots, seg2, row2, nrows2)) {
+            GvTask t2;
+            if (gv_task(p, rg, warp, u + p.nslots, t2)) {
                 fence_proxy_async();
-                gv_issue(p, seg2, row2, nrows2, ring + (unsigned)slot * (unsigned)p.slot_bytes, &full[warp][slot]);
+                gv_issue(p, t2, ring + (unsigned)slot * (unsigned)p.slot_bytes, &full[warp][slot]);
             }
         }
+        if (!t.last) continue;                   // more super-blocks of these rows follow in the next task
         // row sums; lane r finishes row r
         float mine = 0.f;
         #pragma unroll
-        for (int r = 0; r < 4; ++r) { const float v = warp_sum(acc[r]); if (lane == r) mine = v; }
+        for (int r = 0; r < 4; ++r) { const float v = warp_sum(acc[r]); if (lane == r) mine = v; acc[r] = 0.f; }
         if (p.out_mode == 3 && seg == 0) {       // gate values stay in registers until the matching up rows arrive
             #pragma unroll
             for (int r = 0; r < 4; ++r) gate_keep[r] = __shfl_sync(0xFFFFFFFFu, __half2float(__float2half_rn(mine)), r);
@@ -475,11 +526,10 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
                 float res;
                 if (p.residual_pk) {          // written earlier in this launch by another CTA of this rank: valid once its epoch matches
                     uint2 q;
-                    for (uint32_t tries = 0;; ++tries) {
+                    PollGuard guard(p.status);
+                    for (;;) {
                         q = __ldcv(p.residual_pk + row);
-                        if (q.y == push_epoch) break;
-                        if (tries > (1u << 21)) { atomicExch(p.status, JB_ERR_TIMEOUT); break; }
-                        __nanosleep(20);
+                        if (q.y == push_epoch || !guard.again(p.status)) break;
                     }
                     res = __half2float(__ushort_as_half((unsigned short)(q.x & 0xFFFFu)));
                 } else {
@@ -501,6 +551,10 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
         }
     }
     if (timed_out && lane == 0) atomicExch(p.status, JB_ERR_TIMEOUT);
+    if (DBG && p.trace && lane == 0) {
+        if (warp == 0) gv_stamp(p, 5);
+        atomicMax(&p.trace[(size_t)blockIdx.x * GV_NTRACE + 6], global_ns());       // last warp of the CTA to finish
+    }
 }
 
 
@@ -532,10 +586,13 @@ __device__ __forceinline__ GvRange gv_range(const GvParams& p) {
 }
 
 template <int XM, bool DBG>
-__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+__global__ void __launch_bounds__(GV_MAXTHREADS, 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
     __shared__ float red[GV_MAXWARPS];
+    if (DBG && p.trace && threadIdx.x == 0) { gv_stamp(p, 0); p.trace[(size_t)blockIdx.x * GV_NTRACE + 6] = 0ull; }
+    pdl_launch();                // the next kernel's CTAs may take the free half of every SM now; they wait for our completion
+                                 // before they touch our outputs
     const GvRange rg = gv_range(p);
     if ((threadIdx.x & 31) == 0) {
         for (int s = 0; s < p.nslots; ++s) mbar_init(&full[threadIdx.x >> 5][s], 1);
@@ -543,10 +600,14 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
     }
     __syncwarp();
     gv_prefetch(p, rg, smem, full, threadIdx.x >> 5, threadIdx.x & 31, false);   // weights do not depend on the previous kernel
-    pdl_launch();                // dependents may be scheduled; they wait for our completion before touching our outputs
+    float wpre[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+    const bool have_pre = p.do_norm && (int)threadIdx.x < p.K / 8;
+    if (have_pre) gv_norm_w8(p, threadIdx.x, wpre);                               // nor do the norm weights
+    if (DBG && p.trace && threadIdx.x == 0) gv_stamp(p, 1);
     pdl_wait();                  // x (and the residual) come from the kernel before us
+    if (DBG && p.trace && threadIdx.x == 0) gv_stamp(p, 2);
     uint32_t par = 0;
-    gv_phase<XM, DBG>(p, smem, full, red, rg, par);
+    gv_phase<XM, DBG>(p, smem, full, red, rg, par, wpre, have_pre);
 }
 
 // ── chain: up to four GEMVs that feed one another (Wo -> gate/up -> W_down -> next layer's Q/K/V) in ONE launch ──
@@ -557,6 +618,7 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_stream_kernel(const __g
 // recorded in the status word (the phase then runs on whatever has arrived).  All CTAs must be resident at the same
 // time: the grid never exceeds the number of SMs and a CTA takes a whole SM.
 struct GvChain { int n; unsigned int* bar; GvParams ph[4]; };
+static_assert(sizeof(GvChain) <= 4000, "kernel parameter space");
 
 __device__ __forceinline__ void gv_grid_barrier(unsigned int* bar, int* status) {
     __threadfence();
@@ -581,10 +643,11 @@ __device__ __forceinline__ void gv_grid_barrier(unsigned int* bar, int* status) 
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_chain_kernel(const __grid_constant__ GvChain c) {
+__global__ void __launch_bounds__(GV_CHAINTHREADS, 1) gemv_chain_kernel(const __grid_constant__ GvChain c) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
-    __shared__ float red[GV_MAXWARPS];
+    __shared__ __align__(8) uint64_t full[GV_CHAINWARPS][GV_MAXSLOT];
+    __shared__ float red[GV_CHAINWARPS];
+    const float wpre[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {                          // slot barriers of every warp, for all phases
         for (int s = 0; s < GV_MAXSLOT; ++s) mbar_init(&full[warp][s], 1);
@@ -605,8 +668,8 @@ __global__ void __launch_bounds__(GV_MAXTHREADS, 1) gemv_chain_kernel(const __gr
             if (c.bar) gv_grid_barrier(c.bar, p.status); // ... and every CTA with its rows: the next activation vector is complete
             // (no barrier when every input of the phase arrives as packets: each element carries its own arrival mark)
         }
-        if (p.xmode) gv_phase<1, false>(p, smem, full, red, rg, par);
-        else         gv_phase<0, false>(p, smem, full, red, rg, par);
+        if (p.xmode) gv_phase<1, false>(p, smem, full, red, rg, par, wpre, false);
+        else         gv_phase<0, false>(p, smem, full, red, rg, par, wpre, false);
     }
 }
 
@@ -655,7 +718,9 @@ int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const
 
 // Fills the device-side argument block for one GEMV.  max_warps caps the warps per CTA (a chain runs all its phases
 // with one block size); on return smem_bytes / grid hold what this GEMV wants.
-static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& smem_bytes, int& grid, bool& empty) {
+// `budget` = dynamic shared memory a CTA may take; `two_per_sm`: a large product may put two of its own CTAs on every SM
+// (stream kernel only), small ones leave the second half of the SM to the next kernel.
+static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budget, bool two_per_sm, size_t& smem_bytes, int& grid, bool& empty) {
     DeviceCtx* cx = ctx();
     if (!cx) return JB_ERR_CUDA;
     empty = false;
@@ -694,8 +759,12 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
     // memory is split into one staging ring per warp.  Warps per CTA and rows per group are chosen together to
     // minimise the longest chain of work any warp has to run: (row groups of its CTA / warps, rounded up) x
     // (32-lane rounds a group takes, plus half a round of per-group overhead).  Ties go to more warps, larger groups.
-    const int budget = cx->max_smem_optin - 2048;             // opt-in limit minus this kernel's static shared memory
     const int U = nb * 4;
+    // CTAs of this launch: one per SM; two per SM when every SM has far more to stream than one CTA's rings hold
+    // (the logits product), where filling the machine matters more than leaving room for the next kernel.
+    long long all_bytes = 0;
+    for (int i = 0; i < a.nseg; ++i) all_bytes += (long long)a.seg[i].M * nb * block_bytes(a.seg[i].type);
+    const int ncta = (two_per_sm && all_bytes > (long long)cx->sm_count * 6 * budget) ? 2 * cx->sm_count : cx->sm_count;
     int rb_max = 0;
     for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
     uint32_t off = 0;
@@ -707,26 +776,38 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
     p.off_gate = off;
     off = (off + 127) & ~127u;
     p.off_slots = off;
-    static const int warp_choices[] = { 20, 19, 18, 17, 16, 14, 12, 10, 8, 6, 4 };
-    int best_w = 0, best_R = 0; double best_cost = 1e30;
+    static const int warp_choices[] = { 20, 19, 18, 17, 16, 14, 13, 12, 11, 10, 9, 8, 6, 4 };
+    int best_w = 0, best_R = 0, best_C = 1; double best_cost = 1e30;
+    int bb_max = 0;
+    for (int i = 0; i < a.nseg; ++i) bb_max = block_bytes(a.seg[i].type) > bb_max ? block_bytes(a.seg[i].type) : bb_max;
     for (int nwarps : warp_choices) {
         if (nwarps > max_warps) continue;
         const int ring = (budget - (int)off) / nwarps;        // bytes of staging ring per warp
         const int slot_cap = ring / 2;                        // at least two slots per warp
-        for (int cand = 4; cand >= 1; --cand) {
-            if ((long long)cand * rb_max + 16 + 127 > slot_cap) continue;
+        // candidates: R = 4..1 whole rows per task; or one row streamed as C = 2..8 chunks of super-blocks by the same
+        // warp (long rows, where even one row does not fit half a ring)
+        for (int cand = 4; cand >= -8; --cand) {
+            if (cand == 0 || cand == -1) continue;
+            const int R = cand > 0 ? cand : 1, C = cand > 0 ? 1 : -cand;
+            if (C > 1 && (a.out_mode == 3 || C > nb)) continue;
+            const int cb = (nb + C - 1) / C;                  // super-blocks per chunk
+            if (C > 1 && (nb + cb - 1) / cb != C) continue;   // this chunk count would leave an empty last chunk
+            const long long task_bytes = C > 1 ? (long long)cb * bb_max : (long long)R * rb_max;
+            if (task_bytes + 16 + 127 > slot_cap) continue;
             long long groups = 0;       // units a warp takes one at a time: row groups, or (gate, up) pairs of groups
-            for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg); ++i) groups += (a.seg[i].M + cand - 1) / cand;
-            const long long per_cta = (groups + cx->sm_count - 1) / cx->sm_count;
+            for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg); ++i) groups += (a.seg[i].M + R - 1) / R;
+            const long long per_cta = (groups + ncta - 1) / ncta;
             const long long chain = (per_cta + nwarps - 1) / nwarps;
-            const double cost = (double)chain * ((cand * U + 31) / 32 + 0.5) * (a.out_mode == 3 ? 2 : 1);
-            if (cost < best_cost - 1e-9) { best_cost = cost; best_w = nwarps; best_R = cand; }
+            const int items = C > 1 ? cb * 4 : R * U;
+            const double cost = (double)chain * C * ((items + 31) / 32 + 0.5) * (a.out_mode == 3 ? 2 : 1);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best_w = nwarps; best_R = R; best_C = C; }
         }
     }
     if (!best_w) return set_error(JB_ERR_LIMIT, "gemv: one row group does not fit the staging ring (K=%d)", K);
     {
         const int nwarps = best_w, R = best_R;
         const int ring = (budget - (int)off) / nwarps;
+        p.nchunk = best_C; p.chunk_blocks = (nb + best_C - 1) / best_C;
         int slot = 0;
         p.total_bytes = 0;
         long long groups_total = 0;
@@ -736,7 +817,7 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
             d.rb = nb * block_bytes(d.type);
             d.U = U;
             d.R = R; d.trc = nwarps * R;
-            const int need = ((d.R * d.rb + 16 + 127) / 128) * 128;
+            const int need = (((best_C > 1 ? p.chunk_blocks * block_bytes(d.type) : d.R * d.rb) + 16 + 127) / 128) * 128;
             slot = need > slot ? need : slot;
             const long long groups = (d.M + d.R - 1) / d.R;
             p.total_bytes += groups * d.R * d.rb;
@@ -749,9 +830,13 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, size_t& s
         p.nwarps = nwarps;
         smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
-        grid = cx->sm_count;                                   // every SM streams its share, however few groups that is
+        grid = ncta;                                           // every SM streams its share, however few groups that is
         if (grid > groups_total) grid = (int)groups_total;
         if (grid < 1) grid = 1;
+        static const bool verbose = getenv("JLLM_B200_GEMV_DEBUG") != nullptr;
+        if (verbose)
+            fprintf(stderr, "[gemv] K=%d nseg=%d M0=%d type0=%d xmode=%d out=%d: grid %d x %d warps, R=%d chunks=%d x %d blocks, %d slots of %d B, smem %zu\n",
+                    K, a.nseg, a.seg[0].M, a.seg[0].type, a.xmode, a.out_mode, grid, nwarps, R, p.nchunk, p.chunk_blocks, p.nslots, p.slot_bytes, smem_bytes);
         return JB_OK;
     }
 }
@@ -765,13 +850,16 @@ int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
     g_tp_wait_set = g_tp_push_set = false;
     GvParams p;
     size_t smem_bytes = 0; int grid = 0; bool empty = false;
-    const int rc = gv_configure(a, p, GV_MAXWARPS, smem_bytes, grid, empty);
+    const int rc = gv_configure(a, p, GV_MAXWARPS, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
     if (rc || empty) return rc;
-    auto kern = a.dbg_dots ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
-                           : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
-    const int ki = (a.xmode ? 1 : 0) + (a.dbg_dots ? 2 : 0);
+    p.trace = g_trace; g_trace = nullptr;
+    const bool dbg = a.dbg_dots || p.trace;
+    auto kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
+                    : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
+    const int ki = (a.xmode ? 1 : 0) + (dbg ? 2 : 0);
     if (!cx->gemv_attr[ki]) {
-        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 2048));
+        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->gemv_smem_budget));
+        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         cx->gemv_attr[ki] = true;
     }
     JB_CUDA(launch_k(kern, dim3(grid), dim3(p.nwarps * 32), smem_bytes, st, pdl_enabled(), p));
@@ -788,25 +876,24 @@ int launch_gemv_chain(const GemvArgs* args, int n, unsigned int* bar, cudaStream
     for (int i = 1; i < n && !bar; ++i)
         if (!args[i].tp_wait || (args[i].out_mode == 2 && !args[i].residual_pk))
             return set_error(JB_ERR_ARG, "gemv chain: without a grid barrier every input of a later phase must arrive as packets");
-    static GvChain c;                     // 1 KB of parameters: built in place
+    GvChain c;
     c.n = n; c.bar = bar;
     size_t smem_max = 0;
     for (int i = 0; i < n; ++i) {
         if (args[i].dbg_dots) return set_error(JB_ERR_ARG, "gemv chain: no debug output");
         size_t smem_bytes = 0; int grid = 0; bool empty = false;
-        const int rc = gv_configure(args[i], c.ph[i], GV_MAXWARPS, smem_bytes, grid, empty);
+        const int rc = gv_configure(args[i], c.ph[i], GV_CHAINWARPS, cx->max_smem_optin - 2048, false, smem_bytes, grid, empty);
         if (rc) return rc;
         if (empty) return set_error(JB_ERR_ARG, "gemv chain: empty phase");
         c.ph[i].chained = 1;
         smem_max = smem_bytes > smem_max ? smem_bytes : smem_max;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    if (!cx->gemv_chain_attr) {
         JB_CUDA(cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->max_smem_optin - 2048));
-        attr_done = true;
+        cx->gemv_chain_attr = true;
     }
     // every phase splits its rows over the same grid: one CTA per SM, all resident together
-    JB_CUDA(launch_k(gemv_chain_kernel, dim3(cx->sm_count), dim3(GV_MAXTHREADS), smem_max, st, pdl_enabled(), c));
+    JB_CUDA(launch_k(gemv_chain_kernel, dim3(cx->sm_count), dim3(GV_CHAINTHREADS), smem_max, st, pdl_enabled(), c));
     count_launch();
     return JB_OK;
 }

@@ -36,11 +36,9 @@ __device__ __forceinline__ bool tp_wait_flags(const TpDev& tp, int point, uint32
     bool ok = true;
     if (tid < tp.world) {
         const uint32_t* f = reinterpret_cast<const uint32_t*>(tp.peer[tp.rank] + tp.flags_off) + point * TP_MAX_WORLD + tid;
-        uint32_t i = 0;
-        while (ld_acquire_sys(f) < epoch) {
-            if (++i > TP_WAIT_POLLS) { ok = false; break; }
-            __nanosleep(64);
-        }
+        PollGuard guard(tp.status);
+        while (ld_acquire_sys(f) < epoch)
+            if (!guard.again(tp.status, 64, TP_WAIT_POLLS)) { ok = false; break; }
     }
     return ok;
 }
@@ -61,11 +59,10 @@ __global__ void __launch_bounds__(256) tp_unpack_kernel(TpDev tp, __half* dst, i
     const uint2* src = reinterpret_cast<const uint2*>(tp.peer[tp.rank] + buf_off);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         uint2 q;
-        for (uint32_t tries = 0;; ++tries) {
+        PollGuard guard(tp.status);
+        for (;;) {
             q = __ldcv(src + i);
-            if (q.y == epoch) break;
-            if (tries > TP_WAIT_POLLS) { atomicExch(tp.status, JB_ERR_TIMEOUT); break; }
-            __nanosleep(32);
+            if (q.y == epoch || !guard.again(tp.status, 32, TP_WAIT_POLLS)) break;
         }
         dst[i] = __ushort_as_half((unsigned short)(q.x & 0xFFFFu));
     }

@@ -71,6 +71,13 @@ class Decoder:
         check(lib.jllm_b200_decoder_step_sync(C.c_void_p(self._h), C.c_void_p(host_pos_token.data_ptr()), C.c_void_p(host_next.data_ptr()),
                                               _stream(stream)))
 
+    def step_device(self, stream):
+        """Enqueues the next step from the position and token the previous step left on the device (no copy, no wait)."""
+        check(lib.jllm_b200_decoder_step_device(C.c_void_p(self._h), _stream(stream)))
+
+    def reset(self):
+        check(lib.jllm_b200_decoder_reset(C.c_void_p(self._h)))
+
     def logits(self):
         import torch
         ptr = lib.jllm_b200_decoder_logits(C.c_void_p(self._h))
@@ -89,6 +96,12 @@ class Decoder:
 
     def kernels_per_step(self):
         return int(lib.jllm_b200_decoder_kernels_per_step(C.c_void_p(self._h)))
+
+    def recorded_tokens(self, first=0, n=0, stream=None):
+        """(count recorded so far, ids [first, first+n) of the device-side record of every step's greedy token)."""
+        out = np.zeros(max(n, 1), np.int32)
+        cnt = int(lib.jllm_b200_decoder_recorded_tokens(C.c_void_p(self._h), C.c_int(first), C.c_int(n), out.ctypes.data_as(C.c_void_p), _stream(stream)))
+        return cnt, out[:max(0, min(n, cnt - first))]
 
 
 class BatchDecoder:

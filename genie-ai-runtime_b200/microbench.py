@@ -38,10 +38,7 @@ def blocks(ggml_type, rows, K, dev, gen):
     return img.reshape(rows, -1).contiguous()
 
 
-def main():
-    import torch
-    from __graft_entry__ import load_package
-    jb = load_package()
+def parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "mmq"])
     ap.add_argument("--type", type=int, default=12)
@@ -57,9 +54,16 @@ def main():
     ap.add_argument("--norm", action="store_true", help="pair/triple: RMSNorm fused in front of the activation quantiser")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python every iteration instead of replaying a CUDA graph")
-    a = ap.parse_args()
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
+    ap.add_argument("--trace", action="store_true", help="GEMV kinds: record per-CTA time stamps of every launch (diagnostic kernel "
+                    "instantiation) and print where the time of a launch goes")
+    return ap
+
+
+def measure(jb, argv):
+    """One measurement; `argv` as on the command line (e.g. ["gemv", "--type", "12"]).  Returns the result record."""
+    import torch
+    a = parser().parse_args([str(v) for v in argv])
+    dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev)
     gen.manual_seed(1000)
     if a.no_pdl:
@@ -125,8 +129,18 @@ def main():
                              jb.flash_attention_decode_batched(out, q, ls[0], ls[1], ls[2], ls[3], ls[4], B, max(lens), nh, nkv, hd, scale, True, st))
         nbytes = per
         shape = dict(L=L, batch=B, copies=copies)
+    trace = None
+    if a.trace:
+        import ctypes as C
+        NCTA, NST = 2 * 148, 8
+        trace = torch.zeros((a.iters, NCTA, NST), dtype=torch.int64, device=dev)
+        plain = calls
+        def traced(i):
+            jb.lib.jllm_b200_debug_gemv_trace(C.c_void_p(trace[i].data_ptr()))
+            plain[i % len(plain)]()
+        calls = [lambda i=i: traced(i) for i in range(a.iters)]
     with torch.cuda.stream(st):
-        for i in range(max(a.warmup, len(calls))):
+        for i in range(max(a.warmup, len(calls)) if not a.trace else 0):
             calls[i % len(calls)]()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -149,9 +163,33 @@ def main():
             e1.record(st)
         torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / a.iters
+    if a.trace:
+        t = trace.cpu().numpy().astype(np.int64)              # [launch][cta][stamp], ns
+        rows = []
+        for i in range(2, a.iters):
+            live = t[i][:, 0] > 0
+            cur, prev = t[i][live], t[i - 1][t[i - 1][:, 0] > 0]
+            base = prev[:, 6].max()                             # the previous launch's last warp finishes
+            rows.append([cur[:, 0].min() - base, cur[:, 0].max() - base, cur[:, 1].max() - base, cur[:, 2].min() - base, cur[:, 2].max() - base,
+                         cur[:, 3].max() - base, cur[:, 4].min() - base, cur[:, 4].max() - base, cur[:, 5].max() - base, cur[:, 6].max() - base])
+        r = np.median(np.array(rows, np.float64), axis=0) / 1e3
+        names = ["entry_first", "entry_last", "copies_issued_last", "producer_done_first", "producer_done_last", "staged_last",
+                 "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done"]
+        print(json.dumps({"trace_us_after_previous_launch_finished(median)": {n: round(float(v), 2) for n, v in zip(names, r)},
+                          "ctas": int((t[2][:, 0] > 0).sum())}))
     extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else {}
-    print(json.dumps({"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes, **extra,
-                      "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "graph": not a.no_graph, "device_status": jb.device_status(st)}))
+    if a.no_pdl:
+        jb.lib.jllm_b200_set_pdl(1)
+    return {"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes, **extra,
+            "GBps": nbytes / us / 1e3, "pdl": not a.no_pdl, "graph": not a.no_graph, "device_status": jb.device_status(st)}
+
+
+def main():
+    import torch
+    from __graft_entry__ import load_package
+    jb = load_package()
+    torch.cuda.set_device(0)
+    print(json.dumps(measure(jb, sys.argv[1:])))
 
 
 if __name__ == "__main__":

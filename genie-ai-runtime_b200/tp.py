@@ -163,3 +163,14 @@ class TPDecoder:
 
     def kernels_per_step(self):
         return int(self._lib.jllm_b200_decoder_kernels_per_step(C.c_void_p(self._h)))
+
+    def reset(self):
+        from . import check
+        check(self._lib.jllm_b200_decoder_reset(C.c_void_p(self._h)))
+
+    def recorded_tokens(self, first=0, n=0, stream=None):
+        from . import _stream
+        out = np.zeros(max(n, 1), np.int32)
+        cnt = int(self._lib.jllm_b200_decoder_recorded_tokens(C.c_void_p(self._h), C.c_int(first), C.c_int(n), out.ctypes.data_as(C.c_void_p),
+                                                              _stream(stream)))
+        return cnt, out[:max(0, min(n, cnt - first))]

@@ -49,6 +49,11 @@ int         jllm_b200_device_status(void* stream);
 long long   jllm_b200_launch_count(void);        /* kernels launched by this library so far */
 void        jllm_b200_set_pdl(int on);           /* programmatic dependent launch on/off (default on) */
 
+/* Diagnostic: the NEXT GEMV-family call on this thread also records eight %globaltimer stamps (ns) per CTA into
+ * device_buf[cta * 8 + k]: 0 kernel entry, 1 first bulk copies issued, 2 producer kernel complete, 3 activation vector
+ * staged, 4 first row group landed, 5 warp 0 done, 6 last warp done.  device_buf needs 8 x 2 x SM-count entries. */
+void        jllm_b200_debug_gemv_trace(unsigned long long* device_buf);
+
 /* ── mapped-weight registry — include/jllm_kernels.h:40-43, src/engine/model.cpp:39-66 ── */
 const void* jllm_b200_resolve_mapped_weight_device_ptr(const void* host_ptr);
 void        jllm_b200_register_mapped_weight_region(const void* host_base, const void* device_base, int64_t bytes);
@@ -229,6 +234,10 @@ int    jllm_b200_decoder_step_device(jllm_b200_decoder* d, void* stream);
 const float* jllm_b200_decoder_logits(jllm_b200_decoder* d);     /* device pointer, vocab_size floats */
 int    jllm_b200_decoder_last_token(jllm_b200_decoder* d, void* stream);   /* argmax of the last step (synchronises) */
 int    jllm_b200_decoder_kernels_per_step(jllm_b200_decoder* d);
+/* Every step appends its greedy token to a device-side record (cleared by _reset and _generate; it holds max_context + 8
+ * entries).  Returns how many tokens have been recorded (-1 on error; synchronises) and copies up to n of them, starting
+ * at index `first`, to host_out. */
+int    jllm_b200_decoder_recorded_tokens(jllm_b200_decoder* d, int first, int n, int* host_out, void* stream);
 /* Internal activation buffers of the last step, for tests: 0 x, 1 x2, 2 q, 3 k, 4 v, 5 attention out, 6 SwiGLU out,
  * 7 layer-0 K cache, 8 layer-0 K scales. */
 const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);

@@ -32,7 +32,7 @@ def test_every_declared_c_symbol_is_exported():
 
 def test_reference_cpp_symbols_are_exported():
     want = open(os.path.join(ROOT, "tests", "golden", "api_symbols.txt")).read().split()
-    assert len(want) >= 46
+    assert len(want) >= 50          # 46 free functions and non-const members + the four const members of KVCachePool
     missing = sorted(set(want) - _exported())
     assert not missing, missing
 
@@ -48,7 +48,7 @@ def test_no_oracle_or_torch_dependency_in_library():
 def test_pool_object_layout_matches_reference():
     """sizeof/offsets of the pool classes equal the reference's (the engine embeds them by value).
     Compiled against the reference header when the tree is present, else against recorded values."""
-    ref_inc = "/root/reference/include"
+    ref_inc = os.path.join(os.environ.get("JLLM_REFERENCE_DIR", "/root/reference"), "include")
     src = r'''
     #include <cstdio>
     #include <cstddef>
