@@ -11,6 +11,8 @@
 #include "attention.cuh"
 #include "mmq.cuh"
 #include <atomic>
+#include <new>
+#include <vector>
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
@@ -53,6 +55,8 @@ DeviceCtx* ctx() {
     c->gemv_smem_budget &= ~127;
     if (cudaMalloc(&c->d_status, 256) != cudaSuccess) { cuda_error(cudaGetLastError(), "cudaMalloc(status)"); return nullptr; }
     cudaMemset(c->d_status, 0, 256);
+    if (cudaMalloc(&c->attn_tickets, ATTN_TICKET_WORDS * sizeof(unsigned int)) != cudaSuccess) { cuda_error(cudaGetLastError(), "cudaMalloc(tickets)"); return nullptr; }
+    cudaMemset(c->attn_tickets, 0, ATTN_TICKET_WORDS * sizeof(unsigned int));
     c->device = dev;
     return c;
 }
@@ -334,6 +338,49 @@ int jllm_b200_flash_attention_decode_batched(void* o, const void* q, const void*
     c.out = H(o); c.q = CH(q); c.k_list = kl; c.v_list = vl; c.ks_list = ksl; c.vs_list = vsl; c.seq_lens = seq_lens; c.batch = batch;
     c.max_seq = max_seq; c.n_heads = nh; c.n_kv = nkv; c.hd = hd; c.chd = hd; c.scale = scale; c.kv_int8 = i8;
     return launch_attention(c, ST(s));
+}
+
+/* ── attention plan: tensor maps of a fixed set of INT8 caches, built once on the host ── */
+struct jllm_b200_attn_plan { void* maps; const float** ks; const float** vs; int batch, max_seq, n_kv, hd; };
+
+jllm_b200_attn_plan* jllm_b200_attn_plan_create(const void* const* k_list, const void* const* v_list, const float* const* ks_list,
+                                                const float* const* vs_list, int batch, int max_seq_len, int n_kv_heads, int head_dim) {
+    if (!k_list || !v_list || !ks_list || !vs_list || batch <= 0 || max_seq_len <= 0 || n_kv_heads <= 0) { set_error(JB_ERR_ARG, "attention plan: bad arguments"); return nullptr; }
+    if (head_dim != 128) { set_error(JB_ERR_LIMIT, "attention plan: head_dim %d (the tensor-map path handles 128)", head_dim); return nullptr; }
+    if (!ctx()) return nullptr;
+    std::vector<unsigned char> maps((size_t)batch * 2 * 128);
+    for (int b = 0; b < batch; ++b)
+        if (!attn_tma_encode(&maps[((size_t)b * 2 + 0) * 128], k_list[b], max_seq_len, n_kv_heads) ||
+            !attn_tma_encode(&maps[((size_t)b * 2 + 1) * 128], v_list[b], max_seq_len, n_kv_heads)) {
+            set_error(JB_ERR_PTR, "attention plan: tensor map of cache %d refused (caches must be 16-byte aligned device memory)", b);
+            return nullptr;
+        }
+    jllm_b200_attn_plan* p = new (std::nothrow) jllm_b200_attn_plan();
+    if (!p) return nullptr;
+    p->batch = batch; p->max_seq = max_seq_len; p->n_kv = n_kv_heads; p->hd = head_dim;
+    if (cudaMalloc(&p->maps, maps.size()) != cudaSuccess || cudaMalloc((void**)&p->ks, (size_t)batch * sizeof(void*)) != cudaSuccess ||
+        cudaMalloc((void**)&p->vs, (size_t)batch * sizeof(void*)) != cudaSuccess) {
+        cuda_error(cudaGetLastError(), "cudaMalloc(attention plan)"); jllm_b200_attn_plan_destroy(p); return nullptr;
+    }
+    cudaMemcpy(p->maps, maps.data(), maps.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy((void*)p->ks, ks_list, (size_t)batch * sizeof(void*), cudaMemcpyHostToDevice);
+    cudaMemcpy((void*)p->vs, vs_list, (size_t)batch * sizeof(void*), cudaMemcpyHostToDevice);
+    return p;
+}
+void jllm_b200_attn_plan_destroy(jllm_b200_attn_plan* p) {
+    if (!p) return;
+    if (p->maps) cudaFree(p->maps);
+    if (p->ks) cudaFree((void*)p->ks);
+    if (p->vs) cudaFree((void*)p->vs);
+    delete p;
+}
+int jllm_b200_flash_attention_decode_planned(const jllm_b200_attn_plan* p, void* o, const void* q, const int* seq_lens, int nh, float scale, void* s) {
+    if (!p || !o || !q || !seq_lens) return set_error(JB_ERR_PTR, "planned attention: null pointer");
+    AttnCall c;
+    c.out = H(o); c.q = CH(q); c.tma_maps = p->maps; c.ks_list = p->ks; c.vs_list = p->vs; c.seq_lens = seq_lens; c.batch = p->batch;
+    c.max_seq = p->max_seq; c.n_heads = nh; c.n_kv = p->n_kv; c.hd = p->hd; c.chd = p->hd; c.scale = scale; c.kv_int8 = 1;
+    if (!attention_tma_applies(c)) return set_error(JB_ERR_ARG, "planned attention: %d query heads over %d KV heads is not a supported group", nh, p->n_kv);
+    return launch_attention_tma(c, ST(s));
 }
 
 }  // extern "C"

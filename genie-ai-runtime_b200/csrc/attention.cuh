@@ -10,7 +10,10 @@ struct AttnCall {
     // ragged batch: device arrays of per-sequence pointers / lengths (batch entries)
     const void* const* k_list = nullptr; const void* const* v_list = nullptr;
     const float* const* ks_list = nullptr; const float* const* vs_list = nullptr; const int* seq_lens = nullptr;
-    int batch = 1, max_seq = 0;
+    // ragged batch on the TMA path: device array of [batch][K, V] tensor maps (built on the host from the caches' addresses,
+    // see jllm_b200_attn_plan_create); the K/V pointer lists are then not needed
+    const void* tma_maps = nullptr;
+    int batch = 1, max_seq = 0;      // max_seq: rows every cache holds (bounds the slices of a ragged batch and the tensor maps)
     int n_heads = 0, n_kv = 0, hd = 0, chd = 0, seq_len = 0;
     const int* d_pos = nullptr;       // device position: seq_len = *d_pos + 1
     float scale = 1.f; int kv_int8 = 0, window = 0, n_splits = 0;
@@ -22,6 +25,10 @@ float* splitk_buffer(size_t floats, bool may_alloc);
 int    launch_attention_general(const AttnCall& c, cudaStream_t st);
 int    launch_attention(const AttnCall& c, cudaStream_t st);      // picks the fast path when it applies
 int    launch_attn_reduce(__half* out, const float* part, int n_heads, int hd, int n_splits, int batch, cudaStream_t st);
+unsigned int* attn_tickets();                                     // 65536 zeroed words per device (slice counters of the TMA kernel)
+bool   attention_tma_applies(const AttnCall& c);                  // INT8 KV, head_dim 128, GQA 1/2/4, no window, cache extent known
+int    launch_attention_tma(const AttnCall& c, cudaStream_t st);
+bool   attn_tma_encode(void* map_out128, const void* cache_base, int rows, int n_kv);
 bool   attention_fast_applies(const AttnCall& c);                 // INT8 KV, head_dim 128, GQA group of 1, 2 or 4, no window
 int    launch_attention_fast(const AttnCall& c, cudaStream_t st);
 

@@ -77,6 +77,7 @@ struct jllm_b200_batch_decoder {
     int *state = nullptr, *tokens = nullptr, *seq_lens = nullptr, *out_tokens = nullptr, *prompt_dev = nullptr;
     int out_cap = 0, prompt_cap = 0;
     void** lists = nullptr;            // device: [layer][4 (k, v, k scales, v scales)][B] pointers
+    unsigned char* maps = nullptr;     // device: [layer][B][K, V] TMA tensor maps of the caches (128 bytes each)
     void* slab = nullptr;
     int kernels_per_step = 0;
     cudaGraphExec_t graph_exec = nullptr;   // one decode step from the device-side state
@@ -106,6 +107,7 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         AttnCall c;
         c.out = d->att; c.q = d->q; c.k_list = (const void* const*)L; c.v_list = (const void* const*)(L + B);
         c.ks_list = (const float* const*)(L + 2 * B); c.vs_list = (const float* const*)(L + 3 * B); c.seq_lens = d->seq_lens;
+        c.tma_maps = d->maps ? d->maps + (size_t)l * B * 2 * 128 : nullptr;
         c.batch = B; c.max_seq = m.max_context; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads; c.hd = m.head_dim; c.chd = m.head_dim;
         c.scale = scale; c.kv_int8 = 1;
         BCHK(launch_attention(c, st));
@@ -174,6 +176,16 @@ jllm_b200_batch_decoder* jllm_b200_batch_decoder_create(const jllm_b200_model_de
             host[((size_t)l * 4 + 3) * B + b] = d->kv[b].kv_scale_ptr(l, 0, true);
         }
     cudaMemcpy(d->lists, host.data(), host.size() * sizeof(void*), cudaMemcpyHostToDevice);
+    if (model->head_dim == 128) {       // tensor maps of every (layer, stream) cache for the TMA attention path
+        std::vector<unsigned char> maps((size_t)model->n_layers * B * 2 * 128);
+        bool ok = true;
+        for (int l = 0; l < model->n_layers && ok; ++l)
+            for (int b = 0; b < B && ok; ++b)
+                ok = attn_tma_encode(&maps[(((size_t)l * B + b) * 2 + 0) * 128], d->kv[b].key_ptr(l, 0), model->max_context, model->n_kv_heads) &&
+                     attn_tma_encode(&maps[(((size_t)l * B + b) * 2 + 1) * 128], d->kv[b].val_ptr(l, 0), model->max_context, model->n_kv_heads);
+        if (ok && cudaMalloc((void**)&d->maps, maps.size()) == cudaSuccess) cudaMemcpy(d->maps, maps.data(), maps.size(), cudaMemcpyHostToDevice);
+        else { cudaGetLastError(); d->maps = nullptr; }      // the row-copy attention kernel serves the pointer lists instead
+    }
     // scratch the kernels would otherwise grow on first use
     size_t need = 0;
     const int Ms[4] = { (int)QD, (int)I, (int)H, (int)V }; const int Ks[4] = { (int)H, (int)H, (int)I, (int)H };
@@ -190,6 +202,7 @@ void jllm_b200_batch_decoder_destroy(jllm_b200_batch_decoder* d) {
     if (!d) return;
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->slab) cudaFree(d->slab);
+    if (d->maps) cudaFree(d->maps);
     for (auto& p : d->kv) p.destroy();
     delete d;
 }

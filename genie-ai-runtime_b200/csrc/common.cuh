@@ -45,10 +45,13 @@ struct DeviceCtx {
     float* splitk = nullptr; size_t splitk_floats = 0;
     void*  mmq_act = nullptr; size_t mmq_act_bytes = 0;
     RopeTable rope[8]; int n_rope = 0;
-    bool gemv_attr[4] = { false, false, false, false };
+    bool gemv_attr[8] = { false, false, false, false, false, false, false, false };
     bool gemv_chain_attr = false;
+    bool attn_tma_attr[3] = { false, false, false };
+    unsigned int* attn_tickets = nullptr;   // ATTN_TICKET_WORDS zeroed words: slice counters of the TMA attention kernel
     int  gemv_smem_budget = 0;          // dynamic shared memory of a GEMV CTA that shares its SM with one other CTA
 };
+constexpr int ATTN_TICKET_WORDS = 65536;
 DeviceCtx* ctx();                        // context of the current device (created on first use)
 
 // ── device helpers ──────────────────────────────────────────────────────

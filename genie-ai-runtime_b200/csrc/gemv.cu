@@ -585,11 +585,13 @@ __device__ __forceinline__ GvRange gv_range(const GvParams& p) {
     return rg;
 }
 
-template <int XM, bool DBG>
-__global__ void __launch_bounds__(GV_MAXTHREADS, 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+// WHOLE = false: a CTA takes half an SM (see above); WHOLE = true: a CTA takes a whole SM (up to 20 warps and all the
+// shared memory), for products whose rows are so long that half an SM holds too few of them.
+template <int XM, bool DBG, bool WHOLE>
+__global__ void __launch_bounds__(WHOLE ? GV_CHAINTHREADS : GV_MAXTHREADS, WHOLE ? 1 : 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[GV_MAXWARPS][GV_MAXSLOT];
-    __shared__ float red[GV_MAXWARPS];
+    __shared__ __align__(8) uint64_t full[WHOLE ? GV_CHAINWARPS : GV_MAXWARPS][GV_MAXSLOT];
+    __shared__ float red[WHOLE ? GV_CHAINWARPS : GV_MAXWARPS];
     if (DBG && p.trace && threadIdx.x == 0) { gv_stamp(p, 0); p.trace[(size_t)blockIdx.x * GV_NTRACE + 6] = 0ull; }
     pdl_launch();                // the next kernel's CTAs may take the free half of every SM now; they wait for our completion
                                  // before they touch our outputs
@@ -850,15 +852,22 @@ int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
     g_tp_wait_set = g_tp_push_set = false;
     GvParams p;
     size_t smem_bytes = 0; int grid = 0; bool empty = false;
-    const int rc = gv_configure(a, p, GV_MAXWARPS, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
+    // diagnostic switch: JLLM_B200_GEMV_WHOLE=1 gives every GEMV a whole SM per CTA, =0 half an SM; unset: the default policy
+    static const int force = [] { const char* v = getenv("JLLM_B200_GEMV_WHOLE"); return v ? (v[0] == '1' ? 1 : 0) : -1; }();
+    const bool whole = force >= 0 ? force == 1 : false;
+    const int rc = whole ? gv_configure(a, p, GV_CHAINWARPS, cx->max_smem_optin - 2048, false, smem_bytes, grid, empty)
+                         : gv_configure(a, p, GV_MAXWARPS, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
     if (rc || empty) return rc;
     p.trace = g_trace; g_trace = nullptr;
     const bool dbg = a.dbg_dots || p.trace;
-    auto kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true> : gemv_stream_kernel<0, true>)
-                    : (a.xmode ? gemv_stream_kernel<1, false> : gemv_stream_kernel<0, false>);
-    const int ki = (a.xmode ? 1 : 0) + (dbg ? 2 : 0);
+    void (*kern)(GvParams);
+    if (whole) kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true, true> : gemv_stream_kernel<0, true, true>)
+                          : (a.xmode ? gemv_stream_kernel<1, false, true> : gemv_stream_kernel<0, false, true>);
+    else       kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true, false> : gemv_stream_kernel<0, true, false>)
+                          : (a.xmode ? gemv_stream_kernel<1, false, false> : gemv_stream_kernel<0, false, false>);
+    const int ki = (a.xmode ? 1 : 0) + (dbg ? 2 : 0) + (whole ? 4 : 0);
     if (!cx->gemv_attr[ki]) {
-        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->gemv_smem_budget));
+        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, whole ? cx->max_smem_optin - 2048 : cx->gemv_smem_budget));
         JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         cx->gemv_attr[ki] = true;
     }

@@ -198,3 +198,33 @@ def flash_attention_decode_noalloc(output, q, k_cache, v_cache, n_heads, n_kv_he
                                                        i32(head_dim), i32(cache_head_dim), i32(seq_len), f32(scale),
                                                        i32(1 if kv_int8 else 0), _ptr(k_scales), _ptr(v_scales), i32(window),
                                                        _stream(stream)))
+
+
+class AttnPlan:
+    """Ragged batched decode attention over a fixed set of INT8 caches (jllm_b200_attn_plan_*): the tensor maps of the
+    caches are built once; `k_list` ... `vs_list` are sequences of torch CUDA tensors (one per sequence), every cache
+    holding max_seq_len positions of n_kv_heads x 128 int8 values."""
+
+    def __init__(self, k_list, v_list, ks_list, vs_list, max_seq_len, n_kv_heads, head_dim=128):
+        import ctypes as C
+        from . import JllmError, last_error
+        self._keep = (list(k_list), list(v_list), list(ks_list), list(vs_list))
+        B = len(self._keep[0])
+        arr = lambda ts: (C.c_void_p * B)(*[t.data_ptr() for t in ts])
+        lib.jllm_b200_attn_plan_create.restype = C.c_void_p
+        self._h = lib.jllm_b200_attn_plan_create(arr(k_list), arr(v_list), arr(ks_list), arr(vs_list), i32(B), i32(max_seq_len),
+                                                 i32(n_kv_heads), i32(head_dim))
+        if not self._h:
+            raise JllmError(-1, last_error())
+        self.batch = B
+
+    def decode(self, output, q, seq_lens, n_heads, scale, stream=None):
+        import ctypes as C
+        check(lib.jllm_b200_flash_attention_decode_planned(C.c_void_p(self._h), _ptr(output), _ptr(q), _ptr(seq_lens), i32(n_heads),
+                                                           f32(scale), _stream(stream)))
+
+    def close(self):
+        import ctypes as C
+        if self._h:
+            lib.jllm_b200_attn_plan_destroy(C.c_void_p(self._h))
+            self._h = None

@@ -132,6 +132,9 @@ def measure(jb, argv):
     trace = None
     if a.trace:
         import ctypes as C
+        jb.lib.jllm_b200_init(C.c_int(-1))                     # the per-device context must exist before the capture starts
+        calls[0]()
+        torch.cuda.synchronize()
         NCTA, NST = 2 * 148, 8
         trace = torch.zeros((a.iters, NCTA, NST), dtype=torch.int64, device=dev)
         plain = calls

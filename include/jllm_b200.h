@@ -191,6 +191,18 @@ int jllm_b200_flash_attention_decode_batched(void* output, const void* q, const 
                                              int batch, int max_seq_len, int n_heads, int n_kv_heads, int head_dim, float scale,
                                              int kv_int8, void* stream);
 
+/* Ragged batched decode attention over a FIXED set of INT8 caches (head_dim 128): the plan holds one pair of TMA tensor
+ * maps per sequence, built once on the host, so the kernel fetches K/V tiles by 2-D tensor copies as the single-sequence
+ * path does.  k_list / v_list / ks_list / vs_list are HOST arrays of `batch` DEVICE pointers (cache bases, 16-byte
+ * aligned; fp32 scales [pos][n_kv_heads]); every cache holds max_seq_len positions.  seq_lens is a device array that
+ * may change from call to call.  Same result as jllm_b200_flash_attention_decode_batched. */
+typedef struct jllm_b200_attn_plan jllm_b200_attn_plan;
+jllm_b200_attn_plan* jllm_b200_attn_plan_create(const void* const* k_list, const void* const* v_list, const float* const* ks_list,
+                                                const float* const* vs_list, int batch, int max_seq_len, int n_kv_heads, int head_dim);
+void jllm_b200_attn_plan_destroy(jllm_b200_attn_plan* plan);
+int  jllm_b200_flash_attention_decode_planned(const jllm_b200_attn_plan* plan, void* output, const void* q, const int* seq_lens,
+                                              int n_heads, float scale, void* stream);
+
 /* ── decoder session (extension; stands where Engine::decode_step / transformer_layer sit,
  * src/engine/decode.cu:1169-1246, :1437-1530, :2101-2194) ─────────────────────────────
  * Host-side sequencing of the kernels above for a Qwen3/Llama-shaped decoder with INT8 KV:

@@ -169,6 +169,24 @@ def quantize_q8_1(x):
     return qs, d.view(np.float16), s.view(np.float16)
 
 
+class q8_override:
+    """Context manager: while active, the oracle's q8_1 quantiser returns the given blocks (the 36-byte blocks
+    {fp16 d, fp16 s, int8 qs[32]} a run of the reference's GPU quantiser produced) for vectors of that length."""
+
+    def __init__(self, blocks36):
+        b = np.ascontiguousarray(blocks36, np.uint8).reshape(-1, 36)
+        self.d = np.ascontiguousarray(b[:, 0:2]).view(np.uint16).reshape(-1).copy()
+        self.s = np.ascontiguousarray(b[:, 2:4]).view(np.uint16).reshape(-1).copy()
+        self.qs = np.ascontiguousarray(b[:, 4:36]).view(np.int8).reshape(-1).copy()
+
+    def __enter__(self):
+        lib().orc_set_q8_override(_p(self.qs), _p(self.d), _p(self.s), C.c_int(self.qs.size))
+        return self
+
+    def __exit__(self, *a):
+        lib().orc_set_q8_override(None, None, None, C.c_int(0))
+
+
 def q8_int_dots(W, t, M, K, qs):
     G = K // 32 if t == Q4_K else K // 16
     out = np.empty((M, G), np.int32)

@@ -106,6 +106,13 @@ def attention_prefill(N, start=0):
     return dict(q=q, k=k, v=v, ks=ks, vs=vs, N=N, start=start)
 
 
+def prefill_sample(N):
+    """Query tokens of a prefill-attention record that are kept (all of them for a short prompt)."""
+    if N <= 40:
+        return np.arange(N, dtype=np.int32)
+    return np.unique(np.concatenate([np.array([0, 1, 31, 32, 63, 64, N // 2, N - 2, N - 1]), rng_for(2, 60).choice(N, 8, replace=False)])).astype(np.int32)
+
+
 # configuration 3: batched K-quant GEMM (prefill)
 def gemm(t, N):
     if t == 12:

@@ -45,6 +45,13 @@ def main():
     def copies(nbytes):          # enough copies to cover three times a 126 MB L2
         return int(max(1, min(64, (3 * 126e6) // nbytes + 1)))
 
+    def q8_blocks(name, x):
+        blocks = np.zeros(x.size // 32 * 36, np.uint8)
+        rc = lib.refgpu_quantize_q8_1(P(blocks), P(U16(x)), C.c_int(x.size))
+        if rc != 0:
+            raise RuntimeError(f"{name}: reference quantiser returned {rc}")
+        rec[name + "_q8"] = blocks
+
     def gemv(name, c, mode, res=None):
         W = np.ascontiguousarray(c["W"])
         y = np.zeros(c["M"], np.float32 if mode == 2 else np.uint16)
@@ -63,14 +70,16 @@ def main():
             print(json.dumps(times))
 
     try:
-        record(lib, args, rec, times, gemv, ok, copies, tp)
+        record(lib, args, rec, times, gemv, ok, copies, tp, q8_blocks)
     finally:
         save()            # a failing call still leaves the records made before it
 
 
-def record(lib, args, rec, times, gemv, ok, copies, tp):
-    c = gc.gemv_q4k(); gemv("gemv_q4k", c, 0)
-    c = gc.gemv_q6k(); gemv("gemv_q6k", c, 0)
+def record(lib, args, rec, times, gemv, ok, copies, tp, q8_blocks):
+    # the dp4a GEMVs quantise their activation vector to q8_1 blocks first: keep the blocks the reference's own
+    # quantiser makes of each of those vectors next to the results
+    c = gc.gemv_q4k(); gemv("gemv_q4k", c, 0); q8_blocks("gemv_q4k", c["x"])
+    c = gc.gemv_q6k(); gemv("gemv_q6k", c, 0); q8_blocks("gemv_q6k", c["x"])
     W = np.ascontiguousarray(c["W"]); y8 = np.zeros((8, c["M"]), np.uint16)
     ok(lib.refgpu_gemm_batched(P(y8), P(W), C.c_longlong(W.nbytes), C.c_int(14), P(U16(c["X8"])), C.c_int(c["M"]), C.c_int(8),
                                C.c_int(c["K"]), C.c_int(args.iters), tp), "gemm_q6k_b8")
@@ -89,6 +98,7 @@ def record(lib, args, rec, times, gemv, ok, copies, tp):
         for i, y in enumerate(ys):
             rec[f"{name}_y{i}"] = y
         rec[name + "_in"] = gc.digest(*Ws, c["x"])
+        q8_blocks(name, c["x"])
 
     c = gc.q8_1()
     blocks = np.zeros(c["x"].size // 32 * 36, np.uint8)
@@ -111,7 +121,9 @@ def record(lib, args, rec, times, gemv, ok, copies, tp):
         ok(lib.refgpu_attention_prefill(P(out), P(U16(c["q"])), P(c["k"]), P(c["v"]), P(c["ks"]), P(c["vs"]), C.c_int(gc.NH), C.c_int(gc.NKV),
                                         C.c_int(gc.HD), C.c_int(N), C.c_int(0), C.c_float(gc.SCALE), C.c_int(max(1, args.iters // 10)), tp),
            f"prefill_attn_N{N}")
-        rec[f"prefill_attn_N{N}_out"] = out; rec[f"prefill_attn_N{N}_in"] = gc.digest(c["q"], c["k"], c["v"], c["ks"], c["vs"])
+        sel = gc.prefill_sample(N)
+        rec[f"prefill_attn_N{N}_out"] = out.reshape(N, -1)[sel].copy(); rec[f"prefill_attn_N{N}_sel"] = sel
+        rec[f"prefill_attn_N{N}_in"] = gc.digest(c["q"], c["k"], c["v"], c["ks"], c["vs"])
 
     for t, Ns in ((12, gc.GEMM_TOKENS), (14, (2048,))):
         for N in Ns:

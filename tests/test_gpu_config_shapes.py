@@ -1,6 +1,11 @@
 """GPU parity at the benchmark configurations' own shapes, through the C ABI, against BOTH checkers: the CPU oracle
 and the records of the reference's own GPU kernels on the same seeded inputs (tests/golden/ref_gpu.npz).
 
+The reference's dp4a decode GEMV stores corrupted q8_1 block scales when compiled for sm_100a (see
+tests/test_oracle_ref_gpu.py), so for gemv_quant / _pair / _triple the checker is the oracle alone — which
+test_oracle_ref_gpu.py ties to the reference's GPU run through the recorded blocks — and the record is compared
+wherever the reference's GPU result is sound: fp16-x GEMVs, batched products, attention.
+
 Bars: fp outputs 1e-3 relative plus 2e-3 of the output RMS (attention: of the head's largest output); the batched
 products use gpu_util.close_gemm (see its docstring)."""
 import os
@@ -38,7 +43,8 @@ def test_gemv_quant_configs_0_and_1(ref, case):
     c = getattr(gc, case)()
     y = torch.zeros(c["M"], dtype=torch.float16, device="cuda")
     jb.gemv_quant(y, dev(c["W"]), c["t"], dev(c["x"]), c["M"], c["K"])
-    both(y.float().cpu().numpy(), orc.entry_gemv_quant(c["W"], c["t"], c["x"], c["M"], c["K"]), f16(ref[case + "_y"]), case)
+    ok, md = close(y.float().cpu().numpy(), orc.entry_gemv_quant(c["W"], c["t"], c["x"], c["M"], c["K"]).astype(np.float32))
+    assert ok, f"{case} against the oracle: max diff {md}"
     assert jb.device_status() == 0
 
 
@@ -86,7 +92,8 @@ def test_shared_activation_gemvs(ref, case):
                              ys[2], dev(Ws[2]), c["ts"][2], c["Ms"][2], x, c["K"])
     want = orc.entry_gemv_multi(Ws, list(c["ts"]), list(c["Ms"]), c["x"], c["K"])
     for i in range(n):
-        both(ys[i].float().cpu().numpy(), want[i], f16(ref[f"{case}_y{i}"]), f"{case}[{i}]")
+        ok, md = close(ys[i].float().cpu().numpy(), want[i].astype(np.float32))
+        assert ok, f"{case}[{i}] against the oracle: max diff {md}"
 
 
 @pytest.mark.parametrize("case", ["gemv_add_wo", "gemv_add_down"])
@@ -144,10 +151,22 @@ def test_decode_attention_64_ragged_sequences():
     jb.flash_attention_decode_batched(out, dev(q), ptrs[0], ptrs[1], ptrs[2], ptrs[3], torch.tensor(lens, dtype=torch.int32, device="cuda"),
                                       B, int(lens.max()), gc.NH, gc.NKV, gc.HD, gc.SCALE, True)
     got = out.float().cpu().numpy()
+    # the same batch through a plan (tensor maps built once; every cache padded to the longest length)
+    Lmax = int(lens.max())
+    pad = lambda t: torch.cat([t, torch.zeros((Lmax - t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device="cuda")])
+    padded = [tuple(pad(t) for t in d) for d in devs]
+    plan = jb.AttnPlan([p[0] for p in padded], [p[1] for p in padded], [p[2] for p in padded], [p[3] for p in padded], Lmax, gc.NKV)
+    out2 = torch.zeros((B, gc.NH * gc.HD), dtype=torch.float16, device="cuda")
+    lens_d = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    plan.decode(out2, dev(q), lens_d, gc.NH, gc.SCALE)
+    plan.decode(out2, dev(q), lens_d, gc.NH, gc.SCALE)              # twice: the slice counters must be back at zero
+    got2 = out2.float().cpu().numpy()
+    plan.close()
     for b in range(B):
         k, v, ks, vs = host[b]
         want = orc.attention_decode(q[b], k, v, gc.NH, gc.NKV, gc.HD, int(lens[b]), gc.SCALE, True, ks, vs).astype(np.float32)
-        _attn_check(got[b], want, f"sequence {b} (length {lens[b]})")
+        _attn_check(got[b], want, f"pointer lists, sequence {b} (length {lens[b]})")
+        _attn_check(got2[b], want, f"plan, sequence {b} (length {lens[b]})")
     assert jb.device_status() == 0
 
 
