@@ -480,6 +480,32 @@ def main():
                 bd.close()
             except Exception as e:          # the headline line must not depend on the side measurement
                 line["batch_streams"] = {"error": str(e)[:200]}
+        # prompt prefill through the batched path (N = 1 only): the 33-token prompt of this configuration and two longer prompts
+        if world == 1 and not a.no_kernels:
+            try:
+                pf = {}
+                Hc, QDc, KVDc, Ic = CFG["hidden"], CFG["n_heads"] * CFG["head_dim"], CFG["n_kv_heads"] * CFG["head_dim"], CFG["ffn"]
+                layer_params = CFG["n_layers"] * (QDc * Hc + 2 * KVDc * Hc + Hc * QDc + 3 * Ic * Hc)
+                pd = jb.decoder.Decoder(CFG, weights, 2304, jb.decoder.FUSED | jb.decoder.GRAPH | jb.decoder.PREFILL)
+                pr_rng = np.random.Generator(np.random.PCG64(SEED + 2))
+                with torch.cuda.stream(stream):
+                    for n_tok in (N_PROMPT, 512, 2048):
+                        toks = prompt if n_tok == N_PROMPT else pr_rng.integers(0, CFG["vocab"], n_tok).astype(np.int32)
+                        pd.reset(); pd.prefill(toks, 0, stream); torch.cuda.synchronize()
+                        reps_pf = 3
+                        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        p0.record(stream)
+                        for _ in range(reps_pf):
+                            pd.prefill(toks, 0, stream)
+                        p1.record(stream)
+                        torch.cuda.synchronize()
+                        ms = p0.elapsed_time(p1) / reps_pf
+                        pf[f"prompt_{n_tok}"] = {"tokens": n_tok, "ms": round(ms, 3), "tok_s": round(n_tok / (ms * 1e-3), 1),
+                                                 "TFLOPs_matmul": round(2.0 * n_tok * layer_params / (ms * 1e-3) / 1e12, 1)}
+                pd.close()
+                line["prefill"] = pf
+            except Exception as e:
+                line["prefill"] = {"error": str(e)[:200]}
         # CPU baseline on a bounded sample (rank 0, N = 1 only), and the token check against it
         if world == 1 and a.cpu_steps > 0:
             n_cpu = min(a.cpu_steps, N_PROMPT)

@@ -289,7 +289,10 @@ int jllm_b200_flash_attention_prefill_batched(void* o, const void* q, const void
     AttnCall c;
     c.out = H(o); c.q = CH(q); c.k = k; c.v = v; c.ks = ks; c.vs = vs; c.n_heads = nh; c.n_kv = nkv; c.hd = hd; c.chd = chd;
     c.scale = scale; c.kv_int8 = i8; c.window = window; c.causal_start = start; c.batch = N; c.n_splits = 1;
-    return launch_attention_general(c, ST(s));
+    if (start < 0) return set_error(JB_ERR_ARG, "prefill attention: start_pos=%d", start);
+    if (!c.out || !c.q || !k || !v) return set_error(JB_ERR_PTR, "prefill attention: null pointer");
+    // INT8 cache with 128-wide heads: query-tiled tensor-core kernel; everything else: the general slice, one CTA per (head, token)
+    return attention_prefill_fast_applies(c) ? launch_attention_prefill_fast(c, ST(s)) : launch_attention_general(c, ST(s));
 }
 int jllm_b200_flash_attention_decode_dyn(void* o, const void* q, const void* k, const void* v, int nh, int nkv, int hd, int chd,
                                          const int* d_pos, float scale, int i8, const float* kvs, int window, int n_splits, void* s) {
@@ -341,7 +344,7 @@ int jllm_b200_flash_attention_decode_batched(void* o, const void* q, const void*
 }
 
 /* ── attention plan: tensor maps of a fixed set of INT8 caches, built once on the host ── */
-struct jllm_b200_attn_plan { void* maps; const float** ks; const float** vs; int batch, max_seq, n_kv, hd; };
+struct jllm_b200_attn_plan { std::vector<unsigned char> maps; const float** ks = nullptr; const float** vs = nullptr; int batch = 0, max_seq = 0, n_kv = 0, hd = 0; };
 
 jllm_b200_attn_plan* jllm_b200_attn_plan_create(const void* const* k_list, const void* const* v_list, const float* const* ks_list,
                                                 const float* const* vs_list, int batch, int max_seq_len, int n_kv_heads, int head_dim) {
@@ -358,18 +361,16 @@ jllm_b200_attn_plan* jllm_b200_attn_plan_create(const void* const* k_list, const
     jllm_b200_attn_plan* p = new (std::nothrow) jllm_b200_attn_plan();
     if (!p) return nullptr;
     p->batch = batch; p->max_seq = max_seq_len; p->n_kv = n_kv_heads; p->hd = head_dim;
-    if (cudaMalloc(&p->maps, maps.size()) != cudaSuccess || cudaMalloc((void**)&p->ks, (size_t)batch * sizeof(void*)) != cudaSuccess ||
-        cudaMalloc((void**)&p->vs, (size_t)batch * sizeof(void*)) != cudaSuccess) {
+    p->maps.swap(maps);                  // the maps stay on the host: they travel to the kernel as launch parameters
+    if (cudaMalloc((void**)&p->ks, (size_t)batch * sizeof(void*)) != cudaSuccess || cudaMalloc((void**)&p->vs, (size_t)batch * sizeof(void*)) != cudaSuccess) {
         cuda_error(cudaGetLastError(), "cudaMalloc(attention plan)"); jllm_b200_attn_plan_destroy(p); return nullptr;
     }
-    cudaMemcpy(p->maps, maps.data(), maps.size(), cudaMemcpyHostToDevice);
     cudaMemcpy((void*)p->ks, ks_list, (size_t)batch * sizeof(void*), cudaMemcpyHostToDevice);
     cudaMemcpy((void*)p->vs, vs_list, (size_t)batch * sizeof(void*), cudaMemcpyHostToDevice);
     return p;
 }
 void jllm_b200_attn_plan_destroy(jllm_b200_attn_plan* p) {
     if (!p) return;
-    if (p->maps) cudaFree(p->maps);
     if (p->ks) cudaFree((void*)p->ks);
     if (p->vs) cudaFree((void*)p->vs);
     delete p;
@@ -377,7 +378,7 @@ void jllm_b200_attn_plan_destroy(jllm_b200_attn_plan* p) {
 int jllm_b200_flash_attention_decode_planned(const jllm_b200_attn_plan* p, void* o, const void* q, const int* seq_lens, int nh, float scale, void* s) {
     if (!p || !o || !q || !seq_lens) return set_error(JB_ERR_PTR, "planned attention: null pointer");
     AttnCall c;
-    c.out = H(o); c.q = CH(q); c.tma_maps = p->maps; c.ks_list = p->ks; c.vs_list = p->vs; c.seq_lens = seq_lens; c.batch = p->batch;
+    c.out = H(o); c.q = CH(q); c.tma_maps = p->maps.data(); c.ks_list = p->ks; c.vs_list = p->vs; c.seq_lens = seq_lens; c.batch = p->batch;
     c.max_seq = p->max_seq; c.n_heads = nh; c.n_kv = p->n_kv; c.hd = p->hd; c.chd = p->hd; c.scale = scale; c.kv_int8 = 1;
     if (!attention_tma_applies(c)) return set_error(JB_ERR_ARG, "planned attention: %d query heads over %d KV heads is not a supported group", nh, p->n_kv);
     return launch_attention_tma(c, ST(s));

@@ -7,7 +7,7 @@
 // This file holds the general kernel: any head_dim <= 512, FP16 or INT8 cache, sliding
 // window, cache slot stride != head_dim, device-side position, ragged batches, causal prefill
 // (the slice itself is attention_general.cuh).  The INT8 / head_dim 128 paths live in
-// attention_tma.cu (2-D TMA tiles) and attention_fast.cu (row copies, for pointer lists).
+// attention_tma.cu (decode, 2-D TMA tiles) and attention_prefill.cu (causal prefill with query tiling).
 #include "attention.cuh"
 #include "attention_general.cuh"
 #include <cfloat>
@@ -125,10 +125,10 @@ int launch_attention(const AttnCall& c, cudaStream_t st) {
     if (c.n_heads <= 0 || c.n_kv <= 0 || c.n_heads % c.n_kv) return set_error(JB_ERR_ARG, "attention: n_heads=%d n_kv_heads=%d", c.n_heads, c.n_kv);
     if (!c.out || !c.q) return set_error(JB_ERR_PTR, "attention: null q/out");
     if (!c.k_list && (!c.k || !c.v)) return set_error(JB_ERR_PTR, "attention: null cache pointer");
-    // INT8 / head_dim 128: 2-D TMA tiles when the cache extent is known, row copies otherwise (pointer lists in device memory,
-    // device-side position without a bound); everything else goes to the general kernel
-    if (attention_tma_applies(c)) return launch_attention_tma(c, st);
-    return attention_fast_applies(c) ? launch_attention_fast(c, st) : launch_attention_general(c, st);
+    // INT8 / head_dim 128 with a known cache extent (a length, a device-side position with its bound, or a plan of tensor
+    // maps for a ragged batch): 2-D TMA tiles on the tensor cores; everything else — FP16 caches, other head sizes, sliding
+    // windows, pointer lists that live in device memory — goes to the general kernel
+    return attention_tma_applies(c) ? launch_attention_tma(c, st) : launch_attention_general(c, st);
 }
 
 }  // namespace jb

@@ -10,8 +10,8 @@ struct AttnCall {
     // ragged batch: device arrays of per-sequence pointers / lengths (batch entries)
     const void* const* k_list = nullptr; const void* const* v_list = nullptr;
     const float* const* ks_list = nullptr; const float* const* vs_list = nullptr; const int* seq_lens = nullptr;
-    // ragged batch on the TMA path: device array of [batch][K, V] tensor maps (built on the host from the caches' addresses,
-    // see jllm_b200_attn_plan_create); the K/V pointer lists are then not needed
+    // ragged batch on the TMA path: HOST array of [batch][K, V] tensor maps (built from the caches' addresses, see
+    // jllm_b200_attn_plan_create; they travel to the kernel as parameters); the K/V pointer lists are then not needed
     const void* tma_maps = nullptr;
     int batch = 1, max_seq = 0;      // max_seq: rows every cache holds (bounds the slices of a ragged batch and the tensor maps)
     int n_heads = 0, n_kv = 0, hd = 0, chd = 0, seq_len = 0;
@@ -29,7 +29,7 @@ unsigned int* attn_tickets();                                     // 65536 zeroe
 bool   attention_tma_applies(const AttnCall& c);                  // INT8 KV, head_dim 128, GQA 1/2/4, no window, cache extent known
 int    launch_attention_tma(const AttnCall& c, cudaStream_t st);
 bool   attn_tma_encode(void* map_out128, const void* cache_base, int rows, int n_kv);
-bool   attention_fast_applies(const AttnCall& c);                 // INT8 KV, head_dim 128, GQA group of 1, 2 or 4, no window
-int    launch_attention_fast(const AttnCall& c, cudaStream_t st);
+bool   attention_prefill_fast_applies(const AttnCall& c);          // causal prefill (causal_start >= 0), INT8 KV, head_dim 128, GQA 1/2/4
+int    launch_attention_prefill_fast(const AttnCall& c, cudaStream_t st);
 
 }  // namespace jb

@@ -2,8 +2,7 @@
 //
 // Some hosts of this library cannot let it call cudaMalloc: an engine that has already handed every free
 // byte of the GPU to its own KV and scratch pools, a serving loop that forbids driver calls which may
-// synchronise the whole device in the middle of a request, or code that is recording a CUDA graph (where an
-// allocation is an error).  The regular split-K attention grows a per-device partials buffer on demand; this
+// synchronise the whole device in the middle of a request.  The regular split-K attention grows a per-device partials buffer on demand; this
 // file offers the same computation with that buffer replaced by a fixed array compiled into the library.
 //
 // The array lives in every GPU context that loads the library (JLLM_B200_NOALLOC_MAX_FLOATS floats, 1 MiB)

@@ -17,23 +17,30 @@
 // Tensor maps describe this GPU's own memory only and no copy uses cluster multicast.
 #include "attention.cuh"
 #include <cfloat>
+#include <cstring>
 #include <cuda.h>
 
 namespace jb {
 
 constexpr int AM_WARPS  = 4;
 constexpr int AM_TILE   = 32;                        // keys per warp tile
-constexpr int AM_STAGES = 3;
+constexpr int AM_STAGES = 2;                        // tiles in flight per warp; three CTAs (twelve warps) share an SM
 constexpr int AM_HD     = 128;
 constexpr int AM_TILE_BYTES  = AM_TILE * AM_HD;       // one K (or V) tile: 4 KB, rows of 128 bytes, 128-byte swizzle
 constexpr int AM_STAGE_BYTES = 2 * AM_TILE_BYTES;
 constexpr int AM_RING_BYTES  = AM_WARPS * AM_STAGES * AM_STAGE_BYTES;
 constexpr int AM_SMEM = AM_RING_BYTES + AM_WARPS * 256 + 1024 + 64 + 1024;   // + PV weight bytes, query planes, scales, alignment slack
 
+constexpr int AM_BATCH_SEQS = 14;                     // sequences per launch of a ragged batch: 28 tensor maps fit the 4 KB of kernel parameters
+
+// Tensor maps travel as kernel parameters (constant bank).  Maps read from global memory work but were measured at several
+// microseconds per tensor copy, so a ragged batch is launched in groups of AM_BATCH_SEQS sequences instead.
+template <int NSEQ> struct AmMaps { CUtensorMap m[2 * NSEQ]; };
+
 struct AmArgs {
     __half* out; const __half* q;
     const float* ks; const float* vs;
-    const CUtensorMap* maps;                 // ragged batch: [sequence][K, V] tensor maps in device memory; null for one sequence
+    int ragged, z0;                          // ragged batch: sequence blockIdx.z of this launch is sequence z0 + blockIdx.z of the batch
     const float* const* ks_list; const float* const* vs_list; const int* seq_lens;
     int n_heads, n_kv, seq_len; const int* d_pos;
     float scale; int n_splits;
@@ -56,6 +63,8 @@ __device__ __forceinline__ void am_tma_2d(uint32_t dst, const CUtensorMap* map, 
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// 2^x by the hardware approximation (relative error ~2^-22, far inside the fp16 output); 2^-inf = 0
+__device__ __forceinline__ float am_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ uint32_t am_lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
 
 // byte (row, b) of a tile with the 128-byte swizzle: the 16-byte chunk index is xored with the row's low three bits
@@ -63,14 +72,13 @@ __device__ __forceinline__ uint32_t am_swz(uint32_t tile, int row, int b) {
     return tile + (uint32_t)row * 128u + (uint32_t)((((b >> 4) ^ (row & 7)) << 4) | (b & 15));
 }
 
-template <int G>   // query heads per kv head: 1, 2 or 4
-__global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
-                                                                    const AmArgs a) {
+template <int G, int NSEQ>   // G: query heads per kv head (1, 2 or 4); NSEQ: sequences whose tensor maps this launch carries
+__global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid_constant__ AmMaps<NSEQ> mp, const AmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full[AM_WARPS][AM_STAGES];
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, c = lane & 3;
-    const int kvh = blockIdx.x, split = blockIdx.y, z = blockIdx.z;
+    const int kvh = blockIdx.x, split = blockIdx.y, zl = blockIdx.z, z = a.z0 + zl;
 
     const uint32_t ring0 = (smem_u32(smem_raw) + 1023u) & ~1023u;               // swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw + (ring0 - smem_u32(smem_raw));
@@ -79,17 +87,21 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
     int8_t*  qpl = reinterpret_cast<int8_t*>(smem + AM_RING_BYTES + AM_WARPS * 256);        // [G][2 planes][128]
     float*   qsc = reinterpret_cast<float*>(smem + AM_RING_BYTES + AM_WARPS * 256 + 1024);  // dq per head
 
-    const CUtensorMap* km = a.maps ? a.maps + 2 * z : &kmap;
-    const CUtensorMap* vm = a.maps ? a.maps + 2 * z + 1 : &vmap;
+    const CUtensorMap* km = &mp.m[2 * zl];
+    const CUtensorMap* vm = &mp.m[2 * zl + 1];
     if (lane == 0) { for (int s = 0; s < AM_STAGES; ++s) mbar_init(&full[warp][s], 1); }
-    if (tid == 0) fence_mbar_init();
+    if (tid == 0) {
+        fence_mbar_init();
+        asm volatile("prefetch.tensormap [%0];" ::"l"(km) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(vm) : "memory");
+    }
     __syncthreads();
     pdl_launch();
     pdl_wait();
 
     const float* ksp = a.ks; const float* vsp = a.vs;
     int seq = a.d_pos ? (*a.d_pos + 1) : a.seq_len;
-    if (a.maps) { ksp = a.ks_list[z]; vsp = a.vs_list[z]; seq = a.seq_lens[z]; }
+    if (a.ragged) { ksp = a.ks_list[z]; vsp = a.vs_list[z]; seq = a.seq_lens[z]; }
     int per = (seq + a.n_splits - 1) / a.n_splits;
     per = (per + AM_TILE - 1) / AM_TILE * AM_TILE;                               // slices start on tile boundaries
     const int kv0 = split * per, kv1 = min(kv0 + per, seq);
@@ -139,7 +151,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
         }
         reinterpret_cast<uint32_t*>(qpl + (warp * 2 + 0) * AM_HD)[lane] = hi;
         reinterpret_cast<uint32_t*>(qpl + (warp * 2 + 1) * AM_HD)[lane] = lo;
-        if (lane == 0) qsc[warp] = dq * a.scale;
+        if (lane == 0) qsc[warp] = dq * a.scale * 1.4426950408889634f;     // scores in units of log2: the softmax below is 2^x
     }
     __syncthreads();
     // B fragments of QK^T: column n = g is (head g>>1, plane g&1); k-bytes = dims 32*ks + 4c.. and +16
@@ -193,28 +205,36 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
 
         // ── online softmax for head c over the tile's 32 keys ──
         float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        float vmax = fmaxf(fmaxf(vsv[0], vsv[1]), fmaxf(vsv[2], vsv[3]));
         #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, o));
-            vmax = fmaxf(vmax, __shfl_xor_sync(0xFFFFFFFFu, vmax, o));
-        }
+        for (int o = 4; o < 32; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, o));
+        // The softmax weights of a tile are formed relative to the TILE's maximum, and the products p_j * vs_j are held as
+        // 16-bit fixed point relative to the LARGEST product of the tile, so they keep their full precision however far the
+        // tile lies below the running maximum and whatever the spread of the V scales; the tile as a whole is then scaled by
+        // tfac = 2^{tile max - running max}.  A tile always holds at least one unmasked key, so tmax is finite.
         const float m_new = fmaxf(m_run, tmax);
-        const float corr = expf(m_run - m_new);
+        const float corr = am_exp2(m_run - m_new), tfac = am_exp2(tmax - m_new);
         m_run = m_new;
-        const float dw = vmax / 32512.0f, idw = dw > 0.f ? 1.0f / dw : 0.f;
-        float psum = 0.f;
+        float psum = 0.f, pw[4], wmax = 0.f;
         #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const float pv = expf(sc[r] - m_new);            // masked keys: exp(-inf) = 0
+            const float pv = am_exp2(sc[r] - tmax);          // masked keys: 2^-inf = 0
             psum += pv;
-            const int W = head_live ? min(32512, __float2int_rn(pv * vsv[r] * idw)) : 0;
+            pw[r] = pv * vsv[r];
+            wmax = fmaxf(wmax, pw[r]);
+        }
+        #pragma unroll
+        for (int o = 4; o < 32; o <<= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xFFFFFFFFu, wmax, o));
+        const float dw = wmax / 32512.0f, idw = dw > 0.f ? 1.0f / dw : 0.f;
+        #pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int W = head_live ? min(32512, __float2int_rn(pw[r] * idw)) : 0;
             const int l8 = (int)(int8_t)(W & 0xFF), h8 = (W - l8) >> 8;
             const int key = g + 8 * r;
             wsm[(2 * c) * AM_TILE + key] = (uint8_t)h8;
             wsm[(2 * c + 1) * AM_TILE + key] = (uint8_t)l8;
         }
-        l_run = l_run * corr + psum;
+        l_run = l_run * corr + psum * tfac;
+        const float dwt = dw * tfac;
         __syncwarp();
         // B fragments of O = V^T W: column n = g; register kb holds keys 16*kb + {2c, 2c+1, 2c+8, 2c+9}
         uint32_t bw[2];
@@ -242,8 +262,8 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
                 int acc[4] = { 0, 0, 0, 0 };
                 am_mma_s8(acc, af, bw[0], bw[1]);
                 // rows g and g+8 of this MMA are dims 4*(g+16s)+j and 4*(g+8+16s)+j; columns 2c, 2c+1 = (head c, hi/lo)
-                O[(s * 4 + j) * 2 + 0] = O[(s * 4 + j) * 2 + 0] * corr + dw * (float)(acc[0] * 256 + acc[1]);
-                O[(s * 4 + j) * 2 + 1] = O[(s * 4 + j) * 2 + 1] * corr + dw * (float)(acc[2] * 256 + acc[3]);
+                O[(s * 4 + j) * 2 + 0] = O[(s * 4 + j) * 2 + 0] * corr + dwt * (float)(acc[0] * 256 + acc[1]);
+                O[(s * 4 + j) * 2 + 1] = O[(s * 4 + j) * 2 + 1] * corr + dwt * (float)(acc[2] * 256 + acc[3]);
             }
         }
         __syncwarp();
@@ -277,7 +297,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
         float L = 0.f, acc = 0.f;
         #pragma unroll
         for (int w = 0; w < AM_WARPS; ++w) {
-            const float e = expf(sm_m[w * 4 + h] - M);
+            const float e = am_exp2(sm_m[w * 4 + h] - M);
             L += sm_l[w * 4 + h] * e;
             acc += sm_o[(w * 4 + h) * AM_HD + d] * e;
         }
@@ -305,17 +325,23 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 2) attn_tma_kernel(const __grid
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // every slice's (m, l) by one parallel load, the weights e_s = e^{m_s - M} once per head, then each thread sums its
+    // dimension over the slices with independent loads (n_splits <= 64 < 128 threads)
+    float* mg_m = sm_m; float* mg_l = sm_m + 64; float* mg_e = sm_m + 128;
     for (int h = 0; h < G; ++h) {
         const int head = kvh * G + h;
         const float* pb = a.part + ((size_t)z * a.n_heads + head) * a.n_splits * (AM_HD + 2);
+        __syncthreads();
+        if (tid < a.n_splits) { mg_m[tid] = __ldcg(pb + (size_t)tid * (AM_HD + 2)); mg_l[tid] = __ldcg(pb + (size_t)tid * (AM_HD + 2) + 1); }
+        __syncthreads();
         float M = -FLT_MAX;
-        for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(pb + (size_t)s * (AM_HD + 2)));
+        for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, mg_m[s]);
+        if (tid < a.n_splits) mg_e[tid] = am_exp2(mg_m[tid] - M);
+        __syncthreads();
         float L = 0.f, acc = 0.f;
-        for (int s = 0; s < a.n_splits; ++s) {
-            const float e = expf(__ldcg(pb + (size_t)s * (AM_HD + 2)) - M);
-            L += __ldcg(pb + (size_t)s * (AM_HD + 2) + 1) * e;
-            acc += __ldcg(pb + (size_t)s * (AM_HD + 2) + 2 + d) * e;
-        }
+        for (int s = 0; s < a.n_splits; ++s) L += mg_l[s] * mg_e[s];
+        #pragma unroll 8
+        for (int s = 0; s < a.n_splits; ++s) acc += __ldcg(pb + (size_t)s * (AM_HD + 2) + 2 + d) * mg_e[s];
         a.out[((size_t)z * a.n_heads + head) * AM_HD + d] = __float2half_rn(L > 0.f ? acc * (1.0f / L) : 0.f);
     }
 }
@@ -347,9 +373,11 @@ bool attn_tma_encode(void* map_out, const void* base, int rows, int n_kv) {
     const cuuint64_t gstr[1] = { (cuuint64_t)n_kv * AM_HD };
     const cuuint32_t box[2] = { (cuuint32_t)AM_HD, (cuuint32_t)AM_TILE };
     const cuuint32_t estr[2] = { 1, 1 };
-    return fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    alignas(64) CUtensorMap m;               // the driver wants a 64-byte aligned object; map_out may be any 128-byte slot
+    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return false;
+    memcpy(map_out, &m, sizeof m);
+    return true;
 }
 
 static bool am_capturing(cudaStream_t st) {
@@ -358,9 +386,9 @@ static bool am_capturing(cudaStream_t st) {
     return cs != cudaStreamCaptureStatusNone;
 }
 
-// Slices: enough CTAs for two per SM, never shorter than 128 keys, at most 64.
+// Slices: enough CTAs for three per SM, never shorter than 128 keys, at most 64 (the merge holds one slice per thread).
 static int am_splits(int seq, int n_kv, int batch, int sm_count) {
-    const int want = (2 * sm_count + n_kv * batch - 1) / (n_kv * batch);
+    const int want = (3 * sm_count + n_kv * batch - 1) / (n_kv * batch);
     int by_len = seq / 128;
     if (by_len < 1) by_len = 1;
     int ns = want < by_len ? want : by_len;
@@ -369,7 +397,7 @@ static int am_splits(int seq, int n_kv, int batch, int sm_count) {
 }
 
 // The TMA path needs to know how many rows a cache holds (the tensor map's extent): a length by value, a device-side
-// position together with max_seq, or a plan of prebuilt maps for a ragged batch.
+// position together with max_seq, or a plan of prebuilt maps (a host array) for a ragged batch.
 bool attention_tma_applies(const AttnCall& c) {
     const int G = c.n_kv > 0 ? c.n_heads / c.n_kv : 0;
     if (!(c.kv_int8 && c.hd == AM_HD && c.chd == AM_HD && c.window == 0 && c.causal_start < 0 && (G == 1 || G == 2 || G == 4) && c.n_heads == G * c.n_kv))
@@ -380,19 +408,26 @@ bool attention_tma_applies(const AttnCall& c) {
     return c.d_pos ? c.max_seq > 0 : c.seq_len > 0;
 }
 
+template <int NSEQ>
+static int am_launch(const AmMaps<NSEQ>& mp, const AmArgs& a, int G, dim3 grid, DeviceCtx* cx, cudaStream_t st) {
+    auto kern = G == 4 ? attn_tma_kernel<4, NSEQ> : (G == 2 ? attn_tma_kernel<2, NSEQ> : attn_tma_kernel<1, NSEQ>);
+    const int gi = (G == 4 ? 2 : (G == 2 ? 1 : 0)) + (NSEQ == 1 ? 0 : 3);
+    if (!cx->attn_tma_attr[gi]) { JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AM_SMEM)); cx->attn_tma_attr[gi] = true; }
+    JB_CUDA(launch_k(kern, grid, dim3(AM_WARPS * 32), (size_t)AM_SMEM, st, pdl_enabled(), mp, a));
+    count_launch();
+    return JB_OK;
+}
+
 int launch_attention_tma(const AttnCall& c, cudaStream_t st) {
     DeviceCtx* cx = ctx();
     if (!cx) return JB_ERR_CUDA;
     const int batch = c.batch > 0 ? c.batch : 1;
     const int rows = c.tma_maps ? c.max_seq : (c.d_pos ? c.max_seq : c.seq_len);
-    alignas(64) CUtensorMap kmap, vmap;
-    memset(&kmap, 0, sizeof kmap); memset(&vmap, 0, sizeof vmap);
-    if (!c.tma_maps && (!attn_tma_encode(&kmap, c.k, rows, c.n_kv) || !attn_tma_encode(&vmap, c.v, rows, c.n_kv)))
-        return set_error(JB_ERR_CUDA, "attention: tensor map for the KV cache refused");
     int n_splits = c.n_splits > 0 ? c.n_splits : am_splits(rows > 0 ? rows : 1, c.n_kv, batch, cx->sm_count);
+    if (n_splits > 64) n_splits = 64;                       // the merge holds one slice per thread of the last CTA
     AmArgs a = {};
     a.out = c.out; a.q = c.q; a.ks = c.ks; a.vs = c.vs;
-    a.maps = reinterpret_cast<const CUtensorMap*>(c.tma_maps); a.ks_list = c.ks_list; a.vs_list = c.vs_list; a.seq_lens = c.seq_lens;
+    a.ragged = c.tma_maps ? 1 : 0; a.ks_list = c.ks_list; a.vs_list = c.vs_list; a.seq_lens = c.seq_lens;
     a.n_heads = c.n_heads; a.n_kv = c.n_kv; a.seq_len = c.seq_len; a.d_pos = c.d_pos; a.scale = c.scale; a.status = cx->d_status;
     if (n_splits > 1) {
         // partials in the per-device split buffer; one ticket word per (sequence, kv head) in a per-device array that is zeroed
@@ -403,11 +438,23 @@ int launch_attention_tma(const AttnCall& c, cudaStream_t st) {
     }
     a.n_splits = n_splits;
     const int G = c.n_heads / c.n_kv;
-    auto kern = G == 4 ? attn_tma_kernel<4> : (G == 2 ? attn_tma_kernel<2> : attn_tma_kernel<1>);
-    const int gi = G == 4 ? 2 : (G == 2 ? 1 : 0);
-    if (!cx->attn_tma_attr[gi]) { JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AM_SMEM)); cx->attn_tma_attr[gi] = true; }
-    JB_CUDA(launch_k(kern, dim3(c.n_kv, n_splits, batch), dim3(AM_WARPS * 32), (size_t)AM_SMEM, st, pdl_enabled(), kmap, vmap, a));
-    count_launch();
+    if (!c.tma_maps) {
+        alignas(64) AmMaps<1> mp;
+        if (!attn_tma_encode(&mp.m[0], c.k, rows, c.n_kv) || !attn_tma_encode(&mp.m[1], c.v, rows, c.n_kv))
+            return set_error(JB_ERR_CUDA, "attention: tensor map for the KV cache refused");
+        return am_launch<1>(mp, a, G, dim3(c.n_kv, n_splits, 1), cx, st);
+    }
+    // ragged batch: c.tma_maps is a HOST array of [batch][K, V] maps; groups of AM_BATCH_SEQS sequences per launch
+    const CUtensorMap* hm = reinterpret_cast<const CUtensorMap*>(c.tma_maps);
+    for (int z0 = 0; z0 < batch; z0 += AM_BATCH_SEQS) {
+        const int n = batch - z0 < AM_BATCH_SEQS ? batch - z0 : AM_BATCH_SEQS;
+        alignas(64) AmMaps<AM_BATCH_SEQS> mp;
+        memcpy(mp.m, hm + 2 * z0, (size_t)n * 2 * sizeof(CUtensorMap));
+        for (int i = 2 * n; i < 2 * AM_BATCH_SEQS; ++i) mp.m[i] = mp.m[0];
+        a.z0 = z0;
+        const int rc = am_launch<AM_BATCH_SEQS>(mp, a, G, dim3(c.n_kv, n_splits, n), cx, st);
+        if (rc) return rc;
+    }
     return JB_OK;
 }
 

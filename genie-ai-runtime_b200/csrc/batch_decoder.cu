@@ -77,7 +77,7 @@ struct jllm_b200_batch_decoder {
     int *state = nullptr, *tokens = nullptr, *seq_lens = nullptr, *out_tokens = nullptr, *prompt_dev = nullptr;
     int out_cap = 0, prompt_cap = 0;
     void** lists = nullptr;            // device: [layer][4 (k, v, k scales, v scales)][B] pointers
-    unsigned char* maps = nullptr;     // device: [layer][B][K, V] TMA tensor maps of the caches (128 bytes each)
+    std::vector<unsigned char> maps;   // host: [layer][B][K, V] TMA tensor maps of the caches (128 bytes each), passed to the kernel as parameters
     void* slab = nullptr;
     int kernels_per_step = 0;
     cudaGraphExec_t graph_exec = nullptr;   // one decode step from the device-side state
@@ -107,7 +107,7 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         AttnCall c;
         c.out = d->att; c.q = d->q; c.k_list = (const void* const*)L; c.v_list = (const void* const*)(L + B);
         c.ks_list = (const float* const*)(L + 2 * B); c.vs_list = (const float* const*)(L + 3 * B); c.seq_lens = d->seq_lens;
-        c.tma_maps = d->maps ? d->maps + (size_t)l * B * 2 * 128 : nullptr;
+        c.tma_maps = d->maps.empty() ? nullptr : d->maps.data() + (size_t)l * B * 2 * 128;
         c.batch = B; c.max_seq = m.max_context; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads; c.hd = m.head_dim; c.chd = m.head_dim;
         c.scale = scale; c.kv_int8 = 1;
         BCHK(launch_attention(c, st));
@@ -183,8 +183,7 @@ jllm_b200_batch_decoder* jllm_b200_batch_decoder_create(const jllm_b200_model_de
             for (int b = 0; b < B && ok; ++b)
                 ok = attn_tma_encode(&maps[(((size_t)l * B + b) * 2 + 0) * 128], d->kv[b].key_ptr(l, 0), model->max_context, model->n_kv_heads) &&
                      attn_tma_encode(&maps[(((size_t)l * B + b) * 2 + 1) * 128], d->kv[b].val_ptr(l, 0), model->max_context, model->n_kv_heads);
-        if (ok && cudaMalloc((void**)&d->maps, maps.size()) == cudaSuccess) cudaMemcpy(d->maps, maps.data(), maps.size(), cudaMemcpyHostToDevice);
-        else { cudaGetLastError(); d->maps = nullptr; }      // the row-copy attention kernel serves the pointer lists instead
+        if (ok) d->maps.swap(maps);       // else: the general attention kernel serves the pointer lists
     }
     // scratch the kernels would otherwise grow on first use
     size_t need = 0;
@@ -202,7 +201,6 @@ void jllm_b200_batch_decoder_destroy(jllm_b200_batch_decoder* d) {
     if (!d) return;
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->slab) cudaFree(d->slab);
-    if (d->maps) cudaFree(d->maps);
     for (auto& p : d->kv) p.destroy();
     delete d;
 }

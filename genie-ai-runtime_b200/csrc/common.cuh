@@ -47,7 +47,8 @@ struct DeviceCtx {
     RopeTable rope[8]; int n_rope = 0;
     bool gemv_attr[8] = { false, false, false, false, false, false, false, false };
     bool gemv_chain_attr = false;
-    bool attn_tma_attr[3] = { false, false, false };
+    bool attn_tma_attr[6] = { false, false, false, false, false, false };
+    bool attn_prefill_attr[3] = { false, false, false };
     unsigned int* attn_tickets = nullptr;   // ATTN_TICKET_WORDS zeroed words: slice counters of the TMA attention kernel
     int  gemv_smem_budget = 0;          // dynamic shared memory of a GEMV CTA that shares its SM with one other CTA
 };

@@ -9,6 +9,7 @@
 #include "gemv.cuh"
 #include "elementwise.cuh"
 #include "attention.cuh"
+#include "mmq.cuh"
 #include "tp.cuh"
 #include <cfloat>
 #include <cstdlib>
@@ -98,6 +99,12 @@ struct jllm_b200_decoder {
     int tp_off[6] = {0, 0, 0, 0, 0, 0};
     int nh_l = 0, nkv_l = 0, I_l = 0, H_l = 0, V_l = 0;
     uint32_t* seq = nullptr;
+    // batched prompt prefill (flag bit 4): activations of up to pf_cap prompt tokens, allocated on first use
+    bool batched_prefill = false;
+    void* pf_slab = nullptr; int pf_cap = 0, pf_chunk = 2048;
+    __half *pf_x = nullptr, *pf_x2 = nullptr, *pf_normed = nullptr, *pf_y = nullptr, *pf_q = nullptr, *pf_att = nullptr, *pf_k = nullptr,
+           *pf_v = nullptr, *pf_gate = nullptr, *pf_up = nullptr, *pf_sw = nullptr;
+    int* pf_tokens = nullptr;
 };
 
 static int dec_alloc(jllm_b200_decoder* d) {
@@ -348,6 +355,60 @@ static int dec_graph_for(jllm_b200_decoder* d, int n_splits, cudaStream_t st) {
     return JB_OK;
 }
 
+// ── batched prompt prefill: the reference's Engine::transformer_prefill (src/engine/decode.cu:1760-1884) for a chunk of
+// N >= 2 prompt tokens at positions start .. start+N-1: RMSNorm over rows, batched K-quant products (prefill arithmetic),
+// QK-norm + RoPE + INT8 KV store for all tokens in one launch, query-tiled causal attention, Wo, residual, RMSNorm,
+// gate/up, SwiGLU, W_down, residual.  After the last chunk: final norm and logits of the last token only, greedy token.
+static int dec_prefill_alloc(jllm_b200_decoder* d, int cap) {
+    if (cap <= d->pf_cap) return JB_OK;
+    if (d->pf_slab) { cudaFree(d->pf_slab); d->pf_slab = nullptr; d->pf_cap = 0; }
+    const jllm_b200_model_desc& m = d->m;
+    const size_t N = (size_t)cap, H = m.hidden_dim, QD = (size_t)m.n_heads * m.head_dim, KVD = (size_t)m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
+    auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t total = 4 * al(N * H * 2) + 2 * al(N * QD * 2) + 2 * al(N * KVD * 2) + 3 * al(N * I * 2) + al(N * 4);
+    if (cudaMalloc(&d->pf_slab, total) != cudaSuccess) { cudaGetLastError(); return set_error(JB_ERR_NOMEM, "decoder: %zu B of prefill activations", total); }
+    char* p = (char*)d->pf_slab;
+    auto take = [&](size_t b) { char* r = p; p += al(b); return r; };
+    d->pf_x = (__half*)take(N * H * 2); d->pf_x2 = (__half*)take(N * H * 2); d->pf_normed = (__half*)take(N * H * 2); d->pf_y = (__half*)take(N * H * 2);
+    d->pf_q = (__half*)take(N * QD * 2); d->pf_att = (__half*)take(N * QD * 2);
+    d->pf_k = (__half*)take(N * KVD * 2); d->pf_v = (__half*)take(N * KVD * 2);
+    d->pf_gate = (__half*)take(N * I * 2); d->pf_up = (__half*)take(N * I * 2); d->pf_sw = (__half*)take(N * I * 2);
+    d->pf_tokens = (int*)take(N * 4);
+    d->pf_cap = cap;
+    return JB_OK;
+}
+
+static int dec_prefill_chunk(jllm_b200_decoder* d, const int* dev_tokens, int N, int start, cudaStream_t st) {
+    const jllm_b200_model_desc& m = d->m;
+    const int H = m.hidden_dim, QD = m.n_heads * m.head_dim, KVD = m.n_kv_heads * m.head_dim, I = m.intermediate_dim;
+    const float scale = 1.0f / sqrtf((float)m.head_dim);
+    DCHK(launch_embed_rows(d->pf_x, m.tok_embd, m.embd_type, dev_tokens, N, H, st));
+    for (int l = 0; l < m.n_layers; ++l) {
+        const jllm_b200_layer_desc& w = d->layers[l];
+        int8_t* kc = (int8_t*)d->kv.key_ptr(l, 0); int8_t* vc = (int8_t*)d->kv.val_ptr(l, 0);
+        float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
+        DCHK(launch_rmsnorm(d->pf_normed, d->pf_x, nullptr, w.rms_attn, true, N, H, m.rms_eps, st));
+        DCHK(launch_mmq(d->pf_q, resolve_weight(w.wq), w.type_wq, d->pf_normed, QD, N, H, nullptr, st));
+        DCHK(launch_mmq(d->pf_k, resolve_weight(w.wk), w.type_wk, d->pf_normed, KVD, N, H, nullptr, st));
+        DCHK(launch_mmq(d->pf_v, resolve_weight(w.wv), w.type_wv, d->pf_normed, KVD, N, H, nullptr, st));
+        DCHK(launch_qkv_prep_tokens(d->pf_q, d->pf_k, d->pf_v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, N, m.n_heads, m.n_kv_heads,
+                                    m.head_dim, start, m.rope_theta, m.rope_neox != 0, st));
+        AttnCall c;
+        c.out = d->pf_att; c.q = d->pf_q; c.k = kc; c.v = vc; c.ks = ks; c.vs = vs; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads;
+        c.hd = m.head_dim; c.chd = m.head_dim; c.scale = scale; c.kv_int8 = 1; c.causal_start = start; c.batch = N; c.n_splits = 1;
+        DCHK(attention_prefill_fast_applies(c) ? launch_attention_prefill_fast(c, st) : launch_attention_general(c, st));
+        DCHK(launch_mmq(d->pf_y, resolve_weight(w.wo), w.type_wo, d->pf_att, H, N, QD, nullptr, st));
+        DCHK(launch_add_half(d->pf_x2, d->pf_x, d->pf_y, (long long)N * H, st));
+        DCHK(launch_rmsnorm(d->pf_normed, d->pf_x2, nullptr, w.rms_ffn, true, N, H, m.rms_eps, st));
+        DCHK(launch_mmq(d->pf_gate, resolve_weight(w.w_gate), w.type_w_gate, d->pf_normed, I, N, H, nullptr, st));
+        DCHK(launch_mmq(d->pf_up, resolve_weight(w.w_up), w.type_w_up, d->pf_normed, I, N, H, nullptr, st));
+        DCHK(launch_glu(d->pf_sw, d->pf_gate, d->pf_up, N, I, false, st));
+        DCHK(launch_mmq(d->pf_y, resolve_weight(w.w_down), w.type_w_down, d->pf_sw, H, N, I, nullptr, st));
+        DCHK(launch_add_half(d->pf_x, d->pf_x2, d->pf_y, (long long)N * H, st));
+    }
+    return JB_OK;
+}
+
 extern "C" {
 
 jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, int flags) {
@@ -361,7 +422,7 @@ jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, i
     d->m = *model;
     d->layers.assign(model->layers, model->layers + model->n_layers);
     d->m.layers = d->layers.data();
-    d->fused = (flags & 1) != 0; d->use_graph = (flags & 2) != 0; d->chain = (flags & 8) != 0;
+    d->fused = (flags & 1) != 0; d->use_graph = (flags & 2) != 0; d->chain = (flags & 8) != 0; d->batched_prefill = (flags & 16) != 0;
     jllm::KVCachePool::Config c = { model->n_layers, model->n_kv_heads, model->head_dim, model->max_context, 0, 1 };
     if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); delete d; return nullptr; }
     if (dec_alloc(d)) { d->kv.destroy(); delete d; return nullptr; }
@@ -381,7 +442,19 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
     if (model->hidden_dim % QK_K || model->intermediate_dim % QK_K || (model->n_heads * hd) % QK_K || model->intermediate_dim < model->hidden_dim) {
         set_error(JB_ERR_ARG, "decoder: hidden/intermediate/q dims must be multiples of 256, intermediate >= hidden"); return nullptr;
     }
+    // every sharded product pushes its rows from the epilogue of the streaming GEMV, which exists for Q4_K and Q6_K only
+    for (int l = 0; l < model->n_layers; ++l) {
+        const jllm_b200_layer_desc& w = model->layers[l];
+        const int ts[7] = { w.type_wq, w.type_wk, w.type_wv, w.type_wo, w.type_w_gate, w.type_w_up, w.type_w_down };
+        for (int t : ts)
+            if (t != T_Q4K && t != T_Q6K) { set_error(JB_ERR_TYPE, "decoder: ggml type %d in layer %d has no tensor-parallel path (Q4_K and Q6_K only)", t, l); return nullptr; }
+    }
+    if (model->output_type != T_Q4K && model->output_type != T_Q6K) { set_error(JB_ERR_TYPE, "decoder: output type %d has no tensor-parallel path", model->output_type); return nullptr; }
     if (!ctx()) return nullptr;
+    // This rank's own region may hold the packets of an earlier session, whose epochs would pass for fresh ones: clear it.
+    // (The caller must let every rank finish its create before any rank runs a step: a barrier, as TPDecoder does.)
+    if (cudaMemset(regions[rank], 0, jllm_b200_tp_region_bytes(model->hidden_dim, model->n_heads * hd, model->intermediate_dim)) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) { cuda_error(cudaGetLastError(), "cudaMemset(exchange region)"); return nullptr; }
     jllm_b200_decoder* d = new (std::nothrow) jllm_b200_decoder();
     if (!d) return nullptr;
     d->m = *model;
@@ -409,6 +482,7 @@ void jllm_b200_decoder_destroy(jllm_b200_decoder* d) {
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->own_stream) cudaStreamDestroy(d->own_stream);
     if (d->slab) cudaFree(d->slab);
+    if (d->pf_slab) cudaFree(d->pf_slab);
     if (d->seq) cudaFree(d->seq);
     d->kv.destroy();
     delete d;
@@ -427,6 +501,44 @@ int jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, void* 
     return dec_enqueue_step(d, splits_for_ctx(d, position), st);
 }
 
+int jllm_b200_decoder_prefill(jllm_b200_decoder* d, const int* host_tokens, int n_tokens, int start_pos, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d->tp_on) return set_error(JB_ERR_STATE, "decoder: batched prefill is not available in a tensor-parallel session");
+    if (!host_tokens || n_tokens < 2) return set_error(JB_ERR_ARG, "decoder: batched prefill needs at least two tokens (got %d)", n_tokens);
+    if (start_pos < 0 || start_pos + n_tokens > d->m.max_context) return set_error(JB_ERR_LIMIT, "decoder: positions %d..%d exceed the context of %d", start_pos, start_pos + n_tokens - 1, d->m.max_context);
+    for (int i = 0; i < n_tokens; ++i)
+        if (host_tokens[i] < 0 || host_tokens[i] >= d->m.vocab_size) return set_error(JB_ERR_ARG, "decoder: prompt token %d outside the vocabulary", host_tokens[i]);
+    const int chunk = d->pf_chunk < 2 ? 2 : d->pf_chunk;
+    DCHK(dec_prefill_alloc(d, n_tokens < chunk ? n_tokens : chunk));
+    const jllm_b200_model_desc& m = d->m;
+    const int H = m.hidden_dim;
+    int done = 0, last_n = 0;
+    while (done < n_tokens) {
+        int n = n_tokens - done < chunk ? n_tokens - done : chunk;
+        if (n_tokens - done - n == 1) --n;                  // never leave a chunk of one token: a batched product needs two
+        JB_CUDA(cudaMemcpyAsync(d->pf_tokens, host_tokens + done, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, st));
+        DCHK(dec_prefill_chunk(d, d->pf_tokens, n, start_pos + done, st));
+        done += n; last_n = n;
+    }
+    // logits of the last prompt token only (src/engine/decode.cu:2019-2050), greedy token on the device; the step state
+    // moves to the position after the prompt, so jllm_b200_decoder_step_device continues from there
+    JB_CUDA(launch_k(set_state_kernel, dim3(1), dim3(32), 0, st, false, d->state, start_pos + n_tokens - 1, host_tokens[n_tokens - 1]));
+    count_launch();
+    DCHK(launch_rmsnorm(d->normed, d->pf_x + (size_t)(last_n - 1) * H, nullptr, m.output_norm, true, 1, H, m.rms_eps, st));
+    DCHK(jllm_b200_gemv_quant_f32(d->logits, m.output, m.output_type, d->normed, m.vocab_size, H, st));
+    const int ag = m.vocab_size >= 64 * 1024 ? 64 : (m.vocab_size + 1023) / 1024;
+    JB_CUDA(launch_k(argmax_advance_kernel, dim3(ag), dim3(1024), 0, st, pdl_enabled(), (const float*)d->logits, m.vocab_size, d->state,
+                     d->out_tokens, d->out_cap, (unsigned int*)(d->state + 32)));
+    count_launch();
+    d->host_pos = start_pos + n_tokens;
+    return JB_OK;
+}
+int jllm_b200_decoder_set_prefill_chunk(jllm_b200_decoder* d, int tokens) {
+    if (tokens < 2) return set_error(JB_ERR_ARG, "decoder: prefill chunk of %d tokens", tokens);
+    d->pf_chunk = tokens;
+    return JB_OK;
+}
+
 int jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (d->use_graph && (st == nullptr || st == cudaStreamLegacy)) {
@@ -438,6 +550,16 @@ int jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int
     if (n_prompt + n_new > d->m.max_context) return set_error(JB_ERR_LIMIT, "decoder: %d tokens exceed the context of %d", n_prompt + n_new, d->m.max_context);
     for (int i = 0; i < n_prompt; ++i)
         if (host_prompt[i] < 0 || host_prompt[i] >= d->m.vocab_size) return set_error(JB_ERR_ARG, "decoder: prompt token %d outside the vocabulary", host_prompt[i]);
+    if (d->batched_prefill && !d->tp_on && n_prompt >= 2) {
+        // the prompt in one batched pass (the first generated token comes out of it), then n_new - 1 self-feeding decode steps
+        JB_CUDA(cudaMemsetAsync(d->state, 0, 64, st));
+        d->kv.clear();
+        DCHK(jllm_b200_decoder_prefill(d, host_prompt, n_prompt, 0, stream));
+        for (int s = 1; s < n_new; ++s) DCHK(jllm_b200_decoder_step_device(d, stream));
+        if (n_new > 0 && host_out) JB_CUDA(cudaMemcpyAsync(host_out, d->out_tokens, (size_t)n_new * sizeof(int), cudaMemcpyDeviceToHost, st));
+        JB_CUDA(cudaStreamSynchronize(st));
+        return jllm_b200_device_status(stream);
+    }
     JB_CUDA(cudaMemcpyAsync(d->prompt_dev, host_prompt, (size_t)n_prompt * sizeof(int), cudaMemcpyHostToDevice, st));
     JB_CUDA(cudaMemsetAsync(d->state, 0, 64, st));
     d->kv.clear();

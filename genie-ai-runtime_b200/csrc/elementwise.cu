@@ -368,14 +368,15 @@ struct QkvPrepArgs {
     // batch of independent streams at the same position (blockIdx.y = stream): activations q/k/v + y * stride, caches from lists
     int q_stride, kv_stride;
     int8_t* const* k_list; int8_t* const* v_list; float* const* ks_list; float* const* vs_list;
+    int pos_step;       // prompt prefill: row y is the token at position pos + y * pos_step of ONE cache (lists null)
 };
 __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ RopeFreq fr) {
     pdl_wait();
     const int w = blockIdx.x * blockDim.y + threadIdx.y, lane = threadIdx.x;
     const int hd = a.hd, h2 = hd / 2;
-    const int pos = a.d_pos ? *a.d_pos : a.pos;
-    if (w >= a.n_heads + 2 * a.n_kv) return;
     const int sq = blockIdx.y;
+    const int pos = (a.d_pos ? *a.d_pos : a.pos) + sq * a.pos_step;
+    if (w >= a.n_heads + 2 * a.n_kv) return;
     __half* qb = a.q + (size_t)sq * a.q_stride;
     const __half* kb = a.k + (size_t)sq * a.kv_stride; const __half* vb = a.v + (size_t)sq * a.kv_stride;
     int8_t* kcache = a.k_list ? a.k_list[sq] : a.k_cache; int8_t* vcache = a.k_list ? a.v_list[sq] : a.v_cache;
@@ -429,7 +430,7 @@ int launch_qkv_prep(__half* q, const __half* k, const __half* v, const float* q_
     if (!q || !k || !v || !k_cache || !v_cache || !k_scales || !v_scales) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
     if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
     QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, pos, d_pos, (int)neox, (int)do_rope,
-                      0, 0, nullptr, nullptr, nullptr, nullptr };
+                      0, 0, nullptr, nullptr, nullptr, nullptr, 0 };
     const int warps = n_heads + 2 * n_kv;
     JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
     count_launch();
@@ -444,9 +445,25 @@ int launch_qkv_prep_batched(__half* q, const __half* k, const __half* v, const f
     if (!q || !k || !v || !k_list || !v_list || !ks_list || !vs_list || !d_pos) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
     if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
     QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, nullptr, nullptr, nullptr, nullptr, n_heads, n_kv, hd, 0, d_pos, (int)neox, 1,
-                      n_heads * hd, n_kv * hd, k_list, v_list, ks_list, vs_list };
+                      n_heads * hd, n_kv * hd, k_list, v_list, ks_list, vs_list, 0 };
     const int warps = n_heads + 2 * n_kv;
     JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4, batch), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
+    count_launch();
+    return JB_OK;
+}
+
+// the same for the N tokens of a prompt chunk at positions start .. start+N-1 of one cache: q [N][n_heads*hd], k/v [N][n_kv*hd]
+// (Engine::transformer_prefill's per-token RoPE + KV store loop, src/engine/decode.cu:1812-1846, in one launch)
+int launch_qkv_prep_tokens(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
+                           int8_t* k_cache, int8_t* v_cache, float* k_scales, float* v_scales, int N, int n_heads, int n_kv, int hd,
+                           int start_pos, float theta, bool neox, cudaStream_t st) {
+    if (N <= 0) return JB_OK;
+    if (!q || !k || !v || !k_cache || !v_cache || !k_scales || !v_scales) return set_error(JB_ERR_PTR, "qkv_prep: null pointer");
+    if (hd <= 0 || (hd & 1) || hd > 512) return set_error(JB_ERR_ARG, "qkv_prep: head_dim=%d", hd);
+    QkvPrepArgs a = { q, k, v, q_norm, k_norm, eps, k_cache, v_cache, k_scales, v_scales, n_heads, n_kv, hd, start_pos, nullptr, (int)neox, 1,
+                      n_heads * hd, n_kv * hd, nullptr, nullptr, nullptr, nullptr, 1 };
+    const int warps = n_heads + 2 * n_kv;
+    JB_CUDA(launch_k(qkv_prep_kernel, dim3((warps + 3) / 4, N), dim3(32, 4), (size_t)4 * hd * sizeof(float), st, pdl_enabled(), a, make_rope_freq(hd, theta)));
     count_launch();
     return JB_OK;
 }

@@ -29,6 +29,9 @@ int launch_embed_rows(__half* dst, const void* W, int type, const int* d_tokens,
 int launch_qkv_prep_batched(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
                             int8_t* const* k_list, int8_t* const* v_list, float* const* ks_list, float* const* vs_list, int batch,
                             int n_heads, int n_kv, int hd, const int* d_pos, float theta, bool neox, cudaStream_t st);
+int launch_qkv_prep_tokens(__half* q, const __half* k, const __half* v, const float* q_norm, const float* k_norm, float eps,
+                           int8_t* k_cache, int8_t* v_cache, float* k_scales, float* v_scales, int N, int n_heads, int n_kv, int hd,
+                           int start_pos, float theta, bool neox, cudaStream_t st);
 int launch_add_half(__half* out, const __half* a, const __half* b, long long n, cudaStream_t st);
 
 }  // namespace jb

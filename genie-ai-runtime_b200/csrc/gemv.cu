@@ -26,16 +26,16 @@
 
 namespace jb {
 
-// Stream kernel: a CTA takes HALF an SM (at most 14 warps at 72 registers, half the shared memory), and a launch puts
+// Stream kernel: a CTA takes HALF an SM (at most 12 warps at 85 registers, half the shared memory), and a launch puts
 // one CTA on every SM.  The other half is where the CTAs of the NEXT kernel in the stream become resident as soon as
 // this one has issued griddepcontrol.launch_dependents: they set up their barriers and start the bulk copies of their
 // first row groups while this kernel is still computing, so HBM keeps streaming across kernel boundaries.
-constexpr int GV_MAXWARPS = 14;
+constexpr int GV_MAXWARPS = 12;
 constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
 constexpr int GV_CHAINWARPS = 20;              // the chain kernel keeps a whole SM per CTA (its phases overlap inside one launch)
 constexpr int GV_CHAINTHREADS = GV_CHAINWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
-constexpr int GV_NTRACE = 8;                   // time stamps per CTA of a traced launch
+constexpr int GV_NTRACE = 16;                  // time stamps per CTA of a traced launch
 
 struct GvSegDev {
     const uint8_t* W; void* y; int M; int type;
@@ -52,6 +52,7 @@ struct GvParams {
     int do_norm; const void* norm_w; int norm_w_fp32; float eps;
     int32_t* dbg_dots; int* status;
     unsigned long long* trace;  // diagnostic launches only: GV_NTRACE time stamps per CTA
+    int trace_nocompute;        // diagnostic: stream the weights but skip the dot products
     int slot_bytes, nslots, needA, needB, paired_rows, nwarps;
     int nchunk, chunk_blocks;   // a row group is streamed as nchunk tasks of chunk_blocks super-blocks per row (nchunk > 1 only with R = 1)
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
@@ -74,11 +75,6 @@ void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
 }
 
 // ── activation staging ───────────────────────────────────────────────────
-// Layout A (read by Q4_K items), per 256 elements: the 16-element run r = 2*(j>>1)+h of sub-block j = 2*il + p
-// (p = 0: low-nibble partners, p = 1: high-nibble partners) sits at p*128 + (16*r ^ 16*(blk&1)) — the xor keeps
-// the 16-byte reads of eight neighbouring lanes (two blocks x four il) on different banks.  Layout B (Q6_K
-// items): plane k (= 32-wide quarter of a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a
-// second plane with the low bytes follows at +K.
 // Eight consecutive activations as floats: a 16-byte load of the plain fp16 vector, or, for a vector that arrives from
 // the other ranks, 64 bytes of packets polled (bounded) until every epoch word matches; the packets are read past L1.
 __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epoch, float (&v)[8]) {
@@ -128,17 +124,56 @@ __device__ __forceinline__ void gv_norm_w8(const GvParams& p, int it, float (&wn
     }
 }
 
+// Sixteen bytes (eight fp16 activations) of the plain vector.
+__device__ __forceinline__ uint4 gv_raw8(const GvParams& p, int it) {
+    // inside a chain the vector was written earlier in this launch: read it past L1, which may hold older lines
+    return p.chained ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
+}
+__device__ __forceinline__ void gv_unpack8(const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = a.x; v[2 * i + 1] = a.y;
+    }
+}
+
+constexpr int GV_STAGE_REGS = 4;    // staging items (16 bytes each) a thread fetches up front and keeps in registers
+
+// Activation image in shared memory.  Layout A (Q4_K): the int8 codes of super-block b in natural order, cut into
+// sixteen 16-byte chunks j and stored chunk-major, chunk j of block b at (j * nb + b) * 16 — the lanes of a warp work
+// on consecutive super-blocks, so their 16-byte reads are consecutive.  Layout B (Q6_K): plane k (= 32-wide quarter of
+// a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a second plane with the low bytes follows at +K.
+// Group scales xd / xs: four floats of half h of block b at ((h * nb + b) * 4).
+//
 // `wpre`: the norm weights of this thread's first staging item, loaded by the caller before it waited for the
 // producer kernel (they do not depend on it), so their trip to L2 is off the critical path; have_pre = false: none.
 template <int XM>
 __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red, const float (&wpre)[8], bool have_pre) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nw_cta = blockDim.x >> 5;
-    const int K = p.K;
+    const int K = p.K, nitems = K / 8, nb = K / QK_K;
     const uint32_t epoch = p.tp_wait_on ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
+    const bool direct = !p.tp_wait_on;
+    // every item of this thread is requested before any is used: one trip to L2, not one per item
+    uint4 raw[GV_STAGE_REGS];
+    #pragma unroll
+    for (int k = 0; k < GV_STAGE_REGS; ++k) {
+        const int it = tid + k * nthreads;
+        raw[k] = (direct && it < nitems) ? gv_raw8(p, it) : make_uint4(0u, 0u, 0u, 0u);
+    }
     float rrms = 1.0f;
     if (p.do_norm) {   // reference: fused_rmsnorm_residual, src/kernels/fused_norm.cu:33-101
         float ss = 0.f;
-        for (int g8 = tid; g8 < K / 8; g8 += nthreads) {
+        if (direct) {
+            #pragma unroll
+            for (int k = 0; k < GV_STAGE_REGS; ++k) {      // lanes past the end hold zeros
+                float a[8];
+                gv_unpack8(raw[k], a);
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) ss += a[2 * i] * a[2 * i] + a[2 * i + 1] * a[2 * i + 1];
+            }
+        }
+        for (int g8 = tid + (direct ? GV_STAGE_REGS * nthreads : 0); g8 < nitems; g8 += nthreads) {
             float a[8];
             gv_load8(p, g8, epoch, a);
             #pragma unroll
@@ -155,16 +190,14 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     float* xd = reinterpret_cast<float*>(smem + p.off_xd);
     float* xs = reinterpret_cast<float*>(smem + p.off_xs);
     int*   xsum = reinterpret_cast<int*>(smem + p.off_xsum);
-    // Four threads per 32-element group, eight elements each (one 16-byte load); the group's absmax and sums are
-    // combined with two xor-shuffles inside the quad.  K is a multiple of 256, so K/8 is a multiple of 32 and a warp is
-    // either entirely inside the loop or entirely outside: the shuffles are always between live lanes.
-    for (int it = tid; it < K / 8; it += nthreads) {
+    // Four threads per 32-element group, eight elements each; the group's absmax and sums are combined with two
+    // xor-shuffles inside the quad.  K is a multiple of 256, so K/8 is a multiple of 32 and a warp is either entirely
+    // inside an iteration or entirely outside: the shuffles are always between live lanes.
+    auto quantise = [&](int it, float (&v)[8], bool pre) {
         const int gi = it >> 2, q4 = it & 3;
-        float v[8];
-        gv_load8(p, it, epoch, v);
         if (p.do_norm) {
             float wn[8];
-            if (have_pre && it == tid) {
+            if (pre) {
                 #pragma unroll
                 for (int i = 0; i < 8; ++i) wn[i] = wpre[i];
             } else {
@@ -205,7 +238,7 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         }
         const int blk = gi >> 3, j = gi & 7, h = q4 >> 1, e8 = (q4 & 1) * 8;    // 16-element half h, byte offset inside its run
         if (p.needA) {
-            const int off = blk * 256 + (j & 1) * 128 + (((2 * (j >> 1) + h) * 16) ^ ((blk & 1) << 4)) + e8;
+            const int off = ((2 * j + h) * nb + blk) * 16 + e8;
             *reinterpret_cast<uint2*>(xA + off) = make_uint2(hi[0], hi[1]);
             if (XM == 1) *reinterpret_cast<uint2*>(xA + K + off) = make_uint2(lo[0], lo[1]);
         }
@@ -217,14 +250,31 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
             if ((q4 & 1) == 0) xsum[2 * gi + h] = s16;
         }
         if (q4 == 0) {
+            const int si = ((j >> 2) * nb + blk) * 4 + (j & 3);
             if (XM == 0) {
-                xd[gi] = __half2float(__float2half_rn(d));
-                xs[gi] = __half2float(__float2half_rn(__fmul_rn(d, (float)s32)));
+                xd[si] = __half2float(__float2half_rn(d));
+                xs[si] = __half2float(__float2half_rn(__fmul_rn(d, (float)s32)));
             } else {
-                xd[gi] = d;
-                xs[gi] = fsum;
+                xd[si] = d;
+                xs[si] = fsum;
             }
         }
+    };
+    if (direct) {
+        #pragma unroll
+        for (int k = 0; k < GV_STAGE_REGS; ++k) {
+            const int it = tid + k * nthreads;
+            if (it < nitems) {                       // warp-uniform: nitems is a multiple of 32
+                float v[8];
+                gv_unpack8(raw[k], v);
+                quantise(it, v, have_pre && k == 0);
+            }
+        }
+    }
+    for (int it = tid + (direct ? GV_STAGE_REGS * nthreads : 0); it < nitems; it += nthreads) {
+        float v[8];
+        gv_load8(p, it, epoch, v);
+        quantise(it, v, have_pre && it == tid);
     }
 }
 
@@ -249,42 +299,57 @@ __device__ __forceinline__ int dot16_uu(const uint4& w, uint32_t mask, const uin
 }
 
 // shared addresses of the staged activation image
-struct GvX { uint32_t xA, xB, xd, xs, xsum; int K; };
+struct GvX { uint32_t xA, xB, xd, xs, xsum; int K, nb; };
 
-// ── Q4_K: one 32-byte group of quants per lane ───────────────────────────
-// Group il (0..3) of a block holds the low nibbles of sub-block 2*il and the high nibbles of sub-block
-// 2*il+1, 32 elements each.  The lane builds both complete 32-element integer dots — the accumulators the
-// reference builds with eight dp4a each (src/kernels/gemv_q4.cu:487-494) — and folds them as
-//   dall * (sc0*dot0*d8_0 + sc1*dot1*d8_1) - dmin * (m0*s8_0 + m1*s8_1)
-// which is the reference's  Σ dall*sc*(d8*dot) - dmin*m*s8  (:499) with the common factors taken out.
-// `sb` = shared address of the block, il is fixed per lane.
+// ── Q4_K: one whole super-block (256 weights) per lane ───────────────────
+// Group il (0..3) of a block holds the low nibbles of sub-block 2*il and the high nibbles of sub-block 2*il+1, 32
+// elements each.  The lane builds all eight 32-element integer dots — the accumulators the reference builds with eight
+// dp4a each (src/kernels/gemv_q4.cu:487-494) — and folds them as
+//   dall * Σ_j sc_j*dot_j*d8_j  -  dmin * Σ_j m_j*s8_j
+// which is the reference's  Σ dall*sc*(d8*dot) - dmin*m*s8  (:499) with the common factors taken out.  The header is
+// read once and the eight 6-bit scales and mins are unpacked four at a time with word-wide masks
+// (get_scale_min_k4, :185-195).  `sb` = shared address of the block (16-byte aligned).
 template <int XM>
-__device__ __forceinline__ float q4k_item(uint32_t sb, int il, int kblk, const GvX& X, int& dot0, int& dot1) {
+__device__ __forceinline__ float q4k_block(uint32_t sb, int kblk, const GvX& X, int32_t* dots_out) {
     const uint4 hdr = lds128(sb);
-    const uint4 w0 = lds128(sb + 16 + 32 * il), w1 = lds128(sb + 32 + 32 * il);
-    const uint32_t xa = X.xA + kblk * 256 + ((32 * il) ^ ((kblk & 1) << 4));   // the two 16-byte runs sit at xa and xa^16
-    const uint4 xl0 = lds128(xa), xl1 = lds128(xa ^ 16), xh0 = lds128(xa + 128), xh1 = lds128((xa ^ 16) + 128);
-    if (XM == 0) {
-        dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
-        dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
-    } else {
-        const uint32_t xb = xa + X.K;
-        const uint4 yl0 = lds128(xb), yl1 = lds128(xb ^ 16), yh0 = lds128(xb + 128), yh1 = lds128((xb ^ 16) + 128);
-        dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
-               (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
-        dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
-                ((dot16_uu(w0, 0xF0F0F0F0u, yh0) + dot16_uu(w1, 0xF0F0F0F0u, yh1)) >> 4));
+    const uint32_t sc03 = hdr.y & 0x3F3F3F3Fu, mn03 = hdr.z & 0x3F3F3F3Fu;                         // sub-blocks 0..3, a byte each
+    const uint32_t sc47 = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);                    // sub-blocks 4..7
+    const uint32_t mn47 = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    const uint32_t step = (uint32_t)X.nb * 16u;                 // bytes between consecutive 16-byte chunks of one block's codes
+    const uint32_t xa = X.xA + (uint32_t)kblk * 16u;
+    const uint4 dA = lds128(X.xd + (uint32_t)kblk * 16u), dB = lds128(X.xd + (uint32_t)(X.nb + kblk) * 16u);
+    const uint4 sA = lds128(X.xs + (uint32_t)kblk * 16u), sB = lds128(X.xs + (uint32_t)(X.nb + kblk) * 16u);
+    const float d8[8] = { __uint_as_float(dA.x), __uint_as_float(dA.y), __uint_as_float(dA.z), __uint_as_float(dA.w),
+                          __uint_as_float(dB.x), __uint_as_float(dB.y), __uint_as_float(dB.z), __uint_as_float(dB.w) };
+    const float s8[8] = { __uint_as_float(sA.x), __uint_as_float(sA.y), __uint_as_float(sA.z), __uint_as_float(sA.w),
+                          __uint_as_float(sB.x), __uint_as_float(sB.y), __uint_as_float(sB.z), __uint_as_float(sB.w) };
+    float pos = 0.f, neg = 0.f;
+    #pragma unroll
+    for (int il = 0; il < 4; ++il) {
+        const uint4 w0 = lds128(sb + 16 + 32 * il), w1 = lds128(sb + 32 + 32 * il);
+        const uint32_t xc = xa + (uint32_t)(4 * il) * step;     // chunks 4il, 4il+1: sub-block 2il; 4il+2, 4il+3: sub-block 2il+1
+        const uint4 xl0 = lds128(xc), xl1 = lds128(xc + step), xh0 = lds128(xc + 2 * step), xh1 = lds128(xc + 3 * step);
+        int dot0, dot1;
+        if (XM == 0) {
+            dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
+            dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
+        } else {
+            const uint32_t yc = xc + (uint32_t)X.K;             // second plane: low bytes of the 16-bit activations
+            const uint4 yl0 = lds128(yc), yl1 = lds128(yc + step), yh0 = lds128(yc + 2 * step), yh1 = lds128(yc + 3 * step);
+            dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
+                   (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
+            dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
+                    ((dot16_uu(w0, 0xF0F0F0F0u, yh0) + dot16_uu(w1, 0xF0F0F0F0u, yh1)) >> 4));
+        }
+        if (dots_out) { dots_out[2 * il] = dot0; dots_out[2 * il + 1] = dot1; }
+        const uint32_t scw = il < 2 ? sc03 : sc47, mnw = il < 2 ? mn03 : mn47;
+        const int sh = 16 * (il & 1);
+        const int sc0 = (int)((scw >> sh) & 0xFFu), sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
+        const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
+        pos += (float)(sc0 * dot0) * d8[2 * il] + (float)(sc1 * dot1) * d8[2 * il + 1];
+        neg += (float)m0 * s8[2 * il] + (float)m1 * s8[2 * il + 1];
     }
-    // scales / mins of sub-blocks 2*il and 2*il+1 (two adjacent bytes), both halves of get_scale_min_k4 at once
-    const int sh = 16 * (il & 1);
-    const uint32_t a = (hdr.y >> sh) & 0xFFFFu, b = (hdr.z >> sh) & 0xFFFFu, c = (hdr.w >> sh) & 0xFFFFu;
-    const bool hi = il >= 2;
-    const uint32_t sc2 = hi ? ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) : (a & 0x3F3Fu);
-    const uint32_t mn2 = hi ? (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) : (b & 0x3F3Fu);
     const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));      // (d, dmin)
-    const uint2 d8r = lds64(X.xd + (kblk * 8 + 2 * il) * 4), s8r = lds64(X.xs + (kblk * 8 + 2 * il) * 4);
-    const float pos = (float)((int)(sc2 & 0xFF) * dot0) * __uint_as_float(d8r.x) + (float)((int)(sc2 >> 8) * dot1) * __uint_as_float(d8r.y);
-    const float neg = (float)(mn2 & 0xFF) * __uint_as_float(s8r.x) + (float)(mn2 >> 8) * __uint_as_float(s8r.y);
     return dm.x * pos - dm.y * neg;
 }
 
@@ -310,7 +375,7 @@ __device__ __forceinline__ float q6k_item(uint32_t sb, int n, int c, int kblk, c
     const uint32_t sca = sb + 192 + 8 * n + c;
     const uint32_t xb = X.xB + (kblk * 4 + 2 * n + c) * 16;
     const uint32_t xsa = X.xsum + (kblk * 16 + 8 * n + c) * 4;
-    const uint4 xdr = lds128(X.xd + (kblk * 8 + 4 * n) * 4);
+    const uint4 xdr = lds128(X.xd + (uint32_t)(n * X.nb + kblk) * 16u);
     const float xdv[4] = { __uint_as_float(xdr.x), __uint_as_float(xdr.y), __uint_as_float(xdr.z), __uint_as_float(xdr.w) };
     // high bit pairs of the four quarters, already in place (bits 4-5 of every byte)
     uint32_t Hq[4][4];
@@ -341,17 +406,32 @@ __device__ __forceinline__ float q6k_item(uint32_t sb, int n, int c, int kblk, c
     return d * acc;
 }
 
-// One warp, `nrw` (<= 4) consecutive rows in shared memory: lanes stride over the rows' 32-byte items
-// (4 per super-block), each lane adds its terms into the accumulator of the row the item belongs to.
-// Item i of the group is (row i / U, block (i % U) / 4, sub-item i % 4); 32 and U are multiples of 4, so a
-// lane's sub-item never changes.
-// `rb_` = bytes between consecutive rows in shared memory, `U_` = items per row held there (a chunk of the row when the
-// row is streamed in several tasks: its first super-block is kb0), `Ufull` = items of a whole row.
+// One warp, `nrw` (<= 4) consecutive rows in shared memory.  Q4_K: lanes stride over the rows' super-blocks, one whole
+// block per lane per round.  Q6_K: lanes stride over 32-byte items (4 per super-block); 32 and U are multiples of 4, so
+// a lane's sub-item never changes.  Each lane adds its terms into the accumulator of the row the item belongs to.
+// `rb_` = bytes between consecutive rows in shared memory, `U_` = 4 x the super-blocks per row held there (a chunk of
+// the row when the row is streamed in several tasks: its first super-block is kb0), `Ufull` = 4 x those of a whole row.
 template <int XM, int TYPE, bool DBG>
 __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, int U_, int kb0, int Ufull, int lane, const GvX& X,
                                              float (&acc)[4], int32_t* dbg) {
-    const unsigned rb = (unsigned)rb_, U = (unsigned)U_, total = (unsigned)nrw * U;
-    constexpr unsigned BB = TYPE == T_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    const unsigned rb = (unsigned)rb_;
+    if (TYPE == T_Q4K) {
+        const unsigned nbc = (unsigned)U_ >> 2, total = (unsigned)nrw * nbc;
+        for (unsigned base = 0; base < total; base += 32) {
+            const unsigned i = base + lane;
+            const bool valid = i < total;
+            const unsigned ii = valid ? i : 0u;
+            const unsigned rl = (ii >= nbc) + (ii >= 2 * nbc) + (ii >= 3 * nbc);
+            const unsigned blk = ii - rl * nbc;
+            int32_t* o = (DBG && dbg && valid) ? dbg + (size_t)rl * (2 * Ufull) + (kb0 + blk) * 8 : nullptr;
+            float term = q4k_block<XM>(rows + rl * rb + blk * Q4K_BYTES, kb0 + (int)blk, X, DBG ? o : nullptr);
+            if (!valid) term = 0.f;
+            acc[0] += rl == 0 ? term : 0.f; acc[1] += rl == 1 ? term : 0.f;
+            acc[2] += rl == 2 ? term : 0.f; acc[3] += rl == 3 ? term : 0.f;
+        }
+        return;
+    }
+    const unsigned U = (unsigned)U_, total = (unsigned)nrw * U;
     const int sub = lane & 3;
     for (unsigned base = 0; base < total; base += 32) {
         const unsigned i = base + lane;
@@ -359,19 +439,12 @@ __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, in
         const unsigned ii = valid ? i : (unsigned)sub;
         const unsigned rl = (ii >= U) + (ii >= 2 * U) + (ii >= 3 * U);
         const unsigned blk = (ii - rl * U) >> 2;
-        const uint32_t sb = rows + rl * rb + blk * BB;
-        float term;
-        if (TYPE == T_Q4K) {
-            int d0, d1;
-            term = q4k_item<XM>(sb, sub, kb0 + (int)blk, X, d0, d1);
-            if (DBG && dbg && valid) { int32_t* o = dbg + (size_t)rl * (2 * Ufull) + (kb0 + blk) * 8 + 2 * sub; o[0] = d0; o[1] = d1; }
-        } else {
-            int dots[4];
-            term = q6k_item<XM>(sb, sub >> 1, sub & 1, kb0 + (int)blk, X, dots);
-            if (DBG && dbg && valid) {
-                int32_t* o = dbg + (size_t)rl * (4 * Ufull) + (kb0 + blk) * 16 + 8 * (sub >> 1) + (sub & 1);
-                o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
-            }
+        const uint32_t sb = rows + rl * rb + blk * Q6K_BYTES;
+        int dots[4];
+        float term = q6k_item<XM>(sb, sub >> 1, sub & 1, kb0 + (int)blk, X, dots);
+        if (DBG && dbg && valid) {
+            int32_t* o = dbg + (size_t)rl * (4 * Ufull) + (kb0 + blk) * 16 + 8 * (sub >> 1) + (sub & 1);
+            o[0] = dots[0]; o[2] = dots[1]; o[4] = dots[2]; o[6] = dots[3];
         }
         if (!valid) term = 0.f;
         acc[0] += rl == 0 ? term : 0.f; acc[1] += rl == 1 ? term : 0.f;
@@ -468,7 +541,7 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
     if (warp >= p.nwarps) return;            // chain phases may use fewer warps than the CTA has (larger staging rings)
 
     const uint32_t sm0 = smem_u32(smem);
-    const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K };
+    const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K, p.K / QK_K };
     const uint32_t push_epoch = p.tp_push_on ? p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u : 0u;
     bool timed_out = false;
     float gate_keep[4] = { 0.f, 0.f, 0.f, 0.f };
@@ -483,6 +556,7 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
         if (!timed_out && !mbar_wait_bounded(&full[warp][slot], (par >> slot) & 1u)) timed_out = true;
         par ^= 1u << slot;
         if (DBG && p.trace && tid == 0 && u == 0) gv_stamp(p, 4);
+        if (DBG && p.trace && tid == 0 && u < 4) gv_stamp(p, 8 + 2 * u);          // warp 0: task u has landed
         const GvSegDev& s = p.seg[seg];
         uintptr_t g0, g1;
         gv_span(p, t, g0, g1);
@@ -497,9 +571,12 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
         }
         int32_t* dbg = (DBG && seg == 0 && p.dbg_dots) ? p.dbg_dots + (size_t)row0 * (s.type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
         const int Uc = p.nchunk > 1 ? 4 * (t.kb1 - t.kb0) : s.U, kb0 = p.nchunk > 1 ? t.kb0 : 0;
-        if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
-        else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
+        if (!(DBG && p.trace && p.trace_nocompute)) {
+            if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
+            else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
+        }
         __syncwarp();                            // the warp is done reading this slot
+        if (DBG && p.trace && tid == 0 && u < 4) gv_stamp(p, 9 + 2 * u);          // warp 0: task u has been multiplied
         if (lane == 0) {
             GvTask t2;
             if (gv_task(p, rg, warp, u + p.nslots, t2)) {
@@ -508,17 +585,31 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
             }
         }
         if (!t.last) continue;                   // more super-blocks of these rows follow in the next task
-        // row sums; lane r finishes row r
-        float mine = 0.f;
-        #pragma unroll
-        for (int r = 0; r < 4; ++r) { const float v = warp_sum(acc[r]); if (lane == r) mine = v; acc[r] = 0.f; }
+        // Row sums in six shuffles instead of twenty: the halves of the warp take over two rows each (xor 16), the quarters
+        // one row each (xor 8), then three steps inside the octet.  Every lane of octet r ends with the sum of row r; its
+        // first lane finishes the row.
+        float mine;
+        {
+            const bool hi16 = lane & 16, hi8 = lane & 8;
+            float k0 = hi16 ? acc[2] : acc[0], k1 = hi16 ? acc[3] : acc[1];
+            const float g0 = hi16 ? acc[0] : acc[2], g1 = hi16 ? acc[1] : acc[3];
+            k0 += __shfl_xor_sync(0xFFFFFFFFu, g0, 16);
+            k1 += __shfl_xor_sync(0xFFFFFFFFu, g1, 16);
+            float v = hi8 ? k1 : k0;
+            v += __shfl_xor_sync(0xFFFFFFFFu, hi8 ? k0 : k1, 8);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            mine = v;
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        }
+        const int rsel = lane >> 3;              // the row of this lane's octet
         if (p.out_mode == 3 && seg == 0) {       // gate values stay in registers until the matching up rows arrive
-            #pragma unroll
-            for (int r = 0; r < 4; ++r) gate_keep[r] = __shfl_sync(0xFFFFFFFFu, __half2float(__float2half_rn(mine)), r);
+            gate_keep[0] = __half2float(__float2half_rn(mine));      // octet r keeps the gate value of row r
             continue;
         }
-        if (lane < nrows) {
-            const int row = row0 + lane;
+        if ((lane & 7) == 0 && rsel < nrows) {
+            const int row = row0 + rsel;
             if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(mine);
             else if (p.out_mode == 1) reinterpret_cast<float*>(s.y)[row] = mine;
             else if (p.out_mode == 2) {   // src/kernels/gemv_q4.cu:996-999
@@ -538,7 +629,7 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
                 reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), res));
             } else {                      // fused SwiGLU of the gate/up pair (src/kernels/convert.cu:85-104)
                 const float hv = __half2float(__float2half_rn(mine));
-                const float g = lane == 0 ? gate_keep[0] : lane == 1 ? gate_keep[1] : lane == 2 ? gate_keep[2] : gate_keep[3];
+                const float g = gate_keep[0];
                 reinterpret_cast<__half*>(p.seg[0].y)[row] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), hv));
             }
             if (p.tp_push_on) {           // the value just stored, as a packet to every rank (this one included)
@@ -762,11 +853,12 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
     // minimise the longest chain of work any warp has to run: (row groups of its CTA / warps, rounded up) x
     // (32-lane rounds a group takes, plus half a round of per-group overhead).  Ties go to more warps, larger groups.
     const int U = nb * 4;
-    // CTAs of this launch: one per SM; two per SM when every SM has far more to stream than one CTA's rings hold
-    // (the logits product), where filling the machine matters more than leaving room for the next kernel.
-    long long all_bytes = 0;
-    for (int i = 0; i < a.nseg; ++i) all_bytes += (long long)a.seg[i].M * nb * block_bytes(a.seg[i].type);
-    const int ncta = (two_per_sm && all_bytes > (long long)cx->sm_count * 6 * budget) ? 2 * cx->sm_count : cx->sm_count;
+    // CTAs of this launch: two per SM (24 warps).  Leaving the second half of every SM to the NEXT kernel's CTAs, so that they
+    // set up and prefetch while this kernel computes (JLLM_B200_GEMV_CTAS=1), was measured: the next kernel then finds its
+    // first row groups in shared memory, but a launch is bound by the dot products of its own twelve warps per SM and by the
+    // activation staging, not by the wait for weights, and the whole decode step came out 2 % slower.
+    static const int ctas_env = [] { const char* v = getenv("JLLM_B200_GEMV_CTAS"); return v ? atoi(v) : 0; }();
+    const int ncta = (two_per_sm && ctas_env != 1) ? 2 * cx->sm_count : cx->sm_count;
     int rb_max = 0;
     for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
     uint32_t off = 0;
@@ -800,8 +892,11 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
             for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg); ++i) groups += (a.seg[i].M + R - 1) / R;
             const long long per_cta = (groups + ncta - 1) / ncta;
             const long long chain = (per_cta + nwarps - 1) / nwarps;
-            const int items = C > 1 ? cb * 4 : R * U;
-            const double cost = (double)chain * C * ((items + 31) / 32 + 0.5) * (a.out_mode == 3 ? 2 : 1);
+            // rounds of 32 lanes per task: Q4_K lanes take a whole super-block each (a round is four times as long), Q6_K lanes
+            // a quarter of one
+            const int blocks = C > 1 ? cb : R * nb;
+            const double rounds = a.seg[0].type == T_Q4K ? 4.0 * ((blocks + 31) / 32) : (double)((blocks * 4 + 31) / 32);
+            const double cost = (double)chain * C * (rounds + 0.5) * (a.out_mode == 3 ? 2 : 1);
             if (cost < best_cost - 1e-9) { best_cost = cost; best_w = nwarps; best_R = R; best_C = C; }
         }
     }
@@ -854,11 +949,13 @@ int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
     size_t smem_bytes = 0; int grid = 0; bool empty = false;
     // diagnostic switch: JLLM_B200_GEMV_WHOLE=1 gives every GEMV a whole SM per CTA, =0 half an SM; unset: the default policy
     static const int force = [] { const char* v = getenv("JLLM_B200_GEMV_WHOLE"); return v ? (v[0] == '1' ? 1 : 0) : -1; }();
-    const bool whole = force >= 0 ? force == 1 : false;
+    const bool whole = force == 1;
     const int rc = whole ? gv_configure(a, p, GV_CHAINWARPS, cx->max_smem_optin - 2048, false, smem_bytes, grid, empty)
                          : gv_configure(a, p, GV_MAXWARPS, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
     if (rc || empty) return rc;
     p.trace = g_trace; g_trace = nullptr;
+    static const bool nocompute = getenv("JLLM_B200_GEMV_NOCOMPUTE") != nullptr;
+    p.trace_nocompute = (p.trace && nocompute) ? 1 : 0;
     const bool dbg = a.dbg_dots || p.trace;
     void (*kern)(GvParams);
     if (whole) kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true, true> : gemv_stream_kernel<0, true, true>)

@@ -48,9 +48,10 @@ const void* resolve_weight(const void* W);          // device pointer of a weigh
 bool triple_dp4a(int t0, int t1, int t2);            // type mixes the reference runs on its q8_1 + dp4a path
 
 int launch_gemv(const GemvArgs& a, cudaStream_t st);
-// Diagnostic: the next launch_gemv on this thread records GV_NTRACE (8) %globaltimer stamps per CTA into t[cta * 8 + k]:
+// Diagnostic: the next launch_gemv on this thread records GV_NTRACE (16) %globaltimer stamps per CTA into t[cta * 16 + k]:
 // 0 kernel entry, 1 first bulk copies issued, 2 producer kernel complete (griddepcontrol.wait returned), 3 activation
-// vector staged, 4 first row group landed, 5 warp 0 done, 6 last warp done.
+// vector staged, 4 first row group landed, 5 warp 0 done, 6 last warp done, 8 + 2u / 9 + 2u: task u (< 4) of warp 0 has
+// landed / has been multiplied.
 void gemv_set_trace(unsigned long long* t);
 // n <= 4 GEMVs that feed one another, in one launch with grid-wide barriers between them; bar: two zeroed device words,
 // or null when every later phase takes all its inputs as packets (tensor-parallel): packets carry their own arrival mark

@@ -26,7 +26,7 @@ class ModelDesc(C.Structure):
 lib.jllm_b200_decoder_create.restype = C.c_void_p
 lib.jllm_b200_decoder_logits.restype = C.c_void_p
 
-FUSED, GRAPH = 1, 2
+FUSED, GRAPH, PREFILL = 1, 2, 16          # PREFILL: generate() runs the prompt through the batched prefill path
 
 
 class Decoder:
@@ -77,6 +77,16 @@ class Decoder:
 
     def reset(self):
         check(lib.jllm_b200_decoder_reset(C.c_void_p(self._h)))
+
+    def prefill(self, tokens, start_pos=0, stream=None, chunk=None):
+        """Batched prompt prefill (enqueue only); afterwards last_token() / step_device() continue the stream."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        if chunk:
+            check(lib.jllm_b200_decoder_set_prefill_chunk(C.c_void_p(self._h), C.c_int(chunk)))
+        check(lib.jllm_b200_decoder_prefill(C.c_void_p(self._h), t.ctypes.data_as(C.c_void_p), C.c_int(t.size), C.c_int(start_pos), _stream(stream)))
+
+    def last_token(self, stream=None):
+        return int(lib.jllm_b200_decoder_last_token(C.c_void_p(self._h), _stream(stream)))
 
     def logits(self):
         import torch

@@ -110,23 +110,27 @@ def measure(jb, argv):
         lens = [L] if B == 1 else [int(v) for v in np.random.Generator(np.random.PCG64(1002)).integers(256, 8193, B)]
         per = sum(2112 * l + 16384 for l in lens)
         copies = a.copies or max(2, int(np.ceil(3 * L2_BYTES / per)))
+        if B > 1:
+            copies = min(copies, 2)          # 64 caches of 8192 positions are 1 GB per copy
         scale = float(1 / np.sqrt(hd))
-        mk = lambda ts_: torch.tensor([t_.data_ptr() for t_ in ts_], dtype=torch.int64, device=dev)
+        Lmax = max(lens)
+        keep = []
         for _ in range(copies):
-            ks = [torch.randint(-127, 128, (l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
-            vs = [torch.randint(-127, 128, (l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
-            kss = [(torch.randn((l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
-            vss = [(torch.randn((l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
+            # every cache holds Lmax positions (a plan's tensor maps cover whole caches); a sequence uses its first L
+            ks = [torch.randint(-127, 128, (Lmax if B > 1 else l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
+            vs = [torch.randint(-127, 128, (Lmax if B > 1 else l, nkv, hd), dtype=torch.int8, device=dev, generator=gen) for l in lens]
+            kss = [(torch.randn((Lmax if B > 1 else l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
+            vss = [(torch.randn((Lmax if B > 1 else l, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float() for l in lens]
             q = torch.randn(B * nh * hd, device=dev, generator=gen).to(torch.float16)
             out = torch.zeros(B * nh * hd, dtype=torch.float16, device=dev)
             if B == 1:
                 calls.append(lambda q=q, out=out, k=ks[0], v=vs[0], s1=kss[0], s2=vss[0]:
                              jb.flash_attention_decode(out, q, k, v, nh, nkv, hd, hd, L, scale, True, s1, s2, 0, st))
             else:
-                lists = (mk(ks), mk(vs), mk(kss), mk(vss), torch.tensor(lens, dtype=torch.int32, device=dev))
-                keep = (ks, vs, kss, vss)
-                calls.append(lambda q=q, out=out, ls=lists, keep=keep:
-                             jb.flash_attention_decode_batched(out, q, ls[0], ls[1], ls[2], ls[3], ls[4], B, max(lens), nh, nkv, hd, scale, True, st))
+                plan = jb.AttnPlan(ks, vs, kss, vss, Lmax, nkv)
+                lens_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+                keep.append((plan, ks, vs, kss, vss))
+                calls.append(lambda q=q, out=out, plan=plan, lens_d=lens_d: plan.decode(out, q, lens_d, nh, scale, st))
         nbytes = per
         shape = dict(L=L, batch=B, copies=copies)
     trace = None
@@ -135,7 +139,7 @@ def measure(jb, argv):
         jb.lib.jllm_b200_init(C.c_int(-1))                     # the per-device context must exist before the capture starts
         calls[0]()
         torch.cuda.synchronize()
-        NCTA, NST = 2 * 148, 8
+        NCTA, NST = 2 * 148, 16
         trace = torch.zeros((a.iters, NCTA, NST), dtype=torch.int64, device=dev)
         plain = calls
         def traced(i):
@@ -175,9 +179,13 @@ def measure(jb, argv):
             base = prev[:, 6].max()                             # the previous launch's last warp finishes
             rows.append([cur[:, 0].min() - base, cur[:, 0].max() - base, cur[:, 1].max() - base, cur[:, 2].min() - base, cur[:, 2].max() - base,
                          cur[:, 3].max() - base, cur[:, 4].min() - base, cur[:, 4].max() - base, cur[:, 5].max() - base, cur[:, 6].max() - base])
+            for k in range(8, 16):                              # warp 0's tasks: median over CTAs
+                ok = cur[:, k] > 0
+                rows[-1].append(np.median(cur[ok, k]) - base if ok.any() else 0)
         r = np.median(np.array(rows, np.float64), axis=0) / 1e3
         names = ["entry_first", "entry_last", "copies_issued_last", "producer_done_first", "producer_done_last", "staged_last",
-                 "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done"]
+                 "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done",
+                 "t0_landed", "t0_done", "t1_landed", "t1_done", "t2_landed", "t2_done", "t3_landed", "t3_done"]
         print(json.dumps({"trace_us_after_previous_launch_finished(median)": {n: round(float(v), 2) for n, v in zip(names, r)},
                           "ctas": int((t[2][:, 0] > 0).sum())}))
     extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else {}

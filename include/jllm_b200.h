@@ -49,9 +49,10 @@ int         jllm_b200_device_status(void* stream);
 long long   jllm_b200_launch_count(void);        /* kernels launched by this library so far */
 void        jllm_b200_set_pdl(int on);           /* programmatic dependent launch on/off (default on) */
 
-/* Diagnostic: the NEXT GEMV-family call on this thread also records eight %globaltimer stamps (ns) per CTA into
- * device_buf[cta * 8 + k]: 0 kernel entry, 1 first bulk copies issued, 2 producer kernel complete, 3 activation vector
- * staged, 4 first row group landed, 5 warp 0 done, 6 last warp done.  device_buf needs 8 x 2 x SM-count entries. */
+/* Diagnostic: the NEXT GEMV-family call on this thread also records sixteen %globaltimer stamps (ns) per CTA into
+ * device_buf[cta * 16 + k]: 0 kernel entry, 1 first bulk copies issued, 2 producer kernel complete, 3 activation vector
+ * staged, 4 first row group landed, 5 warp 0 done, 6 last warp done, 8 + 2u / 9 + 2u task u (< 4) of warp 0 landed /
+ * multiplied.  device_buf needs 16 x 2 x SM-count entries. */
 void        jllm_b200_debug_gemv_trace(unsigned long long* device_buf);
 
 /* ── mapped-weight registry — include/jllm_kernels.h:40-43, src/engine/model.cpp:39-66 ── */
@@ -226,7 +227,10 @@ typedef struct {
     const jllm_b200_layer_desc* layers;                          /* host array of n_layers entries */
 } jllm_b200_model_desc;
 typedef struct jllm_b200_decoder jllm_b200_decoder;
-/* flags: bit 0 = fused kernels (norm+GEMV, SwiGLU epilogue, one QKV-prep launch) instead of the reference's
+/* flags: bit 4 = jllm_b200_decoder_generate prefills the prompt in one batched pass (jllm_b200_decoder_prefill) instead of
+ * one decode step per prompt token — the reference's default for prompts (its prefill arithmetic differs from the decode
+ * arithmetic in the activation quantiser, so the two give slightly different logits);
+ * bit 0 = fused kernels (norm+GEMV, SwiGLU epilogue, one QKV-prep launch) instead of the reference's
  * launch-for-launch sequence (both give identical bits); bit 1 = replay a captured CUDA graph per step;
  * bit 3 = with bit 0, run Wo / gate-up / W_down / next Q-K-V as ONE chained launch with grid-wide barriers instead of
  * four launches (same bits; measured slower on B200, where dependent launches overlap per SM, so it is off by default). */
@@ -238,6 +242,15 @@ int    jllm_b200_decoder_step(jllm_b200_decoder* d, int token, int position, voi
 /* Feeds `n_prompt` host tokens (one decode step each), then generates `n_new` tokens greedily; the
  * generated ids are copied to host_out.  Inputs and outputs cross the host/device boundary inside the call. */
 int    jllm_b200_decoder_generate(jllm_b200_decoder* d, const int* host_prompt, int n_prompt, int n_new, int* host_out, void* stream);
+/* Batched prompt prefill (stands where Engine::transformer_prefill sits, src/engine/decode.cu:1760-1884): n_tokens >= 2 host
+ * token ids at positions start_pos .. start_pos+n_tokens-1 go through every layer together — RMSNorm over rows, batched
+ * K-quant products, QK-norm + RoPE + INT8 KV store, query-tiled causal attention, SwiGLU FFN — in chunks of at most
+ * 2048 tokens (jllm_b200_decoder_set_prefill_chunk changes that); then the logits of the LAST token and its greedy token
+ * are computed on the device.  Afterwards the session stands at position start_pos + n_tokens with that token, so
+ * jllm_b200_decoder_step_device continues the stream and jllm_b200_decoder_last_token reads the token.  Enqueues only;
+ * not available in a tensor-parallel session. */
+int    jllm_b200_decoder_prefill(jllm_b200_decoder* d, const int* host_tokens, int n_tokens, int start_pos, void* stream);
+int    jllm_b200_decoder_set_prefill_chunk(jllm_b200_decoder* d, int tokens);
 /* One step with the host boundary inside: host_pos_token = {position, token} (pinned host memory recommended) is copied
  * to the device, the step runs, the greedy token is copied to *host_next and the call returns once it has arrived. */
 int    jllm_b200_decoder_step_sync(jllm_b200_decoder* d, const int* host_pos_token, int* host_next, void* stream);
@@ -263,7 +276,9 @@ const void* jllm_b200_decoder_buffer(jllm_b200_decoder* d, int which);
  * jllm_b200_tp_region_bytes() bytes.  All ranks must run the same steps in the same order; the greedy token is
  * reduced across ranks on the device, so every rank returns the same token.  jllm_b200_decoder_logits() gives the
  * rank's vocab_size/world slice.  Waits between ranks are bounded: a rank that never arrives shows up as
- * JLLM_B200_ERR_TIMEOUT in jllm_b200_device_status().  flags: bit 1 = CUDA graph as above. */
+ * JLLM_B200_ERR_TIMEOUT in jllm_b200_device_status().  Create clears this rank's own region (packets of an earlier session
+ * must not pass for fresh ones): let every rank return from create before any rank runs a step.  Weight types other than
+ * Q4_K / Q6_K are refused (JLLM_B200_ERR_TYPE).  flags: bit 1 = CUDA graph as above. */
 jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model, int flags, int rank, int world, void* const* regions);
 size_t jllm_b200_tp_region_bytes(int hidden_dim, int q_dim, int intermediate_dim);
 void*  jllm_b200_tp_alloc(size_t bytes);                    /* zeroed device memory for an exchange region */
@@ -288,8 +303,8 @@ int    jllm_b200_batch_decoder_kernels_per_step(jllm_b200_batch_decoder* d);
 
 /* ── allocation-free decode attention (no counterpart in the reference) ─────────────────────────
  * For hosts that cannot let the library allocate device memory: an engine whose own pools already hold
- * all of the GPU's free memory, a request loop that must avoid driver calls which can stall the device,
- * or a CUDA-graph recording in progress.  Same arguments and result as jllm_b200_flash_attention_decode;
+ * all of the GPU's free memory, or a request loop that must avoid driver calls which can stall the device.
+ * Same arguments and result as jllm_b200_flash_attention_decode;
  * the split-K partials live in a fixed array built into the library (JLLM_B200_NOALLOC_MAX_FLOATS floats
  * per GPU that loads the library, held until the process exits) instead of a buffer grown on demand.
  *   - n_heads * n_slices * (head_dim + 2) must not exceed JLLM_B200_NOALLOC_MAX_FLOATS (n_slices =

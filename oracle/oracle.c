@@ -710,6 +710,58 @@ int orc_decode_step(const orc_model* m, int token, int pos, float* logits) {
     return best;
 }
 
+/* Batched prompt prefill of n tokens at positions start..start+n-1, layer by layer, in the reference's order
+ * (Engine::transformer_prefill, src/engine/decode.cu:1760-1884): RMSNorm over rows, batched K-quant products
+ * (the prefill arithmetic: DS4/D4 activation quantiser, not the decode q8_1 one), per-head QK-norm, per-token RoPE
+ * and INT8 KV store, causal attention over all n queries, Wo, residual add (fp16), RMSNorm, gate/up, SwiGLU, W_down,
+ * residual add; then the final norm and fp32 logits of the LAST token (src/engine/decode.cu:2019-2050 computes the
+ * logits of the last prompt token only).  Returns the greedy token. */
+static void vec_add_h(const uint16_t* a, const uint16_t* b, int n, uint16_t* out) {      /* src/kernels/convert.cu vec_add: half(a + b) */
+    for (int i = 0; i < n; i++) out[i] = orc_f2h(orc_h2f(a[i]) + orc_h2f(b[i]));
+}
+int orc_prefill(const orc_model* m, const int* tokens, int n, int start, float* logits) {
+    const orc_model_cfg* c = &m->cfg;
+    const int H = c->hidden, QD = c->n_heads * c->head_dim, KVD = c->n_kv_heads * c->head_dim, I = c->ffn;
+    const size_t N = (size_t)n;
+    uint16_t *x = malloc(2 * N * H), *normed = malloc(2 * N * H), *x2 = malloc(2 * N * H), *y = malloc(2 * N * H);
+    uint16_t *qb = malloc(2 * N * QD), *kb = malloc(2 * N * KVD), *vb = malloc(2 * N * KVD), *att = malloc(2 * N * QD);
+    uint16_t *g = malloc(2 * N * I), *u = malloc(2 * N * I), *sw = malloc(2 * N * I);
+    for (int t = 0; t < n; t++) orc_dequant_embedding_row(m->tok_embd, m->t_embd, tokens[t], H, x + (size_t)t * H);
+    for (int l = 0; l < c->n_layers; l++) {
+        const orc_layer* w = &m->layers[l];
+        orc_rmsnorm(x, NULL, w->rms_attn, 1, n, H, c->eps, normed);
+        orc_entry_gemm_quant_batched(w->wq, w->t_wq, normed, QD, n, H, qb);
+        orc_entry_gemm_quant_batched(w->wk, w->t_wk, normed, KVD, n, H, kb);
+        orc_entry_gemm_quant_batched(w->wv, w->t_wv, normed, KVD, n, H, vb);
+        if (w->q_norm && w->k_norm) {
+            orc_rmsnorm(qb, NULL, w->q_norm, 1, n * c->n_heads, c->head_dim, c->eps, qb);
+            orc_rmsnorm(kb, NULL, w->k_norm, 1, n * c->n_kv_heads, c->head_dim, c->eps, kb);
+        }
+        for (int t = 0; t < n; t++) {
+            const int pos = start + t;
+            orc_rope(qb + (size_t)t * QD, kb + (size_t)t * KVD, c->n_heads, c->n_kv_heads, c->head_dim, pos, c->rope_theta, 1);
+            orc_fp16_to_int8(kb + (size_t)t * KVD, c->n_kv_heads, c->head_dim, kv_ptr(m, l, pos, 0), kvs_ptr(m, l, pos, 0));
+            orc_fp16_to_int8(vb + (size_t)t * KVD, c->n_kv_heads, c->head_dim, kv_ptr(m, l, pos, 1), kvs_ptr(m, l, pos, 1));
+        }
+        orc_attention_prefill(qb, kv_ptr(m, l, 0, 0), kv_ptr(m, l, 0, 1), c->n_heads, c->n_kv_heads, c->head_dim, c->head_dim, n, start,
+                              1.0f / sqrtf((float)c->head_dim), 1, kvs_ptr(m, l, 0, 0), kvs_ptr(m, l, 0, 1), 0, att);
+        orc_entry_gemm_quant_batched(w->wo, w->t_wo, att, H, n, QD, y);
+        vec_add_h(x, y, n * H, x2);
+        orc_rmsnorm(x2, NULL, w->rms_ffn, 1, n, H, c->eps, normed);
+        orc_entry_gemm_quant_batched(w->gate, w->t_gate, normed, I, n, H, g);
+        orc_entry_gemm_quant_batched(w->up, w->t_up, normed, I, n, H, u);
+        orc_swiglu(g, u, n * I, sw);
+        orc_entry_gemm_quant_batched(w->down, w->t_down, sw, H, n, I, y);
+        vec_add_h(x2, y, n * H, x);
+    }
+    orc_rmsnorm(x + (N - 1) * H, NULL, m->out_norm, 1, 1, H, c->eps, normed);
+    orc_entry_gemv_quant_f32(m->output, m->t_out, normed, c->vocab, H, logits);
+    int best = 0;
+    for (int i = 1; i < c->vocab; i++) if (logits[i] > logits[best]) best = i;
+    free(x); free(normed); free(x2); free(y); free(qb); free(kb); free(vb); free(att); free(g); free(u); free(sw);
+    return best;
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

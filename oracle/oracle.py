@@ -40,6 +40,7 @@ def lib() -> C.CDLL:
         _LIB.orc_f2h.restype = C.c_uint16
         _LIB.orc_f2h.argtypes = [C.c_float]
         _LIB.orc_decode_step.restype = C.c_int
+        _LIB.orc_prefill.restype = C.c_int
         _LIB.orc_dequant_embedding_row.restype = C.c_int
         _LIB.orc_num_threads.restype = C.c_int
     return _LIB
@@ -429,6 +430,23 @@ class Decoder:
 
     def step(self, token, pos):
         return int(lib().orc_decode_step(C.byref(self._m), C.c_int(int(token)), C.c_int(pos), _p(self.logits)))
+
+    def prefill(self, prompt, start=0):
+        """Batched prompt prefill (the reference's transformer_prefill order and prefill arithmetic); returns the greedy
+        token after the last prompt token and leaves its logits in self.logits."""
+        p = np.ascontiguousarray(prompt, np.int32)
+        return int(lib().orc_prefill(C.byref(self._m), _p(p), C.c_int(p.size), C.c_int(start), _p(self.logits)))
+
+    def generate_prefilled(self, prompt, n_new):
+        """Batched prefill of the prompt, then n_new greedy tokens by decode steps."""
+        tok, out = self.prefill(prompt), []
+        pos = len(prompt)
+        for i in range(n_new):
+            out.append(tok)
+            if i + 1 < n_new:
+                tok = self.step(tok, pos)
+                pos += 1
+        return out
 
     def generate(self, prompt, n_new):
         """Feed the prompt one token per step, then decode n_new tokens greedily."""

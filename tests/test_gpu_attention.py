@@ -100,3 +100,40 @@ def test_attention_argument_errors():
         jb.flash_attention_decode(out, out, out, out, 3, 2, 64, 64, 4, 1.0, False, None, None, 0)     # heads not a multiple of kv heads
     with pytest.raises(jb.JllmError):
         jb.flash_attention_decode(out, out, None, out, 2, 2, 64, 64, 4, 1.0, False, None, None, 0)    # null cache
+
+
+@pytest.mark.parametrize("N,start,nh,nkv", [(1, 0, 32, 8), (5, 0, 32, 8), (33, 0, 32, 8), (64, 17, 32, 8), (130, 300, 32, 8), (37, 5, 16, 8), (9, 2, 8, 8)])
+def test_prefill_int8_query_tiled(N, start, nh, nkv):
+    """Causal prefill over an INT8 cache with 128-wide heads (the query-tiled tensor-core kernel): token t at position
+    start + t attends keys [0, start + t]; ragged token counts, non-zero start, GQA groups of 4, 2 and 1."""
+    import torch
+    jb = pkg()
+    hd = 128
+    rng = np.random.Generator(np.random.PCG64(5000 + N + start + nh))
+    L = start + N
+    scale = float(1 / np.sqrt(hd))
+    q = orc.gen_act(rng, N * nh * hd)
+    k, ks = orc.gen_kv(rng, L, nkv, hd); v, vs = orc.gen_kv(rng, L, nkv, hd)
+    out = torch.full((N * nh * hd + 64,), 7.0, dtype=torch.float16, device="cuda")
+    jb.flash_attention_prefill_batched(out, dev(q), dev(k), dev(v), nh, nkv, hd, hd, N, start, scale, True, dev(ks), dev(vs), 0)
+    got = out.float().cpu().numpy()
+    assert np.all(got[N * nh * hd:] == 7.0), "wrote past the output"
+    _check(got[:N * nh * hd], orc.attention_prefill(q, k, v, nh, nkv, hd, N, start, scale, True, ks, vs).reshape(N * nh, hd))
+    assert jb.device_status() == 0
+
+
+@pytest.mark.parametrize("N", [33, 512])
+def test_prefill_int8_matches_reference_gpu_record(N):
+    """The same kernel against what the reference's own prefill attention returned on a B200 (tests/golden/ref_gpu.npz)."""
+    import os
+    import torch
+    from golden import gpu_cases as gc
+    jb = pkg()
+    ref = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_gpu.npz"))
+    c = gc.attention_prefill(N)
+    out = torch.zeros(N * gc.NH * gc.HD, dtype=torch.float16, device="cuda")
+    jb.flash_attention_prefill_batched(out, dev(c["q"]), dev(c["k"]), dev(c["v"]), gc.NH, gc.NKV, gc.HD, gc.HD, N, 0, gc.SCALE, True, dev(c["ks"]), dev(c["vs"]), 0)
+    sel = gc.prefill_sample(N)
+    got = out.float().cpu().numpy().reshape(N, gc.NH, gc.HD)[sel].reshape(-1, gc.HD)
+    want = ref[f"prefill_attn_N{N}_out"].view(np.float16).astype(np.float32).reshape(-1, gc.HD)
+    _check(got, want)

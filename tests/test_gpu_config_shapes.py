@@ -15,7 +15,7 @@ import pytest
 
 from oracle import oracle as orc
 from golden import gpu_cases as gc
-from gpu_util import pkg, dev, close, close_gemm
+from gpu_util import pkg, dev, close, close_gemm, ulp16
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_gpu.npz")
@@ -72,7 +72,7 @@ def test_batch8_q6k_config_1(ref):
     got = y.float().cpu().numpy()
     for name, want in (("oracle", orc.entry_gemm_quant_batched(c["W"], 14, c["X8"], c["M"], 8, c["K"]).astype(np.float32)),
                        ("reference GPU record", f16(ref["gemm_q6k_b8_y"]))):
-        ok, msg = close_gemm(got, want, 8, c["M"])
+        ok, msg = close_gemm(got, want, 8, c["M"], flips=0.0 if name == "oracle" else 1e-4)
         assert ok, f"batch 8 against the {name}: {msg}"
 
 
@@ -117,7 +117,7 @@ def test_logits_slice_f32(ref):
 
 def _attn_check(got, want, what):
     got = np.asarray(got, np.float32).reshape(want.shape)
-    tol = 1e-3 * np.abs(want) + 2e-3 * np.abs(want).max(axis=-1, keepdims=True) + 1e-6
+    tol = 1e-3 * np.abs(want) + 2e-3 * np.abs(want).max(axis=-1, keepdims=True) + ulp16(want)      # + one fp16 ULP of the output
     assert np.all(np.abs(got - want) <= tol), f"{what}: max diff {float(np.abs(got - want).max())}"
 
 
@@ -182,7 +182,7 @@ def test_prefill_gemm_config_3(ref, t, N):
     Xs = np.ascontiguousarray(c["X"][sel])
     want = orc.entry_gemm_quant_batched(c["W"], t, Xs, c["M"], len(sel), c["K"]).astype(np.float32)
     for name, w in (("oracle", want), ("reference GPU record", f16(ref[f"gemm_t{t}_N{N}_y"]))):
-        ok, msg = close_gemm(got, w, len(sel), c["M"])
+        ok, msg = close_gemm(got, w, len(sel), c["M"], flips=0.0 if name == "oracle" else 1e-4)
         assert ok, f"M={c['M']} K={c['K']} N={N} against the {name}: {msg}"
     # every token row, not only the sampled ones, must be finite and of the sampled rows' magnitude
     rms_all = y.float().pow(2).mean(dim=1).sqrt().cpu().numpy()

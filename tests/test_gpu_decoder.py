@@ -91,6 +91,46 @@ def test_logits_match_oracle_and_fused_equals_unfused(small_model):
     a.close(); b.close(); c.close()
 
 
+def test_batched_prefill_matches_oracle_prefill(small_model):
+    """generate() with the batched-prefill flag: the prompt goes through the batched kernels in one pass (the reference's
+    transformer_prefill order and prefill arithmetic), then decode steps; compared with the oracle doing the same.  Also
+    in chunks (4 + 3 + 2 tokens: never a chunk of one), which must give the same stream."""
+    jb = pkg()
+    m, w = small_model
+    rng = np.random.Generator(np.random.PCG64(1004))
+    prompt = rng.integers(0, SMALL["vocab"], 9)
+    n_new, ctx = 16, 64
+    od = orc.Decoder(m, ctx)
+    want = od.generate_prefilled(prompt, n_new)
+    assert np.all(np.isfinite(od.logits)) and len(set(want)) > 1
+    d = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED | jb.decoder.GRAPH | jb.decoder.PREFILL)
+    got = list(d.generate(prompt, n_new))
+    got2 = list(d.generate(prompt, n_new))                  # again through the same session
+    assert jb.device_status() == 0
+    # the explicit entry point, in chunks
+    import torch
+    st = torch.cuda.Stream()
+    d.reset()
+    d.prefill(prompt, 0, st, chunk=4)
+    chunked = [d.last_token(st)]
+    for _ in range(n_new - 1):
+        d.step_device(st)
+        chunked.append(d.last_token(st))
+    d.close()
+    assert got == got2 == chunked, (got, got2, chunked)
+    if got != want:
+        s = next(i for i in range(n_new) if got[i] != want[i])
+        od2 = orc.Decoder(m, ctx)
+        tok = od2.prefill(prompt)
+        for i in range(s):
+            tok = od2.step(want[i], len(prompt) + i)
+        lg = od2.logits
+        rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
+        margin = float(lg[want[s]] - lg[got[s]])
+        print(f"prefilled stream parts at step {s}: oracle margin {margin:.4f} (logit RMS {rms:.3f})")
+        assert 0 <= margin <= NOISE * rms, (s, margin, rms)
+
+
 def test_decoder_argument_errors(small_model):
     jb = pkg()
     m, w = small_model
@@ -131,4 +171,23 @@ def test_full_shape_greedy_stream_config_4():
         rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
         margin = float(lg[want[s]] - lg[got[s]])
         print(f"stream parts at step {s}: oracle margin {margin:.4f} (logit RMS {rms:.3f})")
+        assert 0 <= margin <= NOISE * rms, (s, margin, rms)
+    # the same prompt through the batched prefill path, against the oracle's batched prefill
+    od3 = orc.Decoder(m, ctx)
+    want_p = od3.generate_prefilled(prompt, 8)
+    d = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED | jb.decoder.GRAPH | jb.decoder.PREFILL)
+    got_p = list(d.generate(prompt, 8))
+    d.close()
+    assert jb.device_status() == 0
+    print("oracle prefilled stream", want_p, "\nGPU prefilled stream   ", got_p)
+    if got_p != want_p:
+        s = next(i for i in range(8) if got_p[i] != want_p[i])
+        od4 = orc.Decoder(m, ctx)
+        od4.prefill(prompt)
+        for i in range(s):
+            od4.step(want_p[i], len(prompt) + i)
+        lg = od4.logits
+        rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
+        margin = float(lg[want_p[s]] - lg[got_p[s]])
+        print(f"prefilled stream parts at step {s}: oracle margin {margin:.4f} (logit RMS {rms:.3f})")
         assert 0 <= margin <= NOISE * rms, (s, margin, rms)
