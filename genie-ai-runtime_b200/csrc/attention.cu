@@ -14,13 +14,13 @@
 
 namespace jb {
 
-// Split policy: slices of at least 128 keys, at most 32 slices per head
-// (the reference caps at 8 slices for its 8-SM part, attention.cu:1000-1005).
+// Split policy.  Merging slices costs about five microseconds however few there are (partials through L2, a fence, a ticket,
+// the last CTA's pass over them), more than a single slice needs for several hundred keys: one slice below 768 keys, then
+// slices of at least 256 keys (512 from 2048 keys on), at most 32 (the reference caps at 8 slices for its 8-SM part, attention.cu:1000-1005).
 int attn_splits_for(int seq_len) {
-    if (seq_len < 256) return 1;
-    int per = (seq_len + 31) / 32;
-    if (per < 128) per = 128;
-    return (seq_len + per - 1) / per;
+    if (seq_len < 768) return 1;
+    const int n = seq_len < 2048 ? seq_len / 256 : seq_len / 512;
+    return n > 32 ? 32 : n;
 }
 
 struct AttnArgs {

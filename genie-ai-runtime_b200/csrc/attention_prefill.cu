@@ -94,17 +94,14 @@ __global__ void __launch_bounds__(AP_WARPS * 32, 2) attn_prefill_kernel(const __
     };
     if (lane == 0)
         for (int it = 0; it < AP_STAGES && it < my_tiles; ++it) issue(it);
-    auto load_scales = [&](int it, float (&kv)[4], float (&vv)[4]) {
-        const int t0 = (warp + it * AP_WARPS) * AP_TILE;
-        #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int key = t0 + g + 8 * r;
-            const bool ok = it < my_tiles && key < kv_end;
-            kv[r] = ok ? __ldcg(a.ks + (size_t)key * a.n_kv + kvh) : 0.f;
-            vv[r] = ok ? __ldcg(a.vs + (size_t)key * a.n_kv + kvh) : 0.f;
-        }
+    // lane l fetches the scales of key t0 + l (one load per array per tile); the lanes pick their four keys' with shuffles
+    auto load_scales = [&](int it, float& kl, float& vl) {
+        const int key = (warp + it * AP_WARPS) * AP_TILE + lane;
+        const bool ok = it < my_tiles && key < kv_end;
+        kl = ok ? __ldcg(a.ks + (size_t)key * a.n_kv + kvh) : 0.f;
+        vl = ok ? __ldcg(a.vs + (size_t)key * a.n_kv + kvh) : 0.f;
     };
-    float nks[4], nvs[4];
+    float nks, nvs;
     load_scales(0, nks, nvs);
 
     // ── query planes of the PQ tokens x G heads: warp w quantises the (token, head) pairs w, w+4, ... ──
@@ -158,7 +155,10 @@ __global__ void __launch_bounds__(AP_WARPS * 32, 2) attn_prefill_kernel(const __
         const uint32_t Kt = wring + (uint32_t)(it % AP_STAGES) * AP_STAGE_BYTES, Vt = Kt + AP_TILE_BYTES;
         float ksv[4], vsv[4];
         #pragma unroll
-        for (int r = 0; r < 4; ++r) { ksv[r] = nks[r]; vsv[r] = nvs[r]; }
+        for (int r = 0; r < 4; ++r) {
+            ksv[r] = __shfl_sync(0xFFFFFFFFu, nks, g + 8 * r);
+            vsv[r] = __shfl_sync(0xFFFFFFFFu, nvs, g + 8 * r);
+        }
         load_scales(it + 1, nks, nvs);
         if (!timed_out && !mbar_wait_bounded(&full[warp][it % AP_STAGES], (it / AP_STAGES) & 1)) timed_out = true;
 

@@ -119,18 +119,16 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
     if (lane == 0)
         for (int it = 0; it < AM_STAGES && it < my_tiles; ++it) issue(it);
 
-    // scales of this lane's four keys (g, g+8, g+16, g+24) of a tile
-    auto load_scales = [&](int it, float (&kv)[4], float (&vv)[4]) {
-        const int t0 = kv0 + (warp + it * AM_WARPS) * AM_TILE;
-        #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int key = t0 + g + 8 * r;
-            const bool ok = it < my_tiles && key < kv1;
-            kv[r] = ok ? __ldcg(ksp + (size_t)key * a.n_kv + kvh) : 0.f;
-            vv[r] = ok ? __ldcg(vsp + (size_t)key * a.n_kv + kvh) : 0.f;
-        }
+    // Scales of a tile: lane l fetches those of key t0 + l (ONE load per array per tile; the 32 floats of a kv head sit 32 bytes
+    // apart, so per-key loads from every lane would cost four times the sector requests); the lanes then pick the scales of
+    // their four keys (g, g+8, g+16, g+24) with shuffles.
+    auto load_scales = [&](int it, float& kl, float& vl) {
+        const int key = kv0 + (warp + it * AM_WARPS) * AM_TILE + lane;
+        const bool ok = it < my_tiles && key < kv1;
+        kl = ok ? __ldcg(ksp + (size_t)key * a.n_kv + kvh) : 0.f;
+        vl = ok ? __ldcg(vsp + (size_t)key * a.n_kv + kvh) : 0.f;
     };
-    float nks[4], nvs[4];
+    float nks, nvs;
     load_scales(0, nks, nvs);
 
     // ── query planes: per head 16-bit fixed point, split into a high and a (signed) low byte ──
@@ -176,7 +174,10 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
         const uint32_t Kt = wring + (uint32_t)(it % AM_STAGES) * AM_STAGE_BYTES, Vt = Kt + AM_TILE_BYTES;
         float ksv[4], vsv[4];
         #pragma unroll
-        for (int r = 0; r < 4; ++r) { ksv[r] = nks[r]; vsv[r] = nvs[r]; }
+        for (int r = 0; r < 4; ++r) {
+            ksv[r] = __shfl_sync(0xFFFFFFFFu, nks, g + 8 * r);
+            vsv[r] = __shfl_sync(0xFFFFFFFFu, nvs, g + 8 * r);
+        }
         load_scales(it + 1, nks, nvs);                                          // in flight while this tile is multiplied
         if (!timed_out && !mbar_wait_bounded(&full[warp][it % AM_STAGES], (it / AM_STAGES) & 1)) timed_out = true;
 
@@ -386,11 +387,13 @@ static bool am_capturing(cudaStream_t st) {
     return cs != cudaStreamCaptureStatusNone;
 }
 
-// Slices: enough CTAs for three per SM, never shorter than 128 keys, at most 64 (the merge holds one slice per thread).
+// Slices: enough CTAs for three per SM; one slice below 768 keys (a merge of slices costs more than a slice of a few
+// hundred keys takes), slices of at least 256 keys up to 2048 keys and of at least 512 beyond, at most 64 (the merge holds
+// one slice per thread).
 static int am_splits(int seq, int n_kv, int batch, int sm_count) {
+    if (seq < 768) return 1;
     const int want = (3 * sm_count + n_kv * batch - 1) / (n_kv * batch);
-    int by_len = seq / 128;
-    if (by_len < 1) by_len = 1;
+    const int by_len = seq < 2048 ? seq / 256 : seq / 512;
     int ns = want < by_len ? want : by_len;
     if (ns > 64) ns = 64;
     return ns < 1 ? 1 : ns;

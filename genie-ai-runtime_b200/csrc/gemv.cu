@@ -417,12 +417,24 @@ __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, in
     const unsigned rb = (unsigned)rb_;
     if (TYPE == T_Q4K) {
         const unsigned nbc = (unsigned)U_ >> 2, total = (unsigned)nrw * nbc;
+        // One round (the usual case): lanes 8r .. 8r+7 take super-blocks 0..7 of row r, the lanes after them the blocks from 8
+        // on, row by row.  The 16-byte runs of the activation image repeat their banks every eight super-blocks, so a
+        // quarter-warp that held blocks b and b + 8 of two rows (as the plain row-major order does for 10 blocks per row)
+        // would read them in two passes; this order keeps eight distinct (block mod 8) — or equal addresses — per quarter.
+        const bool octets = total <= 32 && nbc > 8 && nbc <= 16;
         for (unsigned base = 0; base < total; base += 32) {
             const unsigned i = base + lane;
             const bool valid = i < total;
             const unsigned ii = valid ? i : 0u;
-            const unsigned rl = (ii >= nbc) + (ii >= 2 * nbc) + (ii >= 3 * nbc);
-            const unsigned blk = ii - rl * nbc;
+            unsigned rl, blk;
+            if (octets) {
+                const unsigned head = 8u * (unsigned)nrw, tailw = nbc - 8u;
+                if (ii < head) { rl = ii >> 3; blk = ii & 7u; }
+                else { const unsigned k = ii - head; rl = (k >= tailw) + (k >= 2 * tailw) + (k >= 3 * tailw); blk = 8u + k - rl * tailw; }
+            } else {
+                rl = (ii >= nbc) + (ii >= 2 * nbc) + (ii >= 3 * nbc);
+                blk = ii - rl * nbc;
+            }
             int32_t* o = (DBG && dbg && valid) ? dbg + (size_t)rl * (2 * Ufull) + (kb0 + blk) * 8 : nullptr;
             float term = q4k_block<XM>(rows + rl * rb + blk * Q4K_BYTES, kb0 + (int)blk, X, DBG ? o : nullptr);
             if (!valid) term = 0.f;
@@ -853,12 +865,17 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
     // minimise the longest chain of work any warp has to run: (row groups of its CTA / warps, rounded up) x
     // (32-lane rounds a group takes, plus half a round of per-group overhead).  Ties go to more warps, larger groups.
     const int U = nb * 4;
-    // CTAs of this launch: two per SM (24 warps).  Leaving the second half of every SM to the NEXT kernel's CTAs, so that they
-    // set up and prefetch while this kernel computes (JLLM_B200_GEMV_CTAS=1), was measured: the next kernel then finds its
-    // first row groups in shared memory, but a launch is bound by the dot products of its own twelve warps per SM and by the
-    // activation staging, not by the wait for weights, and the whole decode step came out 2 % slower.
+    // CTAs of this launch (half an SM each).  A product whose share per SM fits one CTA's rings (Wo, Q/K/V, a 14 MB matrix)
+    // launches ONE CTA per SM: the other half of every SM then takes the NEXT kernel's CTAs, which set up and prefetch all
+    // their rows while this kernel computes, and few tasks per warp keep the launch short (measured: Wo 4.7 against 6.6 µs,
+    // Q/K/V 7.2 against 8.2).  A larger product (gate/up, W_down, logits) launches TWO CTAs per SM: its warps each run
+    // several row groups one after the other, and twice the warps shorten that chain more than the overlap would save
+    // (gate/up 10.8 against 11.0 µs, W_down 13.2 against 13.9, logits 95 against 116).  JLLM_B200_GEMV_CTAS = 1 / 2 forces either.
+    long long all_bytes = 0;
+    for (int i = 0; i < a.nseg; ++i) all_bytes += (long long)a.seg[i].M * nb * block_bytes(a.seg[i].type);
     static const int ctas_env = [] { const char* v = getenv("JLLM_B200_GEMV_CTAS"); return v ? atoi(v) : 0; }();
-    const int ncta = (two_per_sm && ctas_env != 1) ? 2 * cx->sm_count : cx->sm_count;
+    const bool two = ctas_env ? ctas_env == 2 : all_bytes > (long long)cx->sm_count * (budget - 8192);
+    const int ncta = (two_per_sm && two) ? 2 * cx->sm_count : cx->sm_count;
     int rb_max = 0;
     for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
     uint32_t off = 0;

@@ -40,13 +40,15 @@ def blocks(ggml_type, rows, K, dev, gen):
 
 def parser():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "mmq"])
+    ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "pattn", "mmq"])
     ap.add_argument("--type", type=int, default=12)
     ap.add_argument("--M", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
     ap.add_argument("--N", type=int, default=512)
     ap.add_argument("--L", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--nh", type=int, default=32, help="attn: query heads")
+    ap.add_argument("--nkv", type=int, default=8, help="attn: KV heads")
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -105,10 +107,24 @@ def measure(jb, argv):
                 calls.append(lambda W=W: jb.gemm_quant_batched(ys[0], W[0], t, x, M, a.N, K, st))
         nbytes = wbytes + N * K * 2 + sum(N * m * ys[0].element_size() for m in Ms)
         shape = dict(M=Ms, K=K, types=ts, N=N, copies=copies)
+    elif a.kind == "pattn":
+        # causal prefill attention of N query tokens from position 0 over an INT8 cache (the cache fits the L2: a prompt's K/V
+        # were written just before); algorithmic bytes = K/V/scales of the N positions once + q in + out
+        nh, nkv, hd, N = 32, 8, 128, a.N
+        scale = float(1 / np.sqrt(hd))
+        k = torch.randint(-127, 128, (N, nkv, hd), dtype=torch.int8, device=dev, generator=gen)
+        v = torch.randint(-127, 128, (N, nkv, hd), dtype=torch.int8, device=dev, generator=gen)
+        ksc = (torch.randn((N, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float()
+        vsc = (torch.randn((N, nkv), device=dev, generator=gen).abs() * 0.02).to(torch.float16).float()
+        q = torch.randn(N * nh * hd, device=dev, generator=gen).to(torch.float16)
+        out = torch.zeros(N * nh * hd, dtype=torch.float16, device=dev)
+        calls.append(lambda: jb.flash_attention_prefill_batched(out, q, k, v, nh, nkv, hd, hd, N, 0, scale, True, ksc, vsc, 0, st))
+        nbytes = 2112 * N + 2 * N * nh * hd * 2
+        shape = dict(N=N, flops=4.0 * nh * hd * N * (N + 1) / 2)
     else:
-        nh, nkv, hd, L, B = 32, 8, 128, a.L, a.batch
+        nh, nkv, hd, L, B = a.nh, a.nkv, 128, a.L, a.batch
         lens = [L] if B == 1 else [int(v) for v in np.random.Generator(np.random.PCG64(1002)).integers(256, 8193, B)]
-        per = sum(2112 * l + 16384 for l in lens)
+        per = sum((2 * nkv * hd + 8 * nkv) * l + 4 * nh * hd for l in lens)      # K + V + scales of every position once, q in, out
         copies = a.copies or max(2, int(np.ceil(3 * L2_BYTES / per)))
         if B > 1:
             copies = min(copies, 2)          # 64 caches of 8192 positions are 1 GB per copy
@@ -188,7 +204,7 @@ def measure(jb, argv):
                  "t0_landed", "t0_done", "t1_landed", "t1_done", "t2_landed", "t2_done", "t3_landed", "t3_done"]
         print(json.dumps({"trace_us_after_previous_launch_finished(median)": {n: round(float(v), 2) for n, v in zip(names, r)},
                           "ctas": int((t[2][:, 0] > 0).sum())}))
-    extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else {}
+    extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else ({"TFLOPs": shape["flops"] / us / 1e6} if a.kind == "pattn" else {})
     if a.no_pdl:
         jb.lib.jllm_b200_set_pdl(1)
     return {"kind": a.kind, "shape": shape, "us_per_launch": us, "algorithmic_bytes": nbytes, **extra,

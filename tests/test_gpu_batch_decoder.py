@@ -50,14 +50,15 @@ def oracle_batch(model, prompts, n_new, ctx):
         normed = orc.rmsnorm(X.reshape(-1), None, model["out_norm"], B, H, c["eps"])
         return gemm(model["output"], normed, V, H).astype(np.float32)
 
-    out, logits, toks = [], None, None
+    out, logits, toks, all_logits = [], None, None, []
     for pos in range(P + n_new - 1):
         cur = prompts[:, pos] if pos < P else toks
         logits = step(cur, pos)
         toks = np.argmax(logits, axis=1).astype(np.int32)
         if pos >= P - 1:
             out.append(toks.copy())
-    return np.stack(out), logits
+            all_logits.append(logits.copy())
+    return np.stack(out), logits, all_logits
 
 
 def test_batch_streams_follow_the_oracle():
@@ -68,7 +69,7 @@ def test_batch_streams_follow_the_oracle():
     rng = np.random.Generator(np.random.PCG64(1010))
     B, P, n_new, ctx = 3, 4, 4, 32
     prompts = rng.integers(0, SMALL["vocab"], (B, P)).astype(np.int32)
-    want, want_logits = oracle_batch(m, prompts, n_new, ctx)
+    want, want_logits, step_logits = oracle_batch(m, prompts, n_new, ctx)
     d = jb.decoder.BatchDecoder(m["cfg"], w, ctx, B)
     st = torch.cuda.Stream()
     got = d.generate(prompts, n_new, st)
@@ -83,9 +84,14 @@ def test_batch_streams_follow_the_oracle():
         print("logit error: max %.4f, rms %.4f, logit rms %.4f" % (float(err.max()), float(np.sqrt(np.mean(err ** 2))), rms))
         assert float(np.sqrt(np.mean(err ** 2))) <= ERR_RMS * rms and float(err.max()) <= ERR_MAX * rms
     else:                                                  # a stream may part from the oracle only at a near tie of its two top logits
-        first = np.argwhere(got != want)[0]
-        print("streams part at step", first)
-        assert first[0] >= 1, "the first generated token must agree"
+        # up to the first parting step every stream fed both decoders the same tokens, so the oracle's logits of that step are
+        # the ones to judge the margin by: the oracle's own choice must lead the GPU's by no more than the logit error bound
+        s0 = int(np.argwhere(got != want)[0][0])
+        for b in np.argwhere(got[s0] != want[s0]).reshape(-1):
+            lg0 = step_logits[s0][b]
+            margin = float(lg0[want[s0][b]] - lg0[got[s0][b]])
+            print("stream %d parts at step %d: oracle margin %.4f (logit RMS %.3f)" % (b, s0, margin, rms))
+            assert 0 <= margin <= ERR_MAX * rms, (int(b), s0, margin, rms)
     d.close()
 
 
@@ -100,4 +106,27 @@ def test_batch_decoder_argument_errors():
         d.generate(np.zeros((2, 10), np.int32), 10)        # 20 tokens do not fit a context of 16
     with pytest.raises(jb.JllmError):
         d.generate(np.full((2, 3), 5000, np.int32), 2)     # token outside the vocabulary
+    d.close()
+
+
+def test_batch_decoder_step_device_is_bounded_by_the_context():
+    """step_device keeps a host mirror of the device-side position: before generate it is an error (code 8), and a step that
+    would write K/V rows past the per-stream pools returns code 6 without launching anything."""
+    import torch
+    jb = pkg()
+    m = orc.gen_model(79, **SMALL)
+    w = jb.decoder.upload(m)
+    d = jb.decoder.BatchDecoder(m["cfg"], w, 8, 2)
+    st = torch.cuda.Stream()
+    with pytest.raises(jb.JllmError) as e:
+        d.step_device(st)
+    assert e.value.code == 8
+    d.generate(np.zeros((2, 3), np.int32), 2, st)          # positions 0..3 used: the session stands at position 4
+    for _ in range(4):
+        d.step_device(st)                                   # positions 4..7
+    n0 = jb.launch_count()
+    with pytest.raises(jb.JllmError) as e:
+        d.step_device(st)                                   # position 8 does not exist
+    assert e.value.code == 6 and jb.launch_count() == n0
+    assert jb.device_status(st) == 0
     d.close()
