@@ -30,9 +30,8 @@ namespace jb {
 // one CTA on every SM.  The other half is where the CTAs of the NEXT kernel in the stream become resident as soon as
 // this one has issued griddepcontrol.launch_dependents: they set up their barriers and start the bulk copies of their
 // first row groups while this kernel is still computing, so HBM keeps streaming across kernel boundaries.
-constexpr int GV_MAXWARPS = 12;
-constexpr int GV_MAXTHREADS = GV_MAXWARPS * 32;
-constexpr int GV_CHAINWARPS = 20;              // the chain kernel keeps a whole SM per CTA (its phases overlap inside one launch)
+constexpr int GV_MAXWARPS = 8;                 // 8 warps at 128 registers (rows-deep columns keep many values live)
+constexpr int GV_CHAINWARPS = 16;              // the chain kernel keeps a whole SM per CTA (its phases overlap inside one launch)
 constexpr int GV_CHAINTHREADS = GV_CHAINWARPS * 32;
 constexpr int GV_MAXSLOT = 8;
 constexpr int GV_NTRACE = 16;                  // time stamps per CTA of a traced launch
@@ -41,8 +40,10 @@ struct GvSegDev {
     const uint8_t* W; void* y; int M; int type;
     int rb;          // row bytes
     int U;           // work items per row: 4 per super-block for both types
-    int R;           // rows per warp pass ("row group")
-    int trc;         // rows per chunk = warps * R
+    int R;           // rows per task ("row group")
+    // Q4_K lane map of a task: the warp is cut into `lg` groups of `lw` lanes; lane c of group g owns super-block column
+    // c (and c + lw, ... when a row has more than lw blocks) of the `rl` rows g*rl .. g*rl + rl - 1, so R = lg * rl.
+    uint8_t lw, lg, rl, pad_;
 };
 struct GvParams {
     GvSegDev seg[3]; int nseg;
@@ -54,9 +55,12 @@ struct GvParams {
     unsigned long long* trace;  // diagnostic launches only: GV_NTRACE time stamps per CTA
     int trace_nocompute;        // diagnostic: stream the weights but skip the dot products
     int slot_bytes, nslots, needA, needB, paired_rows, nwarps;
+    int early_slots;            // slots of every ring whose copies are issued before the wait for the producer kernel
     int nchunk, chunk_blocks;   // a row group is streamed as nchunk tasks of chunk_blocks super-blocks per row (nchunk > 1 only with R = 1)
     uint32_t off_xA, off_xB, off_xd, off_xs, off_xsum, off_gate, off_slots;
     long long total_bytes;      // Σ over segments of (row groups x bytes per group)
+    uint32_t gw[3], ng[3];      // per matrix: weight of a row group in the split over CTAs, number of groups
+    uint32_t split_q, split_r;  // Σ gw*ng / grid and % grid
     int tp_wait_on, tp_push_on;
     int xmode;                  // 0 q8_1 activations, 1 16-bit activations
     int chained;                // phase of a chain kernel: activations may have been written by other SMs in this launch
@@ -77,10 +81,11 @@ void gemv_set_tp_hooks(const GemvTpWait* w, const GemvTpPush* q) {
 // ── activation staging ───────────────────────────────────────────────────
 // Eight consecutive activations as floats: a 16-byte load of the plain fp16 vector, or, for a vector that arrives from
 // the other ranks, 64 bytes of packets polled (bounded) until every epoch word matches; the packets are read past L1.
+template <bool TP>
 __device__ __forceinline__ void gv_load8(const GvParams& p, int it, uint32_t epoch, float (&v)[8]) {
-    if (!p.tp_wait_on) {
+    if (!(TP && p.tp_wait_on)) {
         // inside a chain the vector was written earlier in this launch: read it past L1, which may hold older lines
-        const uint4 raw = p.chained ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
+        const uint4 raw = (TP && p.chained) ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
         const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
         #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -125,9 +130,10 @@ __device__ __forceinline__ void gv_norm_w8(const GvParams& p, int it, float (&wn
 }
 
 // Sixteen bytes (eight fp16 activations) of the plain vector.
+template <bool TP>
 __device__ __forceinline__ uint4 gv_raw8(const GvParams& p, int it) {
     // inside a chain the vector was written earlier in this launch: read it past L1, which may hold older lines
-    return p.chained ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
+    return (TP && p.chained) ? __ldcg(reinterpret_cast<const uint4*>(p.x + 8 * it)) : *reinterpret_cast<const uint4*>(p.x + 8 * it);
 }
 __device__ __forceinline__ void gv_unpack8(const uint4& raw, float (&v)[8]) {
     const uint32_t w[4] = { raw.x, raw.y, raw.z, raw.w };
@@ -138,7 +144,8 @@ __device__ __forceinline__ void gv_unpack8(const uint4& raw, float (&v)[8]) {
     }
 }
 
-constexpr int GV_STAGE_REGS = 4;    // staging items (16 bytes each) a thread fetches up front and keeps in registers
+constexpr int GV_PRE = 2;           // staging items whose norm weights a thread loads before it waits for the producer
+constexpr int GV_STAGE_REGS = 5;    // staging items (16 bytes each) a thread fetches up front and keeps in registers
 
 // Activation image in shared memory.  Layout A (Q4_K): the int8 codes of super-block b in natural order, cut into
 // sixteen 16-byte chunks j and stored chunk-major, chunk j of block b at (j * nb + b) * 16 — the lanes of a warp work
@@ -146,21 +153,31 @@ constexpr int GV_STAGE_REGS = 4;    // staging items (16 bytes each) a thread fe
 // a 128-half) at k*K/4, run (blk*4 + 2n + c)*16.  In 16-bit mode a second plane with the low bytes follows at +K.
 // Group scales xd / xs: four floats of half h of block b at ((h * nb + b) * 4).
 //
-// `wpre`: the norm weights of this thread's first staging item, loaded by the caller before it waited for the
-// producer kernel (they do not depend on it), so their trip to L2 is off the critical path; have_pre = false: none.
-template <int XM>
-__device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red, const float (&wpre)[8], bool have_pre) {
+// `wpre`: the norm weights of this thread's first `npre` staging items, loaded by the caller before it waited for the
+// producer kernel (they do not depend on it), so their trip to L2 is off the critical path.
+struct GvRange { int gf[3], gl[3]; };   // row groups [gf, gl) of each segment owned by this CTA
+__device__ __forceinline__ void gv_prefetch(const GvParams& p, const GvRange& rg, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], int warp, int lane, bool later,
+                                            int u0, int u1);
+
+// `late`: slots [p.early_slots, p.nslots) of every warp's ring are still empty; their bulk copies are issued here, right
+// after the loads of the activation vector.  Requests leave an SM in order: a load issued behind the requests of a full
+// ring waits for all of them (measured 1.4 us for the 5 KB vector against 0.6 behind half a ring).
+template <bool DBG, bool TP>
+__device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float* red, const float (&wpre)[GV_PRE][8], int npre,
+                                        const GvRange& rg, uint64_t (*full)[GV_MAXSLOT], bool late) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nw_cta = blockDim.x >> 5;
     const int K = p.K, nitems = K / 8, nb = K / QK_K;
-    const uint32_t epoch = p.tp_wait_on ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
-    const bool direct = !p.tp_wait_on;
+    const uint32_t epoch = (TP && p.tp_wait_on) ? p.tpw.seq[0] * (uint32_t)p.tpw.epochs_per_step + (uint32_t)p.tpw.layer + 1u : 0u;
+    const bool direct = !(TP && p.tp_wait_on);
+    const bool xm = p.xmode != 0;             // 16-bit activations in two int8 planes instead of q8_1 codes (one copy of the code serves both)
     // every item of this thread is requested before any is used: one trip to L2, not one per item
     uint4 raw[GV_STAGE_REGS];
     #pragma unroll
     for (int k = 0; k < GV_STAGE_REGS; ++k) {
         const int it = tid + k * nthreads;
-        raw[k] = (direct && it < nitems) ? gv_raw8(p, it) : make_uint4(0u, 0u, 0u, 0u);
+        raw[k] = (direct && it < nitems) ? gv_raw8<TP>(p, it) : make_uint4(0u, 0u, 0u, 0u);
     }
+    if (late) gv_prefetch(p, rg, smem, full, warp, lane, false, p.early_slots, p.nslots);
     float rrms = 1.0f;
     if (p.do_norm) {   // reference: fused_rmsnorm_residual, src/kernels/fused_norm.cu:33-101
         float ss = 0.f;
@@ -175,16 +192,18 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         }
         for (int g8 = tid + (direct ? GV_STAGE_REGS * nthreads : 0); g8 < nitems; g8 += nthreads) {
             float a[8];
-            gv_load8(p, g8, epoch, a);
+            gv_load8<TP>(p, g8, epoch, a);
             #pragma unroll
             for (int i = 0; i < 4; ++i) ss += a[2 * i] * a[2 * i] + a[2 * i + 1] * a[2 * i + 1];
         }
+        if (DBG && p.trace && tid == 0) p.trace[(size_t)blockIdx.x * GV_NTRACE + 12] = global_ns() + (ss == -1.f);
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
         __syncthreads();
         float tot = 0.f;
         for (int w = 0; w < nw_cta; ++w) tot += red[w];
         rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), p.eps)));
+        if (DBG && p.trace && tid == 0) p.trace[(size_t)blockIdx.x * GV_NTRACE + 13] = global_ns() + (rrms == -1.f);
     }
     uint8_t* xA = smem + p.off_xA; uint8_t* xB = smem + p.off_xB;
     float* xd = reinterpret_cast<float*>(smem + p.off_xd);
@@ -193,13 +212,13 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
     // Four threads per 32-element group, eight elements each; the group's absmax and sums are combined with two
     // xor-shuffles inside the quad.  K is a multiple of 256, so K/8 is a multiple of 32 and a warp is either entirely
     // inside an iteration or entirely outside: the shuffles are always between live lanes.
-    auto quantise = [&](int it, float (&v)[8], bool pre) {
+    auto quantise = [&](int it, float (&v)[8], int pre) {             // pre: index into wpre, or -1
         const int gi = it >> 2, q4 = it & 3;
         if (p.do_norm) {
             float wn[8];
-            if (pre) {
+            if (pre >= 0) {
                 #pragma unroll
-                for (int i = 0; i < 8; ++i) wn[i] = wpre[i];
+                for (int i = 0; i < 8; ++i) wn[i] = pre == 0 ? wpre[0][i] : wpre[1][i];
             } else {
                 gv_norm_w8(p, it, wn);
             }
@@ -211,7 +230,8 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-        const float lim = XM == 0 ? 127.0f : 32767.0f;
+        const float lim = xm ? 32767.0f : 127.0f;
+        const int ilim = xm ? 32767 : 127, hshift = xm ? 8 : 0;
         const float d = __fdiv_rn(amax, lim);                      // q8_1: src/kernels/gemv_q4.cu:445-466
         const float id = d > 0.f ? __fdiv_rn(1.0f, d) : 0.f;
         uint32_t hi[2] = { 0, 0 }, lo[2] = { 0, 0 };
@@ -221,37 +241,34 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
             #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float x = v[4 * w + i];
-                const int q = max(-(int)lim, min((int)lim, __float2int_rn(__fmul_rn(x, id))));
+                const int q = max(-ilim, min(ilim, __float2int_rn(__fmul_rn(x, id))));
                 s8 += q;
-                if (XM == 0) hi[w] |= (uint32_t)(q & 0xFF) << (8 * i);
-                else { hi[w] |= (uint32_t)((q >> 8) & 0xFF) << (8 * i); lo[w] |= (uint32_t)(q & 0xFF) << (8 * i); }
+                hi[w] |= (uint32_t)((q >> hshift) & 0xFF) << (8 * i);
+                lo[w] |= (uint32_t)(q & 0xFF) << (8 * i);          // second plane, 16-bit mode only
             }
         }
         const int s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);          // code sum of this thread's 16-element half
         const int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
-        float fsum = 0.f;
-        if (XM == 1) {
-            // fp32 sum of the group in the order of an 8-lane xor tree over 4-element partial sums
-            const float t = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-            const float t2 = t + __shfl_xor_sync(0xFFFFFFFFu, t, 1);
-            fsum = t2 + __shfl_xor_sync(0xFFFFFFFFu, t2, 2);
-        }
+        // fp32 sum of the group in the order of an 8-lane xor tree over 4-element partial sums (16-bit mode)
+        const float t = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+        const float t2 = t + __shfl_xor_sync(0xFFFFFFFFu, t, 1);
+        const float fsum = t2 + __shfl_xor_sync(0xFFFFFFFFu, t2, 2);
         const int blk = gi >> 3, j = gi & 7, h = q4 >> 1, e8 = (q4 & 1) * 8;    // 16-element half h, byte offset inside its run
         if (p.needA) {
             const int off = ((2 * j + h) * nb + blk) * 16 + e8;
             *reinterpret_cast<uint2*>(xA + off) = make_uint2(hi[0], hi[1]);
-            if (XM == 1) *reinterpret_cast<uint2*>(xA + K + off) = make_uint2(lo[0], lo[1]);
+            if (xm) *reinterpret_cast<uint2*>(xA + K + off) = make_uint2(lo[0], lo[1]);
         }
         if (p.needB) {
             const int n = j >> 2, k = j & 3;
             const int off = k * (K >> 2) + (blk * 4 + 2 * n + h) * 16 + e8;
             *reinterpret_cast<uint2*>(xB + off) = make_uint2(hi[0], hi[1]);
-            if (XM == 1) *reinterpret_cast<uint2*>(xB + K + off) = make_uint2(lo[0], lo[1]);
+            if (xm) *reinterpret_cast<uint2*>(xB + K + off) = make_uint2(lo[0], lo[1]);
             if ((q4 & 1) == 0) xsum[2 * gi + h] = s16;
         }
         if (q4 == 0) {
             const int si = ((j >> 2) * nb + blk) * 4 + (j & 3);
-            if (XM == 0) {
+            if (!xm) {
                 xd[si] = __half2float(__float2half_rn(d));
                 xs[si] = __half2float(__float2half_rn(__fmul_rn(d, (float)s32)));
             } else {
@@ -260,22 +277,24 @@ __device__ __forceinline__ void stage_x(const GvParams& p, uint8_t* smem, float*
             }
         }
     };
-    if (direct) {
-        #pragma unroll
-        for (int k = 0; k < GV_STAGE_REGS; ++k) {
-            const int it = tid + k * nthreads;
-            if (it < nitems) {                       // warp-uniform: nitems is a multiple of 32
-                float v[8];
-                gv_unpack8(raw[k], v);
-                quantise(it, v, have_pre && k == 0);
-            }
-        }
-    }
-    for (int it = tid + (direct ? GV_STAGE_REGS * nthreads : 0); it < nitems; it += nthreads) {
+    // ONE copy of the quantiser in a loop that is not unrolled.  Code size matters here: in a decode step every launch
+    // meets a cold instruction cache (four different kernels have run since its last launch) and fetches its code behind
+    // the weight stream; an unrolled staging phase alone was 20 KB of straight-line code on the path to the first dot.
+    #pragma unroll 1
+    for (int k = 0, it = tid; it < nitems; ++k, it += nthreads) {      // warp-uniform trip count: nitems is a multiple of 32
         float v[8];
-        gv_load8(p, it, epoch, v);
-        quantise(it, v, have_pre && it == tid);
+        if (direct && k < GV_STAGE_REGS) {
+            uint4 r = raw[0];
+            #pragma unroll
+            for (int j = 1; j < GV_STAGE_REGS; ++j)
+                if (k == j) r = raw[j];
+            gv_unpack8(r, v);
+        } else {
+            gv_load8<TP>(p, it, epoch, v);
+        }
+        quantise(it, v, k < npre ? k : -1);
     }
+    if (DBG && p.trace && tid == 0) p.trace[(size_t)blockIdx.x * GV_NTRACE + 14] = global_ns();
 }
 
 // ── shared-memory reads by 32-bit shared address (no generic-pointer arithmetic in the inner loop) ──
@@ -300,58 +319,6 @@ __device__ __forceinline__ int dot16_uu(const uint4& w, uint32_t mask, const uin
 
 // shared addresses of the staged activation image
 struct GvX { uint32_t xA, xB, xd, xs, xsum; int K, nb; };
-
-// ── Q4_K: one whole super-block (256 weights) per lane ───────────────────
-// Group il (0..3) of a block holds the low nibbles of sub-block 2*il and the high nibbles of sub-block 2*il+1, 32
-// elements each.  The lane builds all eight 32-element integer dots — the accumulators the reference builds with eight
-// dp4a each (src/kernels/gemv_q4.cu:487-494) — and folds them as
-//   dall * Σ_j sc_j*dot_j*d8_j  -  dmin * Σ_j m_j*s8_j
-// which is the reference's  Σ dall*sc*(d8*dot) - dmin*m*s8  (:499) with the common factors taken out.  The header is
-// read once and the eight 6-bit scales and mins are unpacked four at a time with word-wide masks
-// (get_scale_min_k4, :185-195).  `sb` = shared address of the block (16-byte aligned).
-template <int XM>
-__device__ __forceinline__ float q4k_block(uint32_t sb, int kblk, const GvX& X, int32_t* dots_out) {
-    const uint4 hdr = lds128(sb);
-    const uint32_t sc03 = hdr.y & 0x3F3F3F3Fu, mn03 = hdr.z & 0x3F3F3F3Fu;                         // sub-blocks 0..3, a byte each
-    const uint32_t sc47 = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);                    // sub-blocks 4..7
-    const uint32_t mn47 = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-    const uint32_t step = (uint32_t)X.nb * 16u;                 // bytes between consecutive 16-byte chunks of one block's codes
-    const uint32_t xa = X.xA + (uint32_t)kblk * 16u;
-    const uint4 dA = lds128(X.xd + (uint32_t)kblk * 16u), dB = lds128(X.xd + (uint32_t)(X.nb + kblk) * 16u);
-    const uint4 sA = lds128(X.xs + (uint32_t)kblk * 16u), sB = lds128(X.xs + (uint32_t)(X.nb + kblk) * 16u);
-    const float d8[8] = { __uint_as_float(dA.x), __uint_as_float(dA.y), __uint_as_float(dA.z), __uint_as_float(dA.w),
-                          __uint_as_float(dB.x), __uint_as_float(dB.y), __uint_as_float(dB.z), __uint_as_float(dB.w) };
-    const float s8[8] = { __uint_as_float(sA.x), __uint_as_float(sA.y), __uint_as_float(sA.z), __uint_as_float(sA.w),
-                          __uint_as_float(sB.x), __uint_as_float(sB.y), __uint_as_float(sB.z), __uint_as_float(sB.w) };
-    float pos = 0.f, neg = 0.f;
-    #pragma unroll
-    for (int il = 0; il < 4; ++il) {
-        const uint4 w0 = lds128(sb + 16 + 32 * il), w1 = lds128(sb + 32 + 32 * il);
-        const uint32_t xc = xa + (uint32_t)(4 * il) * step;     // chunks 4il, 4il+1: sub-block 2il; 4il+2, 4il+3: sub-block 2il+1
-        const uint4 xl0 = lds128(xc), xl1 = lds128(xc + step), xh0 = lds128(xc + 2 * step), xh1 = lds128(xc + 3 * step);
-        int dot0, dot1;
-        if (XM == 0) {
-            dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
-            dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
-        } else {
-            const uint32_t yc = xc + (uint32_t)X.K;             // second plane: low bytes of the 16-bit activations
-            const uint4 yl0 = lds128(yc), yl1 = lds128(yc + step), yh0 = lds128(yc + 2 * step), yh1 = lds128(yc + 3 * step);
-            dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
-                   (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
-            dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
-                    ((dot16_uu(w0, 0xF0F0F0F0u, yh0) + dot16_uu(w1, 0xF0F0F0F0u, yh1)) >> 4));
-        }
-        if (dots_out) { dots_out[2 * il] = dot0; dots_out[2 * il + 1] = dot1; }
-        const uint32_t scw = il < 2 ? sc03 : sc47, mnw = il < 2 ? mn03 : mn47;
-        const int sh = 16 * (il & 1);
-        const int sc0 = (int)((scw >> sh) & 0xFFu), sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
-        const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
-        pos += (float)(sc0 * dot0) * d8[2 * il] + (float)(sc1 * dot1) * d8[2 * il + 1];
-        neg += (float)m0 * s8[2 * il] + (float)m1 * s8[2 * il + 1];
-    }
-    const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));      // (d, dmin)
-    return dm.x * pos - dm.y * neg;
-}
 
 // ── Q6_K: one (half n, column run c) per lane = 64 weights in four 16-element scale groups (quarters k = 0..3
 // at +32k), reference arithmetic src/kernels/gemv_q4.cu:581-618: per group  d*sc*(d8*dot)  with
@@ -406,40 +373,107 @@ __device__ __forceinline__ float q6k_item(uint32_t sb, int n, int c, int kblk, c
     return d * acc;
 }
 
-// One warp, `nrw` (<= 4) consecutive rows in shared memory.  Q4_K: lanes stride over the rows' super-blocks, one whole
-// block per lane per round.  Q6_K: lanes stride over 32-byte items (4 per super-block); 32 and U are multiples of 4, so
-// a lane's sub-item never changes.  Each lane adds its terms into the accumulator of the row the item belongs to.
+// ── Q4_K: one super-block COLUMN per lane, RL rows deep ──────────────────
+// The warp is cut into groups of `lw` lanes; lane c of group g owns super-block column c of the RL consecutive rows
+// g*RL .. g*RL + RL - 1 of the task (a row with more than lw blocks is walked in passes c, c + lw, ...).  The 256
+// activation codes and eight group scales of a column are read from shared memory ONCE and multiplied against all RL
+// rows, so a block costs 9 sixteen-byte shared loads (its own 144 bytes) plus 20 / RL for the activations, instead of
+// 29: the kernel is bound by shared-memory bandwidth once all its weights are in flight, and this is what halves it.
+// Arithmetic per (row, block) is that of the reference (src/kernels/gemv_q4.cu:487-499): eight 32-element dp4a dots,
+// folded as  dall * Σ_j sc_j*dot_j*d8_j  -  dmin * Σ_j m_j*s8_j  with the scales unpacked four at a time by word-wide
+// masks (get_scale_min_k4, :185-195); it does not depend on RL, so every launch shape gives the same bits per row.
+// `nrw` rows are present (the last task of a matrix may hold fewer than lg*RL); acc[r] collects row g*RL + r.
+template <int XM, int RL, bool DBG>
+__device__ __forceinline__ void q4k_columns(uint32_t rows, int nrw, unsigned rb, int nbc, int kb0, int Ufull, int lane, const GvX& X,
+                                            unsigned lw, unsigned lg, float (&acc)[4], int32_t* dbg) {
+    const unsigned g = (unsigned)lane / lw, c = (unsigned)lane - g * lw;
+    const int rbase = (int)g * RL;
+    const int nr = min(RL, nrw - rbase);
+    if (g >= lg || nr <= 0) return;
+    const uint32_t step = (uint32_t)X.nb * 16u;                 // bytes between consecutive 16-byte chunks of one block's codes
+    for (unsigned blk = c; blk < (unsigned)nbc; blk += lw) {
+        const int kblk = kb0 + (int)blk;
+        const uint32_t sb0 = rows + (uint32_t)rbase * rb + blk * Q4K_BYTES;
+        uint32_t sclo[RL], schi[RL];       // 6-bit scales of sub-blocks 0..3 / 4..7, a byte each
+        float dall[RL], pos[RL], fixed[RL];
+        {
+            const uint4 sA = lds128(X.xs + (uint32_t)kblk * 16u), sB = lds128(X.xs + (uint32_t)(X.nb + kblk) * 16u);
+            const float s8[8] = { __uint_as_float(sA.x), __uint_as_float(sA.y), __uint_as_float(sA.z), __uint_as_float(sA.w),
+                                  __uint_as_float(sB.x), __uint_as_float(sB.y), __uint_as_float(sB.z), __uint_as_float(sB.w) };
+            #pragma unroll
+            for (int r = 0; r < RL; ++r) {
+                const uint4 hdr = lds128(sb0 + (uint32_t)min(r, nr - 1) * rb);
+                sclo[r] = hdr.y & 0x3F3F3F3Fu;
+                schi[r] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+                const uint32_t mn03 = hdr.z & 0x3F3F3F3Fu, mn47 = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+                float neg = 0.f;
+                #pragma unroll
+                for (int il = 0; il < 4; ++il) {
+                    const uint32_t mnw = il < 2 ? mn03 : mn47;
+                    const int sh = 16 * (il & 1);
+                    neg += (float)(int)((mnw >> sh) & 0xFFu) * s8[2 * il] + (float)(int)((mnw >> (sh + 8)) & 0xFFu) * s8[2 * il + 1];
+                }
+                const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));      // (d, dmin)
+                dall[r] = dm.x; fixed[r] = dm.y * neg; pos[r] = 0.f;
+            }
+        }
+        const uint32_t xa = X.xA + (uint32_t)kblk * 16u;
+        #pragma unroll 1                                            // kept rolled: a quarter of the code, and the RL rows give the parallelism
+        for (int il = 0; il < 4; ++il) {
+            const uint32_t xc = xa + (uint32_t)(4 * il) * step;     // chunks 4il, 4il+1: sub-block 2il; 4il+2, 4il+3: sub-block 2il+1
+            const uint4 xl0 = lds128(xc), xl1 = lds128(xc + step), xh0 = lds128(xc + 2 * step), xh1 = lds128(xc + 3 * step);
+            uint4 yl0, yl1, yh0, yh1;
+            if (XM == 1) {                                          // second plane: low bytes of the 16-bit activations
+                const uint32_t yc = xc + (uint32_t)X.K;
+                yl0 = lds128(yc); yl1 = lds128(yc + step); yh0 = lds128(yc + 2 * step); yh1 = lds128(yc + 3 * step);
+            }
+            // scales of the two 32-element groups of this quarter: floats 2il, 2il+1 of the block's eight
+            const uint2 dq = lds64(X.xd + (uint32_t)((il >> 1) * X.nb + kblk) * 16u + (uint32_t)(il & 1) * 8u);
+            const float d8a = __uint_as_float(dq.x), d8b = __uint_as_float(dq.y);
+            const int sh = 16 * (il & 1);
+            #pragma unroll
+            for (int r = 0; r < RL; ++r) {
+                const uint32_t sbr = sb0 + (uint32_t)min(r, nr - 1) * rb;
+                const uint4 w0 = lds128(sbr + 16 + 32 * il), w1 = lds128(sbr + 32 + 32 * il);
+                int dot0, dot1;
+                if (XM == 0) {
+                    dot0 = dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1);
+                    dot1 = (dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) >> 4;   // exact: every term is a multiple of 16
+                } else {
+                    dot0 = (dot16_us(w0, 0x0F0F0F0Fu, xl0) + dot16_us(w1, 0x0F0F0F0Fu, xl1)) * 256 +
+                           (dot16_uu(w0, 0x0F0F0F0Fu, yl0) + dot16_uu(w1, 0x0F0F0F0Fu, yl1));
+                    dot1 = ((dot16_us(w0, 0xF0F0F0F0u, xh0) + dot16_us(w1, 0xF0F0F0F0u, xh1)) * 16 +
+                            ((dot16_uu(w0, 0xF0F0F0F0u, yh0) + dot16_uu(w1, 0xF0F0F0F0u, yh1)) >> 4));
+                }
+                if (DBG && dbg && r < nr) {
+                    int32_t* o = dbg + (size_t)(rbase + r) * (2 * Ufull) + (size_t)kblk * 8;
+                    o[2 * il] = dot0; o[2 * il + 1] = dot1;
+                }
+                const uint32_t scw = il < 2 ? sclo[r] : schi[r];
+                const int sc0 = (int)((scw >> sh) & 0xFFu), sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
+                pos[r] += (float)(sc0 * dot0) * d8a + (float)(sc1 * dot1) * d8b;
+            }
+        }
+        #pragma unroll
+        for (int r = 0; r < RL; ++r)
+            if (r < nr) acc[r] += dall[r] * pos[r] - fixed[r];
+    }
+}
+
+// One warp, `nrw` consecutive rows in shared memory.  Q4_K: q4k_columns with the segment's lane map.  Q6_K (nrw <= 4):
+// lanes stride over 32-byte items (4 per super-block); 32 and U are multiples of 4, so a lane's sub-item never changes;
+// each lane adds its terms into the accumulator of the row the item belongs to.
 // `rb_` = bytes between consecutive rows in shared memory, `U_` = 4 x the super-blocks per row held there (a chunk of
 // the row when the row is streamed in several tasks: its first super-block is kb0), `Ufull` = 4 x those of a whole row.
 template <int XM, int TYPE, bool DBG>
 __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, int U_, int kb0, int Ufull, int lane, const GvX& X,
-                                             float (&acc)[4], int32_t* dbg) {
+                                             const GvSegDev& sg, float (&acc)[4], int32_t* dbg) {
     const unsigned rb = (unsigned)rb_;
     if (TYPE == T_Q4K) {
-        const unsigned nbc = (unsigned)U_ >> 2, total = (unsigned)nrw * nbc;
-        // One round (the usual case): lanes 8r .. 8r+7 take super-blocks 0..7 of row r, the lanes after them the blocks from 8
-        // on, row by row.  The 16-byte runs of the activation image repeat their banks every eight super-blocks, so a
-        // quarter-warp that held blocks b and b + 8 of two rows (as the plain row-major order does for 10 blocks per row)
-        // would read them in two passes; this order keeps eight distinct (block mod 8) — or equal addresses — per quarter.
-        const bool octets = total <= 32 && nbc > 8 && nbc <= 16;
-        for (unsigned base = 0; base < total; base += 32) {
-            const unsigned i = base + lane;
-            const bool valid = i < total;
-            const unsigned ii = valid ? i : 0u;
-            unsigned rl, blk;
-            if (octets) {
-                const unsigned head = 8u * (unsigned)nrw, tailw = nbc - 8u;
-                if (ii < head) { rl = ii >> 3; blk = ii & 7u; }
-                else { const unsigned k = ii - head; rl = (k >= tailw) + (k >= 2 * tailw) + (k >= 3 * tailw); blk = 8u + k - rl * tailw; }
-            } else {
-                rl = (ii >= nbc) + (ii >= 2 * nbc) + (ii >= 3 * nbc);
-                blk = ii - rl * nbc;
-            }
-            int32_t* o = (DBG && dbg && valid) ? dbg + (size_t)rl * (2 * Ufull) + (kb0 + blk) * 8 : nullptr;
-            float term = q4k_block<XM>(rows + rl * rb + blk * Q4K_BYTES, kb0 + (int)blk, X, DBG ? o : nullptr);
-            if (!valid) term = 0.f;
-            acc[0] += rl == 0 ? term : 0.f; acc[1] += rl == 1 ? term : 0.f;
-            acc[2] += rl == 2 ? term : 0.f; acc[3] += rl == 3 ? term : 0.f;
+        const int nbc = U_ >> 2;
+        switch (sg.rl) {
+            case 1:  q4k_columns<XM, 1, DBG>(rows, nrw, rb, nbc, kb0, Ufull, lane, X, sg.lw, sg.lg, acc, dbg); break;
+            default: q4k_columns<XM, 3, DBG>(rows, nrw, rb, nbc, kb0, Ufull, lane, X, sg.lw, sg.lg, acc, dbg); break;
         }
         return;
     }
@@ -468,8 +502,6 @@ __device__ __forceinline__ void consume_rows(uint32_t rows, int nrw, int rb_, in
 // pipeline: its lane 0 issues the bulk copy of a group into one of the warp's slots, the warp waits on that
 // slot's mbarrier, consumes the rows and moves on — no CTA-wide barrier in the loop, so dot products start
 // as soon as the first group lands while the rest of the CTA's bytes are still in flight.
-struct GvRange { int gf[3], gl[3]; };   // row groups [gf, gl) of each segment owned by this CTA
-
 // task `u` of warp `warp` -> segment, first row, number of rows
 struct GvTask { int seg, row0, nrows, kb0, kb1; bool last; };   // rows [row0, row0+nrows) x super-blocks [kb0, kb1); last chunk of the rows
 
@@ -522,12 +554,13 @@ __device__ __forceinline__ void gv_issue(const GvParams& p, const GvTask& t, uin
 
 // first tasks of a phase: start the bulk copies of this warp's first row groups.  The slot barriers are created once
 // per kernel and live through all phases of a chain; `later` = not the first phase of the launch.
-__device__ __forceinline__ void gv_prefetch(const GvParams& p, const GvRange& rg, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], int warp, int lane, bool later) {
+__device__ __forceinline__ void gv_prefetch(const GvParams& p, const GvRange& rg, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], int warp, int lane, bool later,
+                                            int u0, int u1) {
     if (warp >= p.nwarps) return;
     uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
     if (lane == 0) {
         if (later) fence_proxy_async();       // the slots were read with ordinary loads in the phase before
-        for (int u = 0; u < p.nslots; ++u) {
+        for (int u = u0; u < u1; ++u) {
             GvTask t;
             if (!gv_task(p, rg, warp, u, t)) break;
             gv_issue(p, t, ring + (unsigned)u * (unsigned)p.slot_bytes, &full[warp][u]);
@@ -541,20 +574,24 @@ __device__ __forceinline__ void gv_stamp(const GvParams& p, int k) {
     p.trace[(size_t)blockIdx.x * GV_NTRACE + k] = global_ns();
 }
 
-template <int XM, bool DBG>
+// Q4: the launch may hold Q4_K matrices (false: Q6_K only — the Q4_K code, which wants 128 registers, is left out of the
+// 80-register instantiation).
+template <bool DBG, bool Q4, bool TP>
 __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint64_t (*full)[GV_MAXSLOT], float* red, const GvRange& rg, uint32_t& par,
-                                         const float (&wpre)[8], bool have_pre) {
+                                         const float (&wpre)[GV_PRE][8], int npre, bool late) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     uint8_t* ring = smem + p.off_slots + (unsigned)warp * (unsigned)(p.nslots * p.slot_bytes);
-    stage_x<XM>(p, smem, red, wpre, have_pre);
+    // the activation format (p.xmode) is a run-time switch inside the quantiser and around the dot products; everything else
+    // exists once
+    stage_x<DBG, TP>(p, smem, red, wpre, npre, rg, full, late);
     __syncthreads();
     if (DBG && p.trace && tid == 0) gv_stamp(p, 3);
     if (warp >= p.nwarps) return;            // chain phases may use fewer warps than the CTA has (larger staging rings)
 
     const uint32_t sm0 = smem_u32(smem);
     const GvX X = { sm0 + p.off_xA, sm0 + p.off_xB, sm0 + p.off_xd, sm0 + p.off_xs, sm0 + p.off_xsum, p.K, p.K / QK_K };
-    const uint32_t push_epoch = p.tp_push_on ? p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u : 0u;
+    const uint32_t push_epoch = (TP && p.tp_push_on) ? p.tpp.seq[0] * (uint32_t)p.tpp.epochs_per_step + (uint32_t)p.tpp.layer + 1u : 0u;
     bool timed_out = false;
     float gate_keep[4] = { 0.f, 0.f, 0.f, 0.f };
     float acc[4] = { 0.f, 0.f, 0.f, 0.f };       // lives across the chunks of a row
@@ -584,8 +621,13 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
         int32_t* dbg = (DBG && seg == 0 && p.dbg_dots) ? p.dbg_dots + (size_t)row0 * (s.type == T_Q4K ? 2 * s.U : 4 * s.U) : nullptr;
         const int Uc = p.nchunk > 1 ? 4 * (t.kb1 - t.kb0) : s.U, kb0 = p.nchunk > 1 ? t.kb0 : 0;
         if (!(DBG && p.trace && p.trace_nocompute)) {
-            if (s.type == T_Q4K) consume_rows<XM, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
-            else                 consume_rows<XM, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, acc, dbg);
+            if (Q4 && s.type == T_Q4K) {
+                if (p.xmode) consume_rows<1, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, s, acc, dbg);
+                else         consume_rows<0, T_Q4K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, s, acc, dbg);
+            } else {
+                if (p.xmode) consume_rows<1, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, s, acc, dbg);
+                else         consume_rows<0, T_Q6K, DBG>(smem_u32(rows), nrows, s.rb, Uc, kb0, s.U, lane, X, s, acc, dbg);
+            }
         }
         __syncwarp();                            // the warp is done reading this slot
         if (DBG && p.trace && tid == 0 && u < 4) gv_stamp(p, 9 + 2 * u);          // warp 0: task u has been multiplied
@@ -597,11 +639,35 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
             }
         }
         if (!t.last) continue;                   // more super-blocks of these rows follow in the next task
-        // Row sums in six shuffles instead of twenty: the halves of the warp take over two rows each (xor 16), the quarters
-        // one row each (xor 8), then three steps inside the octet.  Every lane of octet r ends with the sum of row r; its
-        // first lane finishes the row.
-        float mine;
-        {
+        float mine = 0.f;
+        bool has_row; int row_local;
+        if (Q4 && s.type == T_Q4K) {
+            // Lane c of group g holds partial sums of rows g*rl + r in acc[r]: a guarded shuffle-down tree over the lw lanes of
+            // the group (any width) leaves the totals in the group's first lane, which hands total r to lane r of the group.
+            const unsigned lw = s.lw, g = (unsigned)lane / lw, c = (unsigned)lane - g * lw;
+            #pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                if ((unsigned)off < lw) {
+                    #pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float o = __shfl_down_sync(0xFFFFFFFFu, acc[r], off);
+                        if (c + (unsigned)off < lw) acc[r] += o;
+                    }
+                }
+            }
+            const int first = g < s.lg ? (int)(g * lw) : lane;
+            #pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float o = __shfl_sync(0xFFFFFFFFu, acc[r], first);
+                if (c == (unsigned)r) mine = o;
+            }
+            row_local = (int)(g * s.rl + c);
+            has_row = g < s.lg && c < s.rl && row_local < nrows;
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        } else {
+            // Row sums in six shuffles instead of twenty: the halves of the warp take over two rows each (xor 16), the quarters
+            // one row each (xor 8), then three steps inside the octet.  Every lane of octet r ends with the sum of row r; its
+            // first lane finishes the row.
             const bool hi16 = lane & 16, hi8 = lane & 8;
             float k0 = hi16 ? acc[2] : acc[0], k1 = hi16 ? acc[3] : acc[1];
             const float g0 = hi16 ? acc[0] : acc[2], g1 = hi16 ? acc[1] : acc[3];
@@ -614,20 +680,21 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
             mine = v;
             acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            row_local = lane >> 3;               // the row of this lane's octet
+            has_row = (lane & 7) == 0 && row_local < nrows;
         }
-        const int rsel = lane >> 3;              // the row of this lane's octet
         if (p.out_mode == 3 && seg == 0) {       // gate values stay in registers until the matching up rows arrive
-            gate_keep[0] = __half2float(__float2half_rn(mine));      // octet r keeps the gate value of row r
+            gate_keep[0] = __half2float(__float2half_rn(mine));      // the lane that will finish row r keeps its gate value
             continue;
         }
-        if ((lane & 7) == 0 && rsel < nrows) {
-            const int row = row0 + rsel;
+        if (has_row) {
+            const int row = row0 + row_local;
             if (p.out_mode == 0)      reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(mine);
             else if (p.out_mode == 1) reinterpret_cast<float*>(s.y)[row] = mine;
             else if (p.out_mode == 2) {   // src/kernels/gemv_q4.cu:996-999
                 const __half pr = __float2half_rn(mine);
                 float res;
-                if (p.residual_pk) {          // written earlier in this launch by another CTA of this rank: valid once its epoch matches
+                if (TP && p.residual_pk) {    // written earlier in this launch by another CTA of this rank: valid once its epoch matches
                     uint2 q;
                     PollGuard guard(p.status);
                     for (;;) {
@@ -636,7 +703,7 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
                     }
                     res = __half2float(__ushort_as_half((unsigned short)(q.x & 0xFFFFu)));
                 } else {
-                    res = __half2float(p.chained ? __ldcg(p.residual + row) : p.residual[row]);
+                    res = __half2float((TP && p.chained) ? __ldcg(p.residual + row) : p.residual[row]);
                 }
                 reinterpret_cast<__half*>(s.y)[row] = __float2half_rn(__fadd_rn(__half2float(pr), res));
             } else {                      // fused SwiGLU of the gate/up pair (src/kernels/convert.cu:85-104)
@@ -644,7 +711,7 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
                 const float g = gate_keep[0];
                 reinterpret_cast<__half*>(p.seg[0].y)[row] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), hv));
             }
-            if (p.tp_push_on) {           // the value just stored, as a packet to every rank (this one included)
+            if (TP && p.tp_push_on) {     // the value just stored, as a packet to every rank (this one included)
                 const unsigned short bits = __half_as_ushort(reinterpret_cast<const __half*>(p.out_mode == 3 ? p.seg[0].y : s.y)[row]);
                 const uint2 pkt = make_uint2((uint32_t)bits, push_epoch);
                 #pragma unroll 1
@@ -661,40 +728,44 @@ __device__ __forceinline__ void gv_phase(const GvParams& p, uint8_t* smem, uint6
 }
 
 
-// this CTA's row groups in every segment: an even split of all groups by bytes
+// this CTA's row groups in every segment: an even split of all groups by weight (bytes per group, scaled by the host so
+// that the total fits 31 bits; 1 per group of the first matrix for a gate/up pair).  The arithmetic runs on the path from
+// CTA entry to the first bulk copy: 32-bit only, total * b / grid as q*b + r*b/grid with q, r from the host.
 __device__ __forceinline__ GvRange gv_range(const GvParams& p) {
     GvRange rg;
-    const long long G = gridDim.x, b = blockIdx.x;
-    if (p.paired_rows) {      // out_mode 3: the same groups of both matrices
-        const int R = p.seg[0].R, groups = (p.seg[0].M + R - 1) / R;
-        rg.gf[0] = rg.gf[1] = (int)((long long)groups * b / G);
-        rg.gl[0] = rg.gl[1] = (int)((long long)groups * (b + 1) / G);
-        rg.gf[2] = rg.gl[2] = 0;
-    } else {
-        const long long lo = p.total_bytes * b / G, hi = p.total_bytes * (b + 1) / G;
-        long long cum = 0;
-        #pragma unroll
-        for (int i = 0; i < 3; ++i) {
-            rg.gf[i] = rg.gl[i] = 0;
-            if (i < p.nseg) {
-                const long long R = p.seg[i].R, gb = R * p.seg[i].rb, groups = (p.seg[i].M + R - 1) / R;
-                long long f = lo - cum <= 0 ? 0 : (lo - cum + gb - 1) / gb;
-                long long l = hi - cum <= 0 ? 0 : (hi - cum + gb - 1) / gb;
-                rg.gf[i] = (int)(f > groups ? groups : f); rg.gl[i] = (int)(l > groups ? groups : l);
-                cum += gb * groups;
-            }
+    const unsigned G = gridDim.x, b = blockIdx.x;
+    const unsigned lo = p.split_q * b + (p.split_r * b) / G, hi = p.split_q * (b + 1u) + (p.split_r * (b + 1u)) / G;
+    unsigned cum = 0;
+    #pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        rg.gf[i] = rg.gl[i] = 0;
+        if (i < p.nseg && p.gw[i]) {
+            const unsigned w = p.gw[i], n = p.ng[i];
+            const unsigned f = lo <= cum ? 0u : (lo - cum + w - 1u) / w, l = hi <= cum ? 0u : (hi - cum + w - 1u) / w;
+            rg.gf[i] = (int)(f > n ? n : f); rg.gl[i] = (int)(l > n ? n : l);
+            cum += w * n;
         }
     }
+    if (p.paired_rows) { rg.gf[1] = rg.gf[0]; rg.gl[1] = rg.gl[0]; }      // out_mode 3: the same groups of both matrices
     return rg;
 }
 
-// WHOLE = false: a CTA takes half an SM (see above); WHOLE = true: a CTA takes a whole SM (up to 20 warps and all the
-// shared memory), for products whose rows are so long that half an SM holds too few of them.
-template <int XM, bool DBG, bool WHOLE>
-__global__ void __launch_bounds__(WHOLE ? GV_CHAINTHREADS : GV_MAXTHREADS, WHOLE ? 1 : 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+// TP: with the tensor-parallel hooks (activations and residuals as polled packets, results pushed to the peers); the
+// single-GPU instantiation leaves that code out.
+template <bool DBG, bool TP>
+__global__ void __launch_bounds__(GV_MAXWARPS * 32, 2) gemv_stream_kernel(const __grid_constant__ GvParams p) {
+    constexpr int MW = GV_MAXWARPS;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[WHOLE ? GV_CHAINWARPS : GV_MAXWARPS][GV_MAXSLOT];
-    __shared__ float red[WHOLE ? GV_CHAINWARPS : GV_MAXWARPS];
+    __shared__ __align__(8) uint64_t full[MW][GV_MAXSLOT];
+    __shared__ float red[MW];
+    {   // Touch every 128-byte line of the argument block at once: the first read of each line after a launch misses the
+        // constant cache, and the path to the first bulk copy would otherwise take those misses one after the other.
+        const int* pw = reinterpret_cast<const int*>(&p);
+        int touched = 0;
+        #pragma unroll
+        for (int i = 0; i < (int)(sizeof(GvParams) / 4); i += 32) touched |= pw[i];
+        if (touched == 0x7F7F7F7F && p.nseg == 99) red[0] = 0.f;       // never true; keeps the loads
+    }
     if (DBG && p.trace && threadIdx.x == 0) { gv_stamp(p, 0); p.trace[(size_t)blockIdx.x * GV_NTRACE + 6] = 0ull; }
     pdl_launch();                // the next kernel's CTAs may take the free half of every SM now; they wait for our completion
                                  // before they touch our outputs
@@ -704,15 +775,21 @@ __global__ void __launch_bounds__(WHOLE ? GV_CHAINTHREADS : GV_MAXTHREADS, WHOLE
         fence_mbar_init();
     }
     __syncwarp();
-    gv_prefetch(p, rg, smem, full, threadIdx.x >> 5, threadIdx.x & 31, false);   // weights do not depend on the previous kernel
-    float wpre[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
-    const bool have_pre = p.do_norm && (int)threadIdx.x < p.K / 8;
-    if (have_pre) gv_norm_w8(p, threadIdx.x, wpre);                               // nor do the norm weights
+    gv_prefetch(p, rg, smem, full, threadIdx.x >> 5, threadIdx.x & 31, false, 0, p.early_slots);   // weights do not depend on the previous kernel
+    float wpre[GV_PRE][8];
+    int npre = 0;
+    #pragma unroll
+    for (int k = 0; k < GV_PRE; ++k) {                                            // nor do the norm weights
+        const int it = (int)threadIdx.x + k * (int)blockDim.x;
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) wpre[k][i] = 0.f;
+        if (p.do_norm && it < p.K / 8) { gv_norm_w8(p, it, wpre[k]); npre = k + 1; }
+    }
     if (DBG && p.trace && threadIdx.x == 0) gv_stamp(p, 1);
     pdl_wait();                  // x (and the residual) come from the kernel before us
     if (DBG && p.trace && threadIdx.x == 0) gv_stamp(p, 2);
     uint32_t par = 0;
-    gv_phase<XM, DBG>(p, smem, full, red, rg, par, wpre, have_pre);
+    gv_phase<DBG, true, TP>(p, smem, full, red, rg, par, wpre, npre, p.early_slots < p.nslots);
 }
 
 // ── chain: up to four GEMVs that feed one another (Wo -> gate/up -> W_down -> next layer's Q/K/V) in ONE launch ──
@@ -752,7 +829,7 @@ __global__ void __launch_bounds__(GV_CHAINTHREADS, 1) gemv_chain_kernel(const __
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[GV_CHAINWARPS][GV_MAXSLOT];
     __shared__ float red[GV_CHAINWARPS];
-    const float wpre[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+    const float wpre[GV_PRE][8] = {};
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {                          // slot barriers of every warp, for all phases
         for (int s = 0; s < GV_MAXSLOT; ++s) mbar_init(&full[warp][s], 1);
@@ -761,7 +838,7 @@ __global__ void __launch_bounds__(GV_CHAINTHREADS, 1) gemv_chain_kernel(const __
     __syncwarp();
     uint32_t par = 0;                         // per slot barrier: parity of the phase its next copy completes
     GvRange rg = gv_range(c.ph[0]);
-    gv_prefetch(c.ph[0], rg, smem, full, warp, lane, false);
+    gv_prefetch(c.ph[0], rg, smem, full, warp, lane, false, 0, c.ph[0].nslots);
     pdl_launch();
     pdl_wait();
     for (int i = 0; i < c.n; ++i) {
@@ -769,12 +846,11 @@ __global__ void __launch_bounds__(GV_CHAINTHREADS, 1) gemv_chain_kernel(const __
         if (i > 0) {
             __syncthreads();                  // every warp of this CTA is done with the rings of the phase before
             rg = gv_range(p);
-            gv_prefetch(p, rg, smem, full, warp, lane, true);
+            gv_prefetch(p, rg, smem, full, warp, lane, true, 0, p.nslots);
             if (c.bar) gv_grid_barrier(c.bar, p.status); // ... and every CTA with its rows: the next activation vector is complete
             // (no barrier when every input of the phase arrives as packets: each element carries its own arrival mark)
         }
-        if (p.xmode) gv_phase<1, false>(p, smem, full, red, rg, par, wpre, false);
-        else         gv_phase<0, false>(p, smem, full, red, rg, par, wpre, false);
+        gv_phase<false, true, true>(p, smem, full, red, rg, par, wpre, 0, false);
     }
 }
 
@@ -819,7 +895,24 @@ int launch_gemv_q5k(__half* y, float* y32, const void* W, const __half* x, const
     return JB_OK;
 }
 
-// rows per warp pass: the count of 32-byte items of a row group should fill whole warps
+// the split of the row groups over `grid` CTAs (gv_range)
+static void gv_set_split(GvParams& p, int grid) {
+    unsigned long long tot = 0;
+    for (int shift = 0;; ++shift) {
+        tot = 0;
+        for (int i = 0; i < 3; ++i) {
+            p.gw[i] = 0; p.ng[i] = 0;
+            if (i >= p.nseg || (p.paired_rows && i > 0)) continue;
+            const unsigned long long gb = (unsigned long long)p.seg[i].R * p.seg[i].rb >> shift;
+            p.gw[i] = p.paired_rows ? 1u : (uint32_t)(gb ? gb : 1);
+            p.ng[i] = (uint32_t)((p.seg[i].M + p.seg[i].R - 1) / p.seg[i].R);
+            tot += (unsigned long long)p.gw[i] * p.ng[i];
+        }
+        if (tot < (1ull << 31)) break;
+    }
+    p.split_q = (uint32_t)(tot / grid); p.split_r = (uint32_t)(tot % grid);
+}
+
 
 // Fills the device-side argument block for one GEMV.  max_warps caps the warps per CTA (a chain runs all its phases
 // with one block size); on return smem_bytes / grid hold what this GEMV wants.
@@ -876,8 +969,6 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
     static const int ctas_env = [] { const char* v = getenv("JLLM_B200_GEMV_CTAS"); return v ? atoi(v) : 0; }();
     const bool two = ctas_env ? ctas_env == 2 : all_bytes > (long long)cx->sm_count * (budget - 8192);
     const int ncta = (two_per_sm && two) ? 2 * cx->sm_count : cx->sm_count;
-    int rb_max = 0;
-    for (int i = 0; i < a.nseg; ++i) { const int rb = nb * block_bytes(a.seg[i].type); rb_max = rb > rb_max ? rb : rb_max; }
     uint32_t off = 0;
     p.off_xA = off; off += p.needA ? planes * K : 0;
     p.off_xB = off; off += p.needB ? planes * K : 0;
@@ -887,33 +978,58 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
     p.off_gate = off;
     off = (off + 127) & ~127u;
     p.off_slots = off;
-    static const int warp_choices[] = { 20, 19, 18, 17, 16, 14, 13, 12, 11, 10, 9, 8, 6, 4 };
+    static const int warp_choices[] = { 20, 19, 18, 17, 16, 14, 13, 12, 11, 10, 9, 8, 7, 6, 5, 4, 3, 2 };
+    // Per candidate (warps per CTA, depth): a Q4_K matrix takes `depth` rows per lane — lanes in groups of lw = the row's
+    // blocks spread over the fewest passes, lg = 32 / lw groups, so a task holds lg * depth rows; a Q6_K matrix takes
+    // `depth` rows per task.  Or one row streamed as C = 2..8 chunks of super-blocks by the same warp (long rows, where even
+    // one row does not fit half a ring).  Cost of a candidate = the longest chain of tasks a warp runs, in units of one
+    // 64-weight item per lane.  A Q4_K column of 1 / 3 rows costs 4.0 / 4.2: the rows of a column are independent
+    // instruction streams that fill each other's latencies (measured per task: 1.3 / 1.35 us).
+    // JLLM_B200_GEMV_DEPTH / _WARPS pin either for experiments.
+    static const int pin_depth = [] { const char* v = getenv("JLLM_B200_GEMV_DEPTH"); return v ? atoi(v) : 0; }();
+    static const int pin_warps = [] { const char* v = getenv("JLLM_B200_GEMV_WARPS"); return v ? atoi(v) : 0; }();
+    struct Lane { int lw, lg, rl, rows; };
+    auto lane_map = [&](int type, int depth, int blocks) {      // rows per task of a matrix at this depth
+        Lane m = { 32, 1, 1, depth };
+        if (type == T_Q4K) {
+            const int passes = (blocks + 31) / 32;
+            m.lw = (blocks + passes - 1) / passes;
+            m.lg = 32 / m.lw;
+            m.rl = depth >= 3 && m.lw >= 3 ? 3 : 1;  // columns are instantiated 1 and 3 rows deep (code size)
+            m.rows = m.lg * m.rl;
+        }
+        return m;
+    };
     int best_w = 0, best_R = 0, best_C = 1; double best_cost = 1e30;
-    int bb_max = 0;
-    for (int i = 0; i < a.nseg; ++i) bb_max = block_bytes(a.seg[i].type) > bb_max ? block_bytes(a.seg[i].type) : bb_max;
     for (int nwarps : warp_choices) {
-        if (nwarps > max_warps) continue;
+        if (nwarps > max_warps || (pin_warps && nwarps != pin_warps && pin_warps <= max_warps)) continue;
         const int ring = (budget - (int)off) / nwarps;        // bytes of staging ring per warp
         const int slot_cap = ring / 2;                        // at least two slots per warp
-        // candidates: R = 4..1 whole rows per task; or one row streamed as C = 2..8 chunks of super-blocks by the same
-        // warp (long rows, where even one row does not fit half a ring)
         for (int cand = 4; cand >= -8; --cand) {
             if (cand == 0 || cand == -1) continue;
             const int R = cand > 0 ? cand : 1, C = cand > 0 ? 1 : -cand;
+            if (pin_depth && C == 1 && R != pin_depth) continue;
             if (C > 1 && (a.out_mode == 3 || C > nb)) continue;
             const int cb = (nb + C - 1) / C;                  // super-blocks per chunk
             if (C > 1 && (nb + cb - 1) / cb != C) continue;   // this chunk count would leave an empty last chunk
-            const long long task_bytes = C > 1 ? (long long)cb * bb_max : (long long)R * rb_max;
-            if (task_bytes + 16 + 127 > slot_cap) continue;
-            long long groups = 0;       // units a warp takes one at a time: row groups, or (gate, up) pairs of groups
-            for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg); ++i) groups += (a.seg[i].M + R - 1) / R;
-            const long long per_cta = (groups + ncta - 1) / ncta;
+            long long tasks = 0; double work = 0; bool fits = true;
+            for (int i = 0; i < (a.out_mode == 3 ? 1 : a.nseg) && fits; ++i) {
+                const int type = a.seg[i].type, bbytes = block_bytes(type);
+                const Lane m = lane_map(type, C > 1 ? 1 : R, C > 1 ? cb : nb);
+                const int rows = C > 1 ? 1 : m.rows;
+                const long long task_bytes = (long long)rows * (C > 1 ? cb : nb) * bbytes;
+                if (task_bytes + 16 + 127 > slot_cap) { fits = false; break; }
+                const long long t = ((long long)a.seg[i].M + rows - 1) / rows;
+                const int blocks = C > 1 ? cb : nb;
+                static const double column_cost[4] = { 0.0, 4.0, 0.0, 4.2 };
+                const double per_task = type == T_Q4K ? ((blocks + m.lw - 1) / m.lw) * column_cost[m.rl] + 0.5
+                                                      : (double)((rows * blocks * 4 + 31) / 32) + 0.5;
+                tasks += t; work += (double)t * C * per_task;        // the C chunks of a row run one after the other on one warp
+            }
+            if (!fits || tasks == 0) continue;
+            const long long per_cta = (tasks + ncta - 1) / ncta;
             const long long chain = (per_cta + nwarps - 1) / nwarps;
-            // rounds of 32 lanes per task: Q4_K lanes take a whole super-block each (a round is four times as long), Q6_K lanes
-            // a quarter of one
-            const int blocks = C > 1 ? cb : R * nb;
-            const double rounds = a.seg[0].type == T_Q4K ? 4.0 * ((blocks + 31) / 32) : (double)((blocks * 4 + 31) / 32);
-            const double cost = (double)chain * C * (rounds + 0.5) * (a.out_mode == 3 ? 2 : 1);
+            const double cost = (double)chain * (work / (double)tasks) * (a.out_mode == 3 ? 2 : 1);
             if (cost < best_cost - 1e-9) { best_cost = cost; best_w = nwarps; best_R = R; best_C = C; }
         }
     }
@@ -930,7 +1046,9 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
             d.W = (const uint8_t*)a.seg[i].W; d.y = a.seg[i].y; d.M = a.seg[i].M; d.type = a.seg[i].type;
             d.rb = nb * block_bytes(d.type);
             d.U = U;
-            d.R = R; d.trc = nwarps * R;
+            const Lane m = lane_map(d.type, best_C > 1 ? 1 : R, best_C > 1 ? p.chunk_blocks : nb);
+            d.lw = (uint8_t)m.lw; d.lg = (uint8_t)(best_C > 1 ? 1 : m.lg); d.rl = (uint8_t)m.rl; d.pad_ = 0;
+            d.R = best_C > 1 ? 1 : m.rows;
             const int need = (((best_C > 1 ? p.chunk_blocks * block_bytes(d.type) : d.R * d.rb) + 16 + 127) / 128) * 128;
             slot = need > slot ? need : slot;
             const long long groups = (d.M + d.R - 1) / d.R;
@@ -942,15 +1060,20 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
         p.nslots = ring / slot;
         if (p.nslots > GV_MAXSLOT) p.nslots = GV_MAXSLOT;
         p.nwarps = nwarps;
+        static const int early_env = [] { const char* v = getenv("JLLM_B200_GEMV_EARLY"); return v ? atoi(v) : 0; }();
+        // two CTAs of this kernel per SM start when the producer is about to finish: half a ring first, the rest behind the
+        // activation loads; one CTA per SM starts long before that and fills its whole ring at once
+        p.early_slots = early_env > 0 ? (early_env < p.nslots ? early_env : p.nslots) : (two_per_sm && two ? (p.nslots + 1) / 2 : p.nslots);
         smem_bytes = (size_t)p.off_slots + (size_t)nwarps * p.nslots * slot;
         if (p.paired_rows) groups_total /= 2;
         grid = ncta;                                           // every SM streams its share, however few groups that is
         if (grid > groups_total) grid = (int)groups_total;
         if (grid < 1) grid = 1;
+        gv_set_split(p, grid);
         static const bool verbose = getenv("JLLM_B200_GEMV_DEBUG") != nullptr;
         if (verbose)
-            fprintf(stderr, "[gemv] K=%d nseg=%d M0=%d type0=%d xmode=%d out=%d: grid %d x %d warps, R=%d chunks=%d x %d blocks, %d slots of %d B, smem %zu\n",
-                    K, a.nseg, a.seg[0].M, a.seg[0].type, a.xmode, a.out_mode, grid, nwarps, R, p.nchunk, p.chunk_blocks, p.nslots, p.slot_bytes, smem_bytes);
+            fprintf(stderr, "[gemv] K=%d nseg=%d M0=%d type0=%d xmode=%d out=%d: grid %d x %d warps, depth %d (rows/task %d, lanes %d x %d), chunks=%d x %d blocks, %d slots of %d B, smem %zu\n",
+                    K, a.nseg, a.seg[0].M, a.seg[0].type, a.xmode, a.out_mode, grid, nwarps, R, p.seg[0].R, p.seg[0].lg, p.seg[0].lw, p.nchunk, p.chunk_blocks, p.nslots, p.slot_bytes, smem_bytes);
         return JB_OK;
     }
 }
@@ -964,28 +1087,29 @@ int launch_gemv(const GemvArgs& a0, cudaStream_t st) {
     g_tp_wait_set = g_tp_push_set = false;
     GvParams p;
     size_t smem_bytes = 0; int grid = 0; bool empty = false;
-    // diagnostic switch: JLLM_B200_GEMV_WHOLE=1 gives every GEMV a whole SM per CTA, =0 half an SM; unset: the default policy
-    static const int force = [] { const char* v = getenv("JLLM_B200_GEMV_WHOLE"); return v ? (v[0] == '1' ? 1 : 0) : -1; }();
-    const bool whole = force == 1;
-    const int rc = whole ? gv_configure(a, p, GV_CHAINWARPS, cx->max_smem_optin - 2048, false, smem_bytes, grid, empty)
-                         : gv_configure(a, p, GV_MAXWARPS, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
+    const int cap = GV_MAXWARPS;
+    const int rc = gv_configure(a, p, cap, cx->gemv_smem_budget, true, smem_bytes, grid, empty);
     if (rc || empty) return rc;
     p.trace = g_trace; g_trace = nullptr;
     static const bool nocompute = getenv("JLLM_B200_GEMV_NOCOMPUTE") != nullptr;
     p.trace_nocompute = (p.trace && nocompute) ? 1 : 0;
     const bool dbg = a.dbg_dots || p.trace;
-    void (*kern)(GvParams);
-    if (whole) kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true, true> : gemv_stream_kernel<0, true, true>)
-                          : (a.xmode ? gemv_stream_kernel<1, false, true> : gemv_stream_kernel<0, false, true>);
-    else       kern = dbg ? (a.xmode ? gemv_stream_kernel<1, true, false> : gemv_stream_kernel<0, true, false>)
-                          : (a.xmode ? gemv_stream_kernel<1, false, false> : gemv_stream_kernel<0, false, false>);
-    const int ki = (a.xmode ? 1 : 0) + (dbg ? 2 : 0) + (whole ? 4 : 0);
+    const bool tp = a.tp_wait || a.tp_push || a.residual_pk;
+    if (dbg && tp) return set_error(JB_ERR_ARG, "gemv: no debug output on a tensor-parallel launch");
+    // ONE kernel function serves every single-GPU GEMV of a decode step (both activation formats, both weight types): the
+    // launches of a layer alternate between as few functions as possible, and their code stays in the instruction cache.
+    void (*kern)(GvParams) = dbg ? gemv_stream_kernel<true, false> : (tp ? gemv_stream_kernel<false, true> : gemv_stream_kernel<false, false>);
+    const int ki = dbg ? 1 : (tp ? 2 : 0);
     if (!cx->gemv_attr[ki]) {
-        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, whole ? cx->max_smem_optin - 2048 : cx->gemv_smem_budget));
+        JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cx->gemv_smem_budget));
         JB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         cx->gemv_attr[ki] = true;
     }
-    JB_CUDA(launch_k(kern, dim3(grid), dim3(p.nwarps * 32), smem_bytes, st, pdl_enabled(), p));
+    // warps beyond p.nwarps only help to stage the activation vector (eight elements per thread and round) and leave
+    int block_warps = (a.K / 8 + 31) / 32;
+    block_warps = block_warps > cap ? cap : block_warps;
+    block_warps = block_warps < p.nwarps ? p.nwarps : block_warps;
+    JB_CUDA(launch_k(kern, dim3(grid), dim3(block_warps * 32), smem_bytes, st, pdl_enabled(), p));
     count_launch();
     return JB_OK;
 }
@@ -1008,7 +1132,8 @@ int launch_gemv_chain(const GemvArgs* args, int n, unsigned int* bar, cudaStream
         const int rc = gv_configure(args[i], c.ph[i], GV_CHAINWARPS, cx->max_smem_optin - 2048, false, smem_bytes, grid, empty);
         if (rc) return rc;
         if (empty) return set_error(JB_ERR_ARG, "gemv chain: empty phase");
-        c.ph[i].chained = 1;
+        c.ph[i].chained = 1; c.ph[i].early_slots = c.ph[i].nslots;
+        gv_set_split(c.ph[i], cx->sm_count);   // the chain's grid
         smem_max = smem_bytes > smem_max ? smem_bytes : smem_max;
     }
     if (!cx->gemv_chain_attr) {

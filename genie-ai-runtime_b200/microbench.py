@@ -7,6 +7,7 @@
     python genie-ai-runtime_b200/microbench.py f32   --type 14 --M 151936 --K 2560          # logits
     python genie-ai-runtime_b200/microbench.py attn  --L 8192 [--batch 64]                  # config 2
     python genie-ai-runtime_b200/microbench.py mmq   --type 12 --M 9728 --K 2560 --N 512    # config 3
+    python genie-ai-runtime_b200/microbench.py layer [--trace]                              # the four GEMVs of a decoder layer, chained
 
 Weights are random block images; `--copies` distinct copies (default: enough for 3x the 126 MB L2) are used in
 rotation so that every launch streams from HBM.  Prints one JSON line with the average launch time and the
@@ -40,7 +41,7 @@ def blocks(ggml_type, rows, K, dev, gen):
 
 def parser():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "pattn", "mmq"])
+    ap.add_argument("kind", choices=["gemv", "pair", "triple", "add", "f32", "attn", "pattn", "mmq", "layer"])
     ap.add_argument("--type", type=int, default=12)
     ap.add_argument("--M", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
@@ -56,6 +57,8 @@ def parser():
     ap.add_argument("--norm", action="store_true", help="pair/triple: RMSNorm fused in front of the activation quantiser")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python every iteration instead of replaying a CUDA graph")
+    ap.add_argument("--interleave", type=int, default=0, help="layer: this many launches of a tiny unrelated kernel between the GEMVs "
+                    "(how much a change of kernel costs the next GEMV)")
     ap.add_argument("--trace", action="store_true", help="GEMV kinds: record per-CTA time stamps of every launch (diagnostic kernel "
                     "instantiation) and print where the time of a launch goes")
     return ap
@@ -107,6 +110,33 @@ def measure(jb, argv):
                 calls.append(lambda W=W: jb.gemm_quant_batched(ys[0], W[0], t, x, M, a.N, K, st))
         nbytes = wbytes + N * K * 2 + sum(N * m * ys[0].element_size() for m in Ms)
         shape = dict(M=Ms, K=K, types=ts, N=N, copies=copies)
+    elif a.kind == "layer":
+        # The four weight products of one decoder layer of the 4B shape, each reading what the one before wrote (Q/K/V with the
+        # RMSNorm in front -> Wo + residual -> gate/up with RMSNorm and SwiGLU -> W_down + residual), without the attention
+        # between them: how the GEMV launches behave next to one another, which a single kernel repeated does not show.
+        H, QD, KVD, FF = 2560, 4096, 1024, 9728
+        per = (QD + 2 * KVD) * 10 * 144 + KVD * 10 * (210 - 144) + H * 16 * 144 + 2 * FF * 10 * 144 + H * 38 * 210
+        copies = a.copies or max(2, int(np.ceil(3 * L2_BYTES / per)))
+        h = torch.randn(H, device=dev, generator=gen).to(torch.float16)
+        h2 = torch.zeros(H, dtype=torch.float16, device=dev)
+        q = torch.zeros(QD, dtype=torch.float16, device=dev); kk = torch.zeros(KVD, dtype=torch.float16, device=dev); vv = torch.zeros(KVD, dtype=torch.float16, device=dev)
+        act = torch.zeros(FF, dtype=torch.float16, device=dev)
+        nw = torch.ones(H, dtype=torch.float32, device=dev)
+        layer_launches = []
+        for _ in range(copies):
+            Wq, Wk, Wv = blocks(12, QD, H, dev, gen), blocks(12, KVD, H, dev, gen), blocks(14, KVD, H, dev, gen)
+            Wo, Wg, Wu, Wd = blocks(12, H, QD, dev, gen), blocks(12, FF, H, dev, gen), blocks(12, FF, H, dev, gen), blocks(14, H, FF, dev, gen)
+            layer_launches.append([
+                lambda Wq=Wq, Wk=Wk, Wv=Wv: jb.norm_gemv_quant_triple(q, Wq, 12, QD, kk, Wk, 12, KVD, vv, Wv, 14, KVD, h, nw, True, 1e-6, H, st),
+                lambda Wo=Wo: jb.gemv_quant_add(h2, Wo, 12, q, h, H, QD, st),
+                lambda Wg=Wg, Wu=Wu: jb.norm_gemv_pair_swiglu(act, Wg, Wu, 12, FF, h2, nw, True, 1e-6, H, st),
+                lambda Wd=Wd: jb.gemv_quant_add(h, Wd, 14, act, h2, H, FF, st)])
+        tiny_buf = torch.ones(256, dtype=torch.float16, device=dev)
+        tiny = lambda: [jb.vec_scale(tiny_buf, 256, 1.0, st) for _ in range(a.interleave)]
+        for L in layer_launches:
+            calls.append(lambda L=L: [(f(), tiny()) for f in L])
+        nbytes = per
+        shape = dict(layer="qkv(norm) -> wo+res -> gate/up(norm, swiglu) -> down+res", copies=copies)
     elif a.kind == "pattn":
         # causal prefill attention of N query tokens from position 0 over an INT8 cache (the cache fits the L2: a prompt's K/V
         # were written just before); algorithmic bytes = K/V/scales of the N positions once + q in + out
@@ -156,9 +186,15 @@ def measure(jb, argv):
         calls[0]()
         torch.cuda.synchronize()
         NCTA, NST = 2 * 148, 16
-        trace = torch.zeros((a.iters, NCTA, NST), dtype=torch.int64, device=dev)
+        per_call = 4 if a.kind == "layer" else 1
+        trace = torch.zeros((a.iters * per_call, NCTA, NST), dtype=torch.int64, device=dev)
         plain = calls
         def traced(i):
+            if a.kind == "layer":
+                for k, f in enumerate(layer_launches[i % len(layer_launches)]):
+                    jb.lib.jllm_b200_debug_gemv_trace(C.c_void_p(trace[4 * i + k].data_ptr()))
+                    f()
+                return
             jb.lib.jllm_b200_debug_gemv_trace(C.c_void_p(trace[i].data_ptr()))
             plain[i % len(plain)]()
         calls = [lambda i=i: traced(i) for i in range(a.iters)]
@@ -188,8 +224,13 @@ def measure(jb, argv):
     us = e0.elapsed_time(e1) * 1e3 / a.iters
     if a.trace:
         t = trace.cpu().numpy().astype(np.int64)              # [launch][cta][stamp], ns
+        names = ["entry_first", "entry_last", "copies_issued_last", "producer_done_first", "producer_done_last", "staged_last",
+                 "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done",
+                 "t0_landed", "t0_done", "t1_landed", "t1_done", "t2_landed", "t2_done", "t3_landed", "t3_done"]
         rows = []
-        for i in range(2, a.iters):
+        per_call = 4 if a.kind == "layer" else 1
+        by_kind = [[] for _ in range(per_call)]
+        for i in range(2 * per_call, a.iters * per_call):
             live = t[i][:, 0] > 0
             cur, prev = t[i][live], t[i - 1][t[i - 1][:, 0] > 0]
             base = prev[:, 6].max()                             # the previous launch's last warp finishes
@@ -198,12 +239,12 @@ def measure(jb, argv):
             for k in range(8, 16):                              # warp 0's tasks: median over CTAs
                 ok = cur[:, k] > 0
                 rows[-1].append(np.median(cur[ok, k]) - base if ok.any() else 0)
-        r = np.median(np.array(rows, np.float64), axis=0) / 1e3
-        names = ["entry_first", "entry_last", "copies_issued_last", "producer_done_first", "producer_done_last", "staged_last",
-                 "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done",
-                 "t0_landed", "t0_done", "t1_landed", "t1_done", "t2_landed", "t2_done", "t3_landed", "t3_done"]
-        print(json.dumps({"trace_us_after_previous_launch_finished(median)": {n: round(float(v), 2) for n, v in zip(names, r)},
-                          "ctas": int((t[2][:, 0] > 0).sum())}))
+            by_kind[i % per_call].append(rows[-1])
+        for k, rk in enumerate(by_kind):
+            r = np.median(np.array(rk, np.float64), axis=0) / 1e3
+            print(json.dumps({"launch": ["qkv", "wo", "gate_up", "down"][k] if per_call == 4 else a.kind,
+                              "trace_us_after_previous_launch_finished(median)": {n: round(float(v), 2) for n, v in zip(names, r)},
+                              "ctas": int((t[2 * per_call + k][:, 0] > 0).sum())}))
     extra = {"TFLOPs": 2.0 * a.M * a.N * a.K / us / 1e6} if a.kind == "mmq" else ({"TFLOPs": shape["flops"] / us / 1e6} if a.kind == "pattn" else {})
     if a.no_pdl:
         jb.lib.jllm_b200_set_pdl(1)
