@@ -401,7 +401,8 @@ __global__ void qkv_prep_kernel(const QkvPrepArgs a, const __grid_constant__ Rop
         __syncwarp();
         for (int pr = lane; a.do_rope && pr < h2; pr += 32) {
             const float ang = __fmul_rn((float)pos, fr.f[pr]);
-            const float c = cosf(ang), s = sinf(ang);
+            float c, s;
+            sincosf(ang, &s, &c);          // one range reduction for both (and half the code of cosf + sinf)
             const int i0 = a.neox ? pr : 2 * pr, i1 = a.neox ? pr + h2 : 2 * pr + 1;
             const float v0 = buf[i0], v1 = buf[i1];
             const float r0 = __half2float(__float2half_rn(__fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, s))));

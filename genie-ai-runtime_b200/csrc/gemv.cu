@@ -995,7 +995,8 @@ static int gv_configure(const GemvArgs& a, GvParams& p, int max_warps, int budge
             const int passes = (blocks + 31) / 32;
             m.lw = (blocks + passes - 1) / passes;
             m.lg = 32 / m.lw;
-            m.rl = depth >= 3 && m.lw >= 3 ? 3 : 1;  // columns are instantiated 1 and 3 rows deep (code size)
+            static const int q4_env = [] { const char* v = getenv("JLLM_B200_GEMV_Q4DEPTH"); return v ? atoi(v) : 0; }();
+            m.rl = (q4_env ? q4_env : depth) >= 3 && m.lw >= 3 ? 3 : 1;  // columns are instantiated 1 and 3 rows deep (code size)
             m.rows = m.lg * m.rl;
         }
         return m;
