@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libjllm_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-SOURCES = ["api.cu", "gemv.cu", "elementwise.cu", "attention.cu", "attention_tma.cu", "attention_prefill.cu", "attention_noalloc.cu", "mmq.cu", "mmq_tc.cu", "tp.cu", "decoder.cu", "batch_decoder.cu", "pools.cpp"]
+SOURCES = ["api.cu", "gemv.cu", "elementwise.cu", "attention.cu", "attention_tma.cu", "attention_prefill.cu", "attention_noalloc.cu", "mmq.cu", "mmq_tc.cu", "mmq_stream.cu", "tp.cu", "decoder.cu", "batch_decoder.cu", "pools.cpp"]
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr"]
 

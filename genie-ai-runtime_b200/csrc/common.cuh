@@ -46,6 +46,7 @@ struct DeviceCtx {
     void*  mmq_act = nullptr; size_t mmq_act_bytes = 0;
     RopeTable rope[8]; int n_rope = 0;
     bool gemv_attr[12] = {};
+    bool mms_attr[8] = {};
     bool gemv_chain_attr = false;
     bool attn_tma_attr[6] = { false, false, false, false, false, false };
     bool attn_prefill_attr[3] = { false, false, false };

@@ -110,6 +110,12 @@ int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N
     if (type == T_Q4K && ((uintptr_t)W & 3)) return set_error(JB_ERR_PTR, "batched gemm: Q4_K weights must be 4-byte aligned");
     // JLLM_B200_MMQ=cuda keeps the CUDA-core kernel (the one that can also export the integer accumulators)
     static const bool tc_off = [] { const char* e = getenv("JLLM_B200_MMQ"); return e && !strcmp(e, "cuda"); }();
+    if (!dbg && !tc_off && mmq_stream_applies(W, type, M, N, K)) {
+        const size_t need_s = mmq_stream_scratch_bytes(type, M, N, K);
+        void* sc = mmq_scratch(need_s, !capturing(st));
+        if (!sc) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_s);
+        return launch_mmq_stream(y, W, type, x, sc, M, N, K, st);
+    }
     if (!dbg && !tc_off && mmq_tc_applies(W, type, M, N, K)) {
         const size_t need_tc = mmq_tc_scratch_bytes(type, M, N, K);
         __half* xq = (__half*)mmq_scratch(need_tc, !capturing(st));

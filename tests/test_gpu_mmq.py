@@ -57,6 +57,24 @@ def test_reference_golden_vectors(golden_dir, name, t):
     assert np.max(np.abs(y.float().cpu().numpy() - ref)) <= 0.5
 
 
+@pytest.mark.parametrize("t,M,N,K", [(12, 9728, 64, 2560), (14, 2560, 64, 9728), (12, 4096, 8, 2560), (14, 1024, 24, 2560), (12, 2560, 2, 4096),
+                                      (14, 151, 57, 768)])
+def test_few_tokens_stream_the_weights_once(t, M, N, K):
+    """2..64 tokens go through the weight-streaming kernel (csrc/mmq_stream.cu): the decoder's own shapes at 64 streams, every
+    token-tile count, ragged row and token edges, and K ranges split over CTAs (few rows, long K)."""
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1007 + M + N))
+    W = orc.gen_weight(rng, t, M, K)
+    X = orc.gen_act(rng, N * K)
+    y = torch.full((N * M,), float("nan"), dtype=torch.float16, device="cuda")
+    jb.gemm_quant_batched(y, dev(W), t, dev(X), M, N, K)
+    want = orc.entry_gemm_quant_batched(W, t, X, M, N, K).astype(np.float32).reshape(-1)
+    ok, md = close_gemm(y.float().cpu().numpy(), want, N, M)
+    assert ok, md
+    assert jb.device_status() == 0
+
+
 @pytest.mark.parametrize("t", [12, 14])
 def test_tensor_core_and_cuda_core_paths_agree(t):
     """The tcgen05 kernel and the CUDA-core kernel (the one that exports the integer accumulators) compute the same
