@@ -4,32 +4,37 @@
 // :1245-1616 dispatch).  The GGUF super-block layout is read unchanged from HBM.
 //
 // Shape of the kernel
-//   * grid = one CTA per SM with 4 to 20 warps; every CTA owns one contiguous range of row groups of the (up to
-//     three) weight matrices, split evenly by bytes, so all SMs stream the same amount.  Warps per CTA and rows per
-//     group are chosen per launch so that the longest chain of work any warp runs is shortest (gv_configure).
+//   * ONE kernel function serves every GEMV entry point, both weight types and both activation formats: the launches of
+//     a decode step alternate between as few functions as possible and the code stays small (70 KB), because every launch
+//     fetches whatever the instruction cache has lost of it behind its own weight stream.
+//   * grid = one or two CTAs per SM, half an SM each (8 warps at 128 registers, 111 KB of shared memory); every CTA owns
+//     one contiguous range of row groups of the (up to three) weight matrices, split evenly by bytes.  Consuming warps,
+//     rows per task and K chunks of long rows are chosen per launch so that the longest chain of work any warp runs is
+//     shortest (gv_configure); further warps of the CTA only help to stage the activations.
 //   * weights travel HBM -> shared memory with 1-D TMA bulk copies (cp.async.bulk + mbarrier complete_tx); every
 //     warp runs its own ring of slots with one mbarrier per slot, no CTA-wide barrier in the loop; Q6_K rows
 //     (210-byte blocks, 2-byte aligned) are copied as the enclosing 16-byte aligned span and re-aligned with funnel
-//     shifts when read from shared memory.
-//   * the activation vector is quantised once per SM by all threads of the CTA (four threads per 32-element group)
-//     into shared memory (q8_1 codes, or 16-bit fixed point for the entry points whose reference path keeps fp16
-//     activations), optionally after a fused RMSNorm, laid out so that the 16-byte runs the lanes read are
-//     bank-conflict free.
-//   * each lane takes one 32-byte run of quants per step, dots it with dp4a, and a warp reduces the rows it owns
-//     with shuffles; outputs are deterministic.
-//   * launched with programmatic dependent launch: weight copies are issued before griddepcontrol.wait.
-//   * the same body runs as one phase of an optional chained launch (gemv_chain_kernel), and carries the
-//     tensor-parallel hooks: activations polled as {value, epoch} packets, results pushed as packets to every rank.
+//     shifts when read from shared memory.  Half of every ring is requested before griddepcontrol.wait, the other half
+//     right after the loads of the activation vector (requests leave an SM in order).
+//   * the activation vector is quantised once per CTA by all its threads (four threads per 32-element group) into shared
+//     memory (q8_1 codes, or 16-bit fixed point for the entry points whose reference path keeps fp16 activations),
+//     optionally after a fused RMSNorm, laid out so that the 16-byte runs the lanes read are bank-conflict free.
+//   * Q4_K: a lane owns one super-block column of three consecutive rows (the activations of the column are read once for
+//     the three rows, which are independent instruction streams); Q6_K: a lane owns 64 weights of one row; integer dots
+//     with dp4a, rows reduced with shuffles; outputs are deterministic.
+//   * launched with programmatic dependent launch (launch_dependents first thing).
+//   * the same body runs as one phase of an optional chained launch (gemv_chain_kernel), and an instantiation of its own
+//     carries the tensor-parallel hooks: activations polled as {value, epoch} packets, results pushed to every rank.
 #include "gemv.cuh"
 #include <cstdio>
 #include <cstdlib>
 
 namespace jb {
 
-// Stream kernel: a CTA takes HALF an SM (at most 12 warps at 85 registers, half the shared memory), and a launch puts
-// one CTA on every SM.  The other half is where the CTAs of the NEXT kernel in the stream become resident as soon as
-// this one has issued griddepcontrol.launch_dependents: they set up their barriers and start the bulk copies of their
-// first row groups while this kernel is still computing, so HBM keeps streaming across kernel boundaries.
+// Stream kernel: a CTA takes HALF an SM.  A product whose share per SM fits one ring launches one CTA per SM, and the other
+// half is where the CTAs of the NEXT kernel in the stream become resident as soon as this one has issued
+// griddepcontrol.launch_dependents: they set up their barriers and start their bulk copies while this kernel is still
+// computing.  A larger product launches two CTAs per SM.
 constexpr int GV_MAXWARPS = 8;                 // 8 warps at 128 registers (rows-deep columns keep many values live)
 constexpr int GV_CHAINWARPS = 16;              // the chain kernel keeps a whole SM per CTA (its phases overlap inside one launch)
 constexpr int GV_CHAINTHREADS = GV_CHAINWARPS * 32;
