@@ -775,11 +775,13 @@ __global__ void __launch_bounds__(GV_MAXWARPS * 32, 2) gemv_stream_kernel(const 
     pdl_launch();                // the next kernel's CTAs may take the free half of every SM now; they wait for our completion
                                  // before they touch our outputs
     const GvRange rg = gv_range(p);
+    if (DBG && p.trace && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * GV_NTRACE + 7] = global_ns() + (rg.gf[0] == -7);
     if ((threadIdx.x & 31) == 0) {
         for (int s = 0; s < p.nslots; ++s) mbar_init(&full[threadIdx.x >> 5][s], 1);
         fence_mbar_init();
     }
     __syncwarp();
+    if (DBG && p.trace && threadIdx.x == 0) gv_stamp(p, 15);
     gv_prefetch(p, rg, smem, full, threadIdx.x >> 5, threadIdx.x & 31, false, 0, p.early_slots);   // weights do not depend on the previous kernel
     float wpre[GV_PRE][8];
     int npre = 0;

@@ -226,7 +226,8 @@ def measure(jb, argv):
         t = trace.cpu().numpy().astype(np.int64)              # [launch][cta][stamp], ns
         names = ["entry_first", "entry_last", "copies_issued_last", "producer_done_first", "producer_done_last", "staged_last",
                  "first_rows_landed_first", "first_rows_landed_last", "warp0_done_last", "all_done",
-                 "t0_landed", "t0_done", "t1_landed", "t1_done", "t2_landed", "t2_done", "t3_landed", "t3_done"]
+                 "t0_landed", "t0_done", "t1_landed", "t1_done", "x_loaded", "norm_known", "quantised", "barriers_ready",
+                 "range_known", "entry_median"]
         rows = []
         per_call = 4 if a.kind == "layer" else 1
         by_kind = [[] for _ in range(per_call)]
@@ -236,9 +237,10 @@ def measure(jb, argv):
             base = prev[:, 6].max()                             # the previous launch's last warp finishes
             rows.append([cur[:, 0].min() - base, cur[:, 0].max() - base, cur[:, 1].max() - base, cur[:, 2].min() - base, cur[:, 2].max() - base,
                          cur[:, 3].max() - base, cur[:, 4].min() - base, cur[:, 4].max() - base, cur[:, 5].max() - base, cur[:, 6].max() - base])
-            for k in range(8, 16):                              # warp 0's tasks: median over CTAs
+            for k in list(range(8, 16)) + [7]:                  # warp 0's tasks and staging phases: median over CTAs
                 ok = cur[:, k] > 0
                 rows[-1].append(np.median(cur[ok, k]) - base if ok.any() else 0)
+            rows[-1].append(np.median(cur[:, 0]) - base)       # median CTA entry
             by_kind[i % per_call].append(rows[-1])
         for k, rk in enumerate(by_kind):
             r = np.median(np.array(rk, np.float64), axis=0) / 1e3
