@@ -17,6 +17,7 @@
 // Tensor maps describe this GPU's own memory only and no copy uses cluster multicast.
 #include "attention.cuh"
 #include <cfloat>
+#include <cstdlib>
 #include <cstring>
 #include <cuda.h>
 
@@ -29,8 +30,10 @@ constexpr int AM_HD     = 128;
 constexpr int AM_TILE_BYTES  = AM_TILE * AM_HD;       // one K (or V) tile: 4 KB, rows of 128 bytes, 128-byte swizzle
 constexpr int AM_STAGE_BYTES = 2 * AM_TILE_BYTES;
 constexpr int AM_RING_BYTES  = AM_WARPS * AM_STAGES * AM_STAGE_BYTES;
-constexpr int AM_SMEM = AM_RING_BYTES + AM_WARPS * 256 + 1024 + 64 + 1024;   // + PV weight bytes, query planes, scales, alignment slack
+constexpr int AM_SCALE_BYTES = AM_WARPS * AM_STAGES * 2 * AM_TILE * 4;           // per warp and stage: K and V scales of the tile's 32 keys
+constexpr int AM_SMEM = AM_RING_BYTES + AM_WARPS * 256 + 1024 + 64 + AM_SCALE_BYTES + 1024;   // + PV weight bytes, query planes, scales, alignment slack
 
+constexpr int AM_PREC = AM_HD + 4;                    // floats of a slice's partial record: m, l, two pad words, acc[128] (16-byte aligned)
 constexpr int AM_BATCH_SEQS = 14;                     // sequences per launch of a ragged batch: 28 tensor maps fit the 4 KB of kernel parameters
 
 // Tensor maps travel as kernel parameters (constant bank).  Maps read from global memory work but were measured at several
@@ -45,6 +48,7 @@ struct AmArgs {
     int n_heads, n_kv, seq_len; const int* d_pos;
     float scale; int n_splits;
     float* part; unsigned int* tickets; int* status;
+    int nocompute;                           // diagnostic: fetch the tiles, skip the arithmetic
 };
 
 __device__ __forceinline__ void am_mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -86,10 +90,11 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
     uint8_t* wsm = smem + AM_RING_BYTES + warp * 256;                            // [8 columns][32 keys] int8
     int8_t*  qpl = reinterpret_cast<int8_t*>(smem + AM_RING_BYTES + AM_WARPS * 256);        // [G][2 planes][128]
     float*   qsc = reinterpret_cast<float*>(smem + AM_RING_BYTES + AM_WARPS * 256 + 1024);  // dq per head
+    float*   ssm = reinterpret_cast<float*>(smem + AM_RING_BYTES + AM_WARPS * 256 + 1024 + 64) + warp * AM_STAGES * 2 * AM_TILE;   // [stage][K | V][32]
 
     const CUtensorMap* km = &mp.m[2 * zl];
     const CUtensorMap* vm = &mp.m[2 * zl + 1];
-    if (lane == 0) { for (int s = 0; s < AM_STAGES; ++s) mbar_init(&full[warp][s], 1); }
+    if (lane == 0) { for (int s = 0; s < AM_STAGES; ++s) mbar_init(&full[warp][s], 1 + 32); }      // lane 0's byte count + every lane's scale copies
     if (tid == 0) {
         fence_mbar_init();
         asm volatile("prefetch.tensormap [%0];" ::"l"(km) : "memory");
@@ -108,28 +113,31 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
     const int ntiles_cta = kv1 > kv0 ? (kv1 - kv0 + AM_TILE - 1) / AM_TILE : 0;
     const int my_tiles = ntiles_cta > warp ? (ntiles_cta - warp + AM_WARPS - 1) / AM_WARPS : 0;
 
-    auto issue = [&](int it) {      // tile `it` of this warp -> stage it % AM_STAGES (lane 0)
+    // Tile `it` of this warp -> stage it % AM_STAGES; called by the whole warp.  Lane 0 issues the two tensor copies; lane l
+    // copies the K and V scale of key t0 + l (the 32 floats of a kv head sit 32 bytes apart) with 4-byte cp.async into the
+    // stage's scale slots and makes them count on the same mbarrier (cp.async.mbarrier.arrive.noinc): the scales travel with
+    // their tile, as far ahead as the tile itself, and no warp ever waits for a plain load behind the SM's queue of tile
+    // requests (with per-lane loads one tile ahead, `long_scoreboard` was the top stall: 3.1 warps per issued instruction).
+    auto issue = [&](int it) {
         const int t0 = kv0 + (warp + it * AM_WARPS) * AM_TILE;
         const uint32_t st = wring + (uint32_t)(it % AM_STAGES) * AM_STAGE_BYTES;
         uint64_t* bar = &full[warp][it % AM_STAGES];
-        mbar_expect_tx(bar, (uint32_t)AM_STAGE_BYTES);                           // rows past the tensor's end are zero-filled and counted
-        am_tma_2d(st, km, kvh * AM_HD, t0, bar);
-        am_tma_2d(st + AM_TILE_BYTES, vm, kvh * AM_HD, t0, bar);
+        float* sd = ssm + (it % AM_STAGES) * 2 * AM_TILE + lane;
+        const int key = t0 + lane;
+        if (key < kv1) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(sd)), "l"(ksp + (size_t)key * a.n_kv + kvh) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(sd + AM_TILE)), "l"(vsp + (size_t)key * a.n_kv + kvh) : "memory");
+        } else {
+            sd[0] = 0.f; sd[AM_TILE] = 0.f;
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+        if (lane == 0) {
+            mbar_expect_tx(bar, (uint32_t)AM_STAGE_BYTES);                       // rows past the tensor's end are zero-filled and counted
+            am_tma_2d(st, km, kvh * AM_HD, t0, bar);
+            am_tma_2d(st + AM_TILE_BYTES, vm, kvh * AM_HD, t0, bar);
+        }
     };
-    if (lane == 0)
-        for (int it = 0; it < AM_STAGES && it < my_tiles; ++it) issue(it);
-
-    // Scales of a tile: lane l fetches those of key t0 + l (ONE load per array per tile; the 32 floats of a kv head sit 32 bytes
-    // apart, so per-key loads from every lane would cost four times the sector requests); the lanes then pick the scales of
-    // their four keys (g, g+8, g+16, g+24) with shuffles.
-    auto load_scales = [&](int it, float& kl, float& vl) {
-        const int key = kv0 + (warp + it * AM_WARPS) * AM_TILE + lane;
-        const bool ok = it < my_tiles && key < kv1;
-        kl = ok ? __ldcg(ksp + (size_t)key * a.n_kv + kvh) : 0.f;
-        vl = ok ? __ldcg(vsp + (size_t)key * a.n_kv + kvh) : 0.f;
-    };
-    float nks, nvs;
-    load_scales(0, nks, nvs);
+    for (int it = 0; it < AM_STAGES && it < my_tiles; ++it) issue(it);
 
     // ── query planes: per head 16-bit fixed point, split into a high and a (signed) low byte ──
     if (warp < G) {
@@ -172,14 +180,18 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
     for (int it = 0; it < my_tiles; ++it) {
         const int t0 = kv0 + (warp + it * AM_WARPS) * AM_TILE;
         const uint32_t Kt = wring + (uint32_t)(it % AM_STAGES) * AM_STAGE_BYTES, Vt = Kt + AM_TILE_BYTES;
-        float ksv[4], vsv[4];
-        #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            ksv[r] = __shfl_sync(0xFFFFFFFFu, nks, g + 8 * r);
-            vsv[r] = __shfl_sync(0xFFFFFFFFu, nvs, g + 8 * r);
-        }
-        load_scales(it + 1, nks, nvs);                                          // in flight while this tile is multiplied
         if (!timed_out && !mbar_wait_bounded(&full[warp][it % AM_STAGES], (it / AM_STAGES) & 1)) timed_out = true;
+        if (a.nocompute) {                      // diagnostic: how fast do the tiles alone arrive?
+            __syncwarp();
+            if (it + AM_STAGES < my_tiles) { if (lane == 0) fence_proxy_async(); issue(it + AM_STAGES); }
+            continue;
+        }
+        float ksv[4], vsv[4];
+        {
+            const float* sd = ssm + (it % AM_STAGES) * 2 * AM_TILE;
+            #pragma unroll
+            for (int r = 0; r < 4; ++r) { ksv[r] = sd[g + 8 * r]; vsv[r] = sd[AM_TILE + g + 8 * r]; }
+        }
 
         // ── S = K Q^T: rows = keys, columns = (head, plane) ──
         float sc[4];
@@ -268,7 +280,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
             }
         }
         __syncwarp();
-        if (lane == 0 && it + AM_STAGES < my_tiles) { fence_proxy_async(); issue(it + AM_STAGES); }
+        if (it + AM_STAGES < my_tiles) { if (lane == 0) fence_proxy_async(); issue(it + AM_STAGES); }
     }
     if (timed_out && lane == 0) atomicExch(a.status, JB_ERR_TIMEOUT);
 
@@ -306,9 +318,9 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
         if (a.n_splits == 1) {
             a.out[((size_t)z * a.n_heads + head) * AM_HD + d] = __float2half_rn(L > 0.f ? acc / L : 0.f);
         } else {
-            float* pb = a.part + (((size_t)z * a.n_heads + head) * a.n_splits + split) * (AM_HD + 2);
+            float* pb = a.part + (((size_t)z * a.n_heads + head) * a.n_splits + split) * AM_PREC;
             if (d == 0) { pb[0] = ntiles_cta > 0 ? M : -FLT_MAX; pb[1] = L; }
-            pb[2 + d] = acc;
+            pb[4 + d] = acc;
         }
     }
     if (a.n_splits == 1) return;
@@ -326,24 +338,37 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 3) attn_tma_kernel(const __grid
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // every slice's (m, l) by one parallel load, the weights e_s = e^{m_s - M} once per head, then each thread sums its
-    // dimension over the slices with independent loads (n_splits <= 64 < 128 threads)
-    float* mg_m = sm_m; float* mg_l = sm_m + 64; float* mg_e = sm_m + 128;
-    for (int h = 0; h < G; ++h) {
-        const int head = kvh * G + h;
-        const float* pb = a.part + ((size_t)z * a.n_heads + head) * a.n_splits * (AM_HD + 2);
-        __syncthreads();
-        if (tid < a.n_splits) { mg_m[tid] = __ldcg(pb + (size_t)tid * (AM_HD + 2)); mg_l[tid] = __ldcg(pb + (size_t)tid * (AM_HD + 2) + 1); }
-        __syncthreads();
-        float M = -FLT_MAX;
-        for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, mg_m[s]);
-        if (tid < a.n_splits) mg_e[tid] = am_exp2(mg_m[tid] - M);
-        __syncthreads();
-        float L = 0.f, acc = 0.f;
-        for (int s = 0; s < a.n_splits; ++s) L += mg_l[s] * mg_e[s];
-        #pragma unroll 8
-        for (int s = 0; s < a.n_splits; ++s) acc += __ldcg(pb + (size_t)s * (AM_HD + 2) + 2 + d) * mg_e[s];
-        a.out[((size_t)z * a.n_heads + head) * AM_HD + d] = __float2half_rn(L > 0.f ? acc * (1.0f / L) : 0.f);
+    // One warp per head, no CTA barrier: lane l reads (m, l) of slices l and l + 32 (n_splits <= 64), the warp reduces the
+    // maximum and the sum, then every lane adds its four dimensions over the slices in order with independent 16-byte loads
+    // (a serial pass per head with a barrier and an L2 round trip per batch of slices used to cost 0.3 us per slice: 20 of the
+    // 29 us of a 32768-key call).
+    if (warp < G) {
+        const int head = kvh * G + warp;
+        const float* pb = a.part + ((size_t)z * a.n_heads + head) * a.n_splits * AM_PREC;
+        const bool in0 = lane < a.n_splits, in1 = lane + 32 < a.n_splits;
+        const float m0 = in0 ? __ldcg(pb + (size_t)lane * AM_PREC) : -FLT_MAX, m1 = in1 ? __ldcg(pb + (size_t)(lane + 32) * AM_PREC) : -FLT_MAX;
+        const float l0 = in0 ? __ldcg(pb + (size_t)lane * AM_PREC + 1) : 0.f, l1 = in1 ? __ldcg(pb + (size_t)(lane + 32) * AM_PREC + 1) : 0.f;
+        const float M = warp_max(fmaxf(m0, m1));
+        const float e0 = in0 ? am_exp2(m0 - M) : 0.f, e1 = in1 ? am_exp2(m1 - M) : 0.f;
+        const float L = warp_sum(l0 * e0 + l1 * e1);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        // sixteen loads in flight per lane: four L2 round trips for the 64 slices a call can have
+        for (int s0 = 0; s0 < a.n_splits; s0 += 16) {
+            float4 v[16];
+            #pragma unroll
+            for (int i = 0; i < 16; ++i)
+                v[i] = s0 + i < a.n_splits ? __ldcg(reinterpret_cast<const float4*>(pb + (size_t)(s0 + i) * AM_PREC + 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            #pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int s = s0 + i;
+                const float e = __shfl_sync(0xFFFFFFFFu, s < 32 ? e0 : e1, s & 31);
+                acc.x += v[i].x * e; acc.y += v[i].y * e; acc.z += v[i].z * e; acc.w += v[i].w * e;
+            }
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        const __half2 o0 = __floats2half2_rn(acc.x * inv, acc.y * inv), o1 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+        uint2 st2; st2.x = *reinterpret_cast<const uint32_t*>(&o0); st2.y = *reinterpret_cast<const uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(a.out + ((size_t)z * a.n_heads + head) * AM_HD + 4 * lane) = st2;
     }
 }
 
@@ -392,7 +417,7 @@ static bool am_capturing(cudaStream_t st) {
 // one slice per thread).
 static int am_splits(int seq, int n_kv, int batch, int sm_count) {
     if (seq < 768) return 1;
-    const int want = (3 * sm_count + n_kv * batch - 1) / (n_kv * batch);
+    const int want = 3 * sm_count / (n_kv * batch);          // rounded DOWN: all CTAs resident at once (three per SM), no second wave of a few stragglers
     const int by_len = seq < 2048 ? seq / 256 : seq / 512;
     int ns = want < by_len ? want : by_len;
     if (ns > 64) ns = 64;
@@ -432,10 +457,12 @@ int launch_attention_tma(const AttnCall& c, cudaStream_t st) {
     a.out = c.out; a.q = c.q; a.ks = c.ks; a.vs = c.vs;
     a.ragged = c.tma_maps ? 1 : 0; a.ks_list = c.ks_list; a.vs_list = c.vs_list; a.seq_lens = c.seq_lens;
     a.n_heads = c.n_heads; a.n_kv = c.n_kv; a.seq_len = c.seq_len; a.d_pos = c.d_pos; a.scale = c.scale; a.status = cx->d_status;
+    static const bool nocompute = getenv("JLLM_B200_ATTN_NOCOMPUTE") != nullptr;
+    a.nocompute = nocompute ? 1 : 0;
     if (n_splits > 1) {
         // partials in the per-device split buffer; one ticket word per (sequence, kv head) in a per-device array that is zeroed
         // once and that every call leaves at zero
-        a.part = (size_t)batch * c.n_kv <= (size_t)ATTN_TICKET_WORDS ? splitk_buffer((size_t)batch * c.n_heads * n_splits * (c.hd + 2), !am_capturing(st)) : nullptr;
+        a.part = (size_t)batch * c.n_kv <= (size_t)ATTN_TICKET_WORDS ? splitk_buffer((size_t)batch * c.n_heads * n_splits * AM_PREC, !am_capturing(st)) : nullptr;
         if (!a.part) n_splits = 1;       // no scratch (or capture in progress): one slice per kv head, still on the GPU
         else a.tickets = cx->attn_tickets;
     }

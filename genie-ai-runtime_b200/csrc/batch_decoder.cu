@@ -194,7 +194,7 @@ jllm_b200_batch_decoder* jllm_b200_batch_decoder_create(const jllm_b200_model_de
     }
     { const size_t a = mmq_tc_scratch_bytes(T_Q6K, (int)H, B, (int)QD), b2 = mmq_tc_scratch_bytes(T_Q4K, (int)H, B, (int)QD); need = a > need ? a : need; need = b2 > need ? b2 : need; }
     mmq_scratch(need, true);
-    splitk_buffer((size_t)B * model->n_heads * 64 * (model->head_dim + 2), true);
+    splitk_buffer((size_t)B * model->n_heads * 64 * (model->head_dim + 4), true);
     return d;
 }
 void jllm_b200_batch_decoder_destroy(jllm_b200_batch_decoder* d) {

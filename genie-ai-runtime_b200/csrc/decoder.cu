@@ -427,7 +427,7 @@ jllm_b200_decoder* jllm_b200_decoder_create(const jllm_b200_model_desc* model, i
     if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); delete d; return nullptr; }
     if (dec_alloc(d)) { d->kv.destroy(); delete d; return nullptr; }
     // scratch that must exist before any graph capture
-    splitk_buffer((size_t)model->n_heads * 64 * (model->head_dim + 2), true);
+    splitk_buffer((size_t)model->n_heads * 64 * (model->head_dim + 4), true);
     return d;
 }
 
@@ -474,7 +474,7 @@ jllm_b200_decoder* jllm_b200_decoder_create_tp(const jllm_b200_model_desc* model
     jllm::KVCachePool::Config c = { model->n_layers, d->nkv_l, hd, model->max_context, 0, 1 };
     if (!d->kv.init(c) || !d->kv.kv_scale_ptr(0, 0, false)) { set_error(JB_ERR_NOMEM, "decoder: KV pool allocation failed"); d->kv.destroy(); cudaFree(d->seq); delete d; return nullptr; }
     if (dec_alloc(d)) { d->kv.destroy(); cudaFree(d->seq); delete d; return nullptr; }
-    splitk_buffer((size_t)d->nh_l * 64 * (hd + 2), true);
+    splitk_buffer((size_t)d->nh_l * 64 * (hd + 4), true);
     return d;
 }
 void jllm_b200_decoder_destroy(jllm_b200_decoder* d) {
