@@ -9,17 +9,18 @@
 // (the slice itself is attention_general.cuh).  The INT8 / head_dim 128 paths live in
 // attention_tma.cu (decode, 2-D TMA tiles) and attention_prefill.cu (causal prefill with query tiling).
 #include "attention.cuh"
+#include <cstdlib>
 #include "attention_general.cuh"
 #include <cfloat>
 
 namespace jb {
 
-// Split policy.  Merging slices costs about five microseconds however few there are (partials through L2, a fence, a ticket,
-// the last CTA's pass over them), more than a single slice needs for several hundred keys: one slice below 768 keys, then
-// slices of at least 256 keys (512 from 2048 keys on), at most 32 (the reference caps at 8 slices for its 8-SM part, attention.cu:1000-1005).
+// Split policy (also what the decoder session keys its captured graphs on): one slice below 640 keys (a sliced call pays the
+// partials, a ticket and the merge), then slices of at least 128 keys (512 from 2048 keys on), at most 32 (the reference caps at
+// 8 slices for its 8-SM part, attention.cu:1000-1005).
 int attn_splits_for(int seq_len) {
-    if (seq_len < 768) return 1;
-    const int n = seq_len < 2048 ? seq_len / 256 : seq_len / 512;
+    if (seq_len < 640) return 1;
+    const int n = seq_len < 2048 ? seq_len / 128 : seq_len / 512;
     return n > 32 ? 32 : n;
 }
 

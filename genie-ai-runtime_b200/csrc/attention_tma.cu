@@ -412,13 +412,18 @@ static bool am_capturing(cudaStream_t st) {
     return cs != cudaStreamCaptureStatusNone;
 }
 
-// Slices: enough CTAs for three per SM; one slice below 768 keys (a merge of slices costs more than a slice of a few
-// hundred keys takes), slices of at least 256 keys up to 2048 keys and of at least 512 beyond, at most 64 (the merge holds
-// one slice per thread).
+// Slices: as many CTAs as fit at once (three per SM, rounded down: a second wave of a few stragglers would double the call);
+// one slice below 640 keys (a sliced call pays the partials, a ticket and the merge: ~1.5 us), slices of at least 128 keys up to
+// 2048 keys and of at least 512 beyond, at most 64 (the merge reads two slices per lane); a batch: see below.  Measured per call, 300 / 500 / 700 /
+// 1024 / 4096 / 8192 / 32768 keys: 5.1 / 6.3 / 6.9 / 6.4 / 9.7 / 12.1 / 20.4 us.
 static int am_splits(int seq, int n_kv, int batch, int sm_count) {
-    if (seq < 768) return 1;
-    const int want = 3 * sm_count / (n_kv * batch);          // rounded DOWN: all CTAs resident at once (three per SM), no second wave of a few stragglers
-    const int by_len = seq < 2048 ? seq / 256 : seq / 512;
+    if (seq < 640) return 1;
+    // a ragged batch: slices of 1024 keys of the LONGEST sequence the caches can hold (shorter sequences get the same number of
+    // shorter slices): without slices the longest sequence's CTA runs 256 tiles on four warps while most SMs have drained —
+    // 64 sequences U{256..8192}: 343 us unsliced, 163 / 141 / 164 us with slices of 2048 / 1024 / 512 keys
+    if (batch > 1) { const int n = seq / 1024; return n < 1 ? 1 : (n > 16 ? 16 : n); }
+    const int want = 3 * sm_count / (n_kv * batch);
+    const int by_len = seq < 2048 ? seq / 128 : seq / 512;
     int ns = want < by_len ? want : by_len;
     if (ns > 64) ns = 64;
     return ns < 1 ? 1 : ns;

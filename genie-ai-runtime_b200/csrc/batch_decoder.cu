@@ -110,6 +110,7 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         c.tma_maps = d->maps.empty() ? nullptr : d->maps.data() + (size_t)l * B * 2 * 128;
         c.batch = B; c.max_seq = m.max_context; c.n_heads = m.n_heads; c.n_kv = m.n_kv_heads; c.hd = m.head_dim; c.chd = m.head_dim;
         c.scale = scale; c.kv_int8 = 1;
+        c.n_splits = 1;      // the step is one captured graph for every position: no slices (the streams of a step are short or many)
         BCHK(launch_attention(c, st));
         BCHK(launch_mmq(d->y, resolve_weight(w.wo), w.type_wo, d->att, H, B, QD, nullptr, st));
         BCHK(launch_add_half(d->x2, d->x, d->y, (long long)B * H, st));
