@@ -99,8 +99,8 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         void** L = d->lists + (size_t)l * 4 * B;
         BCHK(launch_rmsnorm(d->normed, d->x, nullptr, w.rms_attn, true, B, H, m.rms_eps, st));
         BCHK(launch_mmq(d->q, resolve_weight(w.wq), w.type_wq, d->normed, QD, B, H, nullptr, st));
-        BCHK(launch_mmq(d->k, resolve_weight(w.wk), w.type_wk, d->normed, KVD, B, H, nullptr, st));
-        BCHK(launch_mmq(d->v, resolve_weight(w.wv), w.type_wv, d->normed, KVD, B, H, nullptr, st));
+        BCHK(launch_mmq_ex(d->k, resolve_weight(w.wk), w.type_wk, d->normed, KVD, B, H, nullptr, true, st));      // same activations as Q
+        BCHK(launch_mmq_ex(d->v, resolve_weight(w.wv), w.type_wv, d->normed, KVD, B, H, nullptr, true, st));
         BCHK(launch_qkv_prep_batched(d->q, d->k, d->v, w.q_norm, w.k_norm, m.rms_eps, (int8_t* const*)L, (int8_t* const*)(L + B),
                                      (float* const*)(L + 2 * B), (float* const*)(L + 3 * B), B, m.n_heads, m.n_kv_heads, m.head_dim,
                                      d->state, m.rope_theta, m.rope_neox != 0, st));
@@ -112,14 +112,12 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         c.scale = scale; c.kv_int8 = 1;
         c.n_splits = 1;      // the step is one captured graph for every position: no slices (the streams of a step are short or many)
         BCHK(launch_attention(c, st));
-        BCHK(launch_mmq(d->y, resolve_weight(w.wo), w.type_wo, d->att, H, B, QD, nullptr, st));
-        BCHK(launch_add_half(d->x2, d->x, d->y, (long long)B * H, st));
+        BCHK(launch_mmq_ex(d->x2, resolve_weight(w.wo), w.type_wo, d->att, H, B, QD, d->x, false, st));           // + residual
         BCHK(launch_rmsnorm(d->normed, d->x2, nullptr, w.rms_ffn, true, B, H, m.rms_eps, st));
         BCHK(launch_mmq(d->gate, resolve_weight(w.w_gate), w.type_w_gate, d->normed, I, B, H, nullptr, st));
-        BCHK(launch_mmq(d->up, resolve_weight(w.w_up), w.type_w_up, d->normed, I, B, H, nullptr, st));
+        BCHK(launch_mmq_ex(d->up, resolve_weight(w.w_up), w.type_w_up, d->normed, I, B, H, nullptr, true, st));    // same activations as gate
         BCHK(launch_glu(d->sw, d->gate, d->up, B, I, false, st));
-        BCHK(launch_mmq(d->y, resolve_weight(w.w_down), w.type_w_down, d->sw, H, B, I, nullptr, st));
-        BCHK(launch_add_half(d->x, d->x2, d->y, (long long)B * H, st));
+        BCHK(launch_mmq_ex(d->x, resolve_weight(w.w_down), w.type_w_down, d->sw, H, B, I, d->x2, false, st));     // + residual
     }
     BCHK(launch_rmsnorm(d->normed, d->x, nullptr, m.output_norm, true, B, H, m.rms_eps, st));
     BCHK(launch_mmq(d->logits, resolve_weight(m.output), m.output_type, d->normed, V, B, H, nullptr, st));

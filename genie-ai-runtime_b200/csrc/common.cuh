@@ -47,6 +47,8 @@ struct DeviceCtx {
     RopeTable rope[8]; int n_rope = 0;
     bool gemv_attr[12] = {};
     bool mms_attr[8] = {};
+    // the activation operand the few-token GEMM quantised last (see launch_mmq_stream: reuse_operand)
+    const void* mms_op_x = nullptr; void* mms_op_scratch = nullptr; void* mms_op_stream = nullptr; int mms_op_n = 0, mms_op_k = 0, mms_op_ds4 = -1;
     bool gemv_chain_attr = false;
     bool attn_tma_attr[6] = { false, false, false, false, false, false };
     bool attn_prefill_attr[3] = { false, false, false };

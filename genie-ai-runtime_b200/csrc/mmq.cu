@@ -102,7 +102,20 @@ static bool capturing(cudaStream_t st) {
     return cs != cudaStreamCaptureStatusNone;
 }
 
+int launch_add_half(__half* out, const __half* a, const __half* b, long long n, cudaStream_t st);      // elementwise.cu
+
+static int launch_mmq_impl(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg, const __half* residual,
+                           bool same_x, cudaStream_t st);
+
 int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg, cudaStream_t st) {
+    return launch_mmq_impl(y, W, type, x, M, N, K, dbg, nullptr, false, st);
+}
+int launch_mmq_ex(__half* y, const void* W, int type, const __half* x, int M, int N, int K, const __half* residual, bool same_x, cudaStream_t st) {
+    return launch_mmq_impl(y, W, type, x, M, N, K, nullptr, residual, same_x, st);
+}
+
+static int launch_mmq_impl(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg, const __half* residual,
+                           bool same_x, cudaStream_t st) {
     if (M <= 0 || N <= 0) return JB_OK;
     if (K <= 0 || K % QK_K) return set_error(JB_ERR_ARG, "batched gemm: K=%d is not a positive multiple of 256", K);
     if (type != T_Q4K && type != T_Q6K) return set_error(JB_ERR_TYPE, "batched gemm: ggml type %d", type);
@@ -114,7 +127,11 @@ int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N
         const size_t need_s = mmq_stream_scratch_bytes(type, M, N, K);
         void* sc = mmq_scratch(need_s, !capturing(st));
         if (!sc) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_s);
-        return launch_mmq_stream(y, W, type, x, sc, M, N, K, st);
+        return launch_mmq_stream(y, W, type, x, sc, M, N, K, residual, same_x, st);
+    }
+    if (residual) {          // the other kernels have no fused exit: product, then the add (in place)
+        const int rc = launch_mmq_impl(y, W, type, x, M, N, K, dbg, nullptr, false, st);
+        return rc ? rc : launch_add_half(y, residual, y, (long long)N * M, st);
     }
     if (!dbg && !tc_off && mmq_tc_applies(W, type, M, N, K)) {
         const size_t need_tc = mmq_tc_scratch_bytes(type, M, N, K);

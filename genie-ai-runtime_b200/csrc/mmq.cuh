@@ -9,6 +9,10 @@ namespace jb {
 // src/kernels/gemv_q4.cu:2478-2495 -> mmq_q4k_llama.cu / mmq_q6k_llama.cu).
 // dbg_dots (optional): integer accumulators [N][M][K/32] (Q4_K) or [N][M][K/16] (Q6_K).
 int launch_mmq(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg_dots, cudaStream_t st);
+// the same with a residual added on the way out (y = half(float(residual) + float(half(product))), residual [N][M] or null)
+// and, for a second matrix multiplied by the SAME activations right after the first on this stream, `same_x_as_last`
+int launch_mmq_ex(__half* y, const void* W, int type, const __half* x, int M, int N, int K, const __half* residual, bool same_x_as_last,
+                  cudaStream_t st);
 size_t mmq_scratch_bytes(int N, int K);
 // tensor-core path (mmq_tc.cu): tcgen05.mma over fp16 operands built from the same quantised values
 bool   mmq_tc_applies(const void* W, int type, int M, int N, int K);
@@ -18,6 +22,7 @@ void*  mmq_scratch(size_t bytes, bool may_alloc);
 // few tokens (2..64): weights streamed once, mma.sync on fp16 operands with the tensor-core path's arithmetic (mmq_stream.cu)
 bool   mmq_stream_applies(const void* W, int type, int M, int N, int K);
 size_t mmq_stream_scratch_bytes(int type, int M, int N, int K);
-int    launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void* scratch, int M, int N, int K, cudaStream_t st);
+int    launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void* scratch, int M, int N, int K, const __half* residual,
+                         bool reuse_operand, cudaStream_t st);
 
 }  // namespace jb

@@ -36,6 +36,7 @@ constexpr int MS_KS = 4;                           // warps per row group (quart
 
 struct MsArgs {
     __half* y; float* part;                       // output, or fp32 partials [split][N][M] when nsplit > 1
+    const __half* res;                            // optional residual [N][M]: y = half(float(res) + float(half(product)))
     const uint8_t* W; const __half* xb;           // weights; activation operand, block-major
     int M, N, NP, K, nb;                          // NP = tokens padded to a multiple of 8
     int rg, nsplit, blocks_per_split, nstage;
@@ -311,20 +312,25 @@ __global__ void __launch_bounds__(MS_MAXRG * MS_KS * 32, 1) mms_kernel(const MsA
         for (int e = 0; e < 4; ++e) {
             const int row = row0 + 16 * rgi + g + 8 * (e >> 1), tok = 8 * t + 2 * c + (e & 1);
             if (row < a.M && tok < a.N) {
-                if (a.nsplit == 1) a.y[(size_t)tok * a.M + row] = __float2half_rn(acc[t][e]);
+                if (a.nsplit == 1) {
+                    const size_t o = (size_t)tok * a.M + row;
+                    const __half pr = __float2half_rn(acc[t][e]);
+                    a.y[o] = a.res ? __float2half_rn(__fadd_rn(__half2float(a.res[o]), __half2float(pr))) : pr;
+                }
                 else a.part[((size_t)blockIdx.y * a.N + tok) * a.M + row] = acc[t][e];
             }
         }
     }
 }
 
-__global__ void mms_reduce_kernel(__half* y, const float* part, long long n, int nsplit) {
+__global__ void mms_reduce_kernel(__half* y, const float* part, const __half* res, long long n, int nsplit) {
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float s = 0.f;
     for (int k = 0; k < nsplit; ++k) s += part[(size_t)k * n + i];      // fixed order: the result does not depend on timing
-    y[i] = __float2half_rn(s);
+    const __half pr = __float2half_rn(s);
+    y[i] = res ? __float2half_rn(__fadd_rn(__half2float(res[i]), __half2float(pr))) : pr;
 }
 
 // ── host side ─────────────────────────────────────────────────────────────
@@ -370,7 +376,12 @@ size_t mmq_stream_scratch_bytes(int type, int M, int N, int K) {
     return (((size_t)nb * NPk * MS_XROWB + 255) & ~(size_t)255) + (size_t)32 * N * M * sizeof(float);   // operand + partials of up to 32 K ranges
 }
 
-int launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void* scratch, int M, int N, int K, cudaStream_t st) {
+// `residual` (optional, [N][M]): the residual exit of a layer fused in (add_half arithmetic: the product is rounded to fp16
+// first).  `reuse_operand`: the caller multiplies the SAME activations by another matrix of the same weight type right after
+// the previous call on this stream (Q and K, gate and up): the quantised operand in `scratch` is still valid and the quantise
+// launch is skipped; the library checks pointer, shape, flavour and scratch address and quantises again if anything differs.
+int launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void* scratch, int M, int N, int K, const __half* residual,
+                      bool reuse_operand, cudaStream_t st) {
     DeviceCtx* cx = ctx();
     if (!cx) return JB_ERR_CUDA;
     const int nb = K / QK_K, NT = ms_tiles(N);
@@ -380,10 +391,16 @@ int launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void*
     const MsShape sh = ms_shape(type, M, NPk, nb, cx->sm_count, (size_t)cx->max_smem_optin);
     if (!sh.rg) return set_error(JB_ERR_LIMIT, "batched gemm: no launch shape for N=%d", N);
     const long long groups = (long long)NPk * (K / 32);
-    JB_CUDA(launch_k(mms_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xb, N, NPk, K, (int)(type == T_Q4K)));
-    count_launch();
+    const int ds4 = type == T_Q4K;
+    const bool same = reuse_operand && cx->mms_op_x == (const void*)x && cx->mms_op_scratch == scratch && cx->mms_op_n == N && cx->mms_op_k == K &&
+                      cx->mms_op_ds4 == ds4 && cx->mms_op_stream == (void*)st;
+    if (!same) {
+        JB_CUDA(launch_k(mms_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xb, N, NPk, K, ds4));
+        count_launch();
+        cx->mms_op_x = x; cx->mms_op_scratch = scratch; cx->mms_op_n = N; cx->mms_op_k = K; cx->mms_op_ds4 = ds4; cx->mms_op_stream = (void*)st;
+    }
     MsArgs a = {};
-    a.y = y; a.part = part; a.W = (const uint8_t*)W; a.xb = xb; a.M = M; a.N = N; a.NP = NPk; a.K = K; a.nb = nb;
+    a.y = y; a.part = part; a.res = residual; a.W = (const uint8_t*)W; a.xb = xb; a.M = M; a.N = N; a.NP = NPk; a.K = K; a.nb = nb;
     a.rg = sh.rg; a.nsplit = sh.nsplit; a.blocks_per_split = sh.bps; a.nstage = sh.nstage; a.status = cx->d_status;
     void (*kern)(MsArgs);
     #define MS_PICK(T) (NT == 1 ? mms_kernel<T, 1> : (NT == 2 ? mms_kernel<T, 2> : (NT == 4 ? mms_kernel<T, 4> : mms_kernel<T, 8>)))
@@ -402,7 +419,7 @@ int launch_mmq_stream(__half* y, const void* W, int type, const __half* x, void*
     count_launch();
     if (sh.nsplit > 1) {
         const long long n = (long long)N * M;
-        JB_CUDA(launch_k(mms_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)part, n, sh.nsplit));
+        JB_CUDA(launch_k(mms_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)part, residual, n, sh.nsplit));
         count_launch();
     }
     return JB_OK;
