@@ -54,7 +54,9 @@ def test_integer_accumulators_bit_exact(t, M, K):
     assert np.array_equal(dots.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("t,M,K", [(12, 2560, 4096), (14, 2560, 9728), (13, 50, 1024), (12, 5, 256)])
+@pytest.mark.parametrize("t,M,K", [(12, 2560, 4096), (14, 2560, 9728), (13, 50, 1024), (12, 5, 256),
+                                    # the row shards of Wo and W_down at 4 and 8 tensor-parallel ranks
+                                    (12, 640, 4096), (14, 640, 9728), (12, 320, 4096), (14, 320, 9728)])
 def test_gemv_quant_add(t, M, K):
     import torch
     jb = pkg()
@@ -83,7 +85,8 @@ def test_gemv_quant_f32(t, M, K):
     assert ok, f"max diff {md}"
 
 
-@pytest.mark.parametrize("types,Ms,K", [((12, 12), (9728, 9728), 2560), ((12, 14), (70, 33), 1024), ((12, 12), (5, 3), 256)])
+@pytest.mark.parametrize("types,Ms,K", [((12, 12), (9728, 9728), 2560), ((12, 14), (70, 33), 1024), ((12, 12), (5, 3), 256),
+                                        ((12, 12), (2432, 2432), 2560), ((12, 12), (1216, 1216), 2560)])      # gate/up shards at 4 / 8 ranks
 def test_gemv_quant_pair(types, Ms, K):
     import torch
     jb = pkg()
