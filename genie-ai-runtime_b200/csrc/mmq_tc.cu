@@ -44,8 +44,8 @@ struct TcArgs {
     __half* y; const uint8_t* W; int type; int M, N, K;
     int n_main, n_min;        // K tiles of weights, K tiles of the min and centring terms (Q4_K)
     int* status;
-    int ksplit;               // K ranges per output tile (1: results go straight to y; >1: fp32 partials, summed by a second kernel)
-    float* part;              // [ksplit][N][M] fp32
+    int n_full, ksplit;       // output tiles [0, n_full) are computed whole; each later one ("tail" tile) as `ksplit` K ranges whose
+    float* part;              // fp32 partials [ksplit][tail tile][token of the tile][128 rows] a second kernel sums
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -56,11 +56,21 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 // tensor pipe and the warps that feed it, and a sleeping warp wakes up far later than the barrier flips.
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
         uint32_t ok;
+#ifdef JB_TC_SPIN
         asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
                      : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+#else
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+#endif
         if (ok) return true;
+        if ((i & 1023u) == 1023u) {           // a poll may block for a hardware-defined interval: bound the wait in time as well
+            const unsigned long long t = global_ns();
+            if (!t0) t0 = t; else if (t - t0 > 2000000000ull) return false;
+        }
     }
     return false;
 }
@@ -100,7 +110,7 @@ __device__ __forceinline__ void tc_store_chunk(uint8_t* a_tile, int rl, int c, u
 // constant 8 * dA comes back through an extra K column per sub-block (see tc_dequant_q4k_extra).
 __device__ __forceinline__ void tc_nib4(uint32_t n4, __half2 dA, uint32_t& lo, uint32_t& hi) {
     const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6408));    // 1024 + 8
-    const uint32_t a = __byte_perm(n4, 0, 0x4140) | 0x64006400u, b = __byte_perm(n4, 0, 0x4342) | 0x64006400u;
+    const uint32_t a = __byte_perm(n4, 0x64646464u, 0x4140), b = __byte_perm(n4, 0x64646464u, 0x4342);      // 0x6400 | q = the half 1024 + q
     const __half2 ha = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&a), k1024), dA);
     const __half2 hb = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&b), k1024), dA);
     lo = *reinterpret_cast<const uint32_t*>(&ha); hi = *reinterpret_cast<const uint32_t*>(&hb);
@@ -142,22 +152,30 @@ __device__ __forceinline__ void tc_dequant_q4k(uint8_t* a_tile, int rl, const Ra
 // Q4_K extra K tiles: 8 columns per chunk = the 8 sub-blocks of one block.  Chunks [0, nb) hold the min term
 // half(-dmin) * half(m) (multiplied by the per-group sums of x, as in the reference); chunks [nb, 2nb) hold
 // 8 * half(d * sc), which multiplied by the per-group sums of the quantised activations restores the centring of
-// the codes.  Thread h writes chunks 4h..4h+3 of tile `tm`.
-__device__ __forceinline__ void tc_dequant_q4k_extra(uint8_t* a_tile, int rl, const uint8_t* row_blocks, int nb, int tm, int h) {
-    #pragma unroll 1
-    for (int c = 4 * h; c < 4 * h + 4; ++c) {
-        const int bi = 8 * tm + c;
+// the codes.  Thread h writes chunks 4h..4h+3 of tile `tm`: the four block headers they are made of are fetched
+// together (tc_extra_load), ahead of the wait for the stage, so one L2 latency is exposed per tile at most.
+__device__ __forceinline__ void tc_extra_load(uint4 (&hd)[4], const uint8_t* row_blocks, int nb, int tm, int h) {
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int bi = 8 * tm + 4 * h + i;
+        hd[i] = make_uint4(0, 0, 0, 0);
+        if (row_blocks && bi < 2 * nb) hd[i] = __ldg(reinterpret_cast<const uint4*>(row_blocks + (size_t)(bi >= nb ? bi - nb : bi) * Q4K_BYTES));
+    }
+}
+__device__ __forceinline__ void tc_dequant_q4k_extra(uint8_t* a_tile, int rl, const uint4 (&hd)[4], bool have_row, int nb, int tm, int h) {
+    const __half eight = __ushort_as_half((unsigned short)0x4800);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = 4 * h + i, bi = 8 * tm + c;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row_blocks && bi < 2 * nb) {
+        if (have_row && bi < 2 * nb) {
             const bool centre = bi >= nb;
-            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(row_blocks + (size_t)(centre ? bi - nb : bi) * Q4K_BYTES));
-            const __half dh = __ushort_as_half((unsigned short)(hd.x & 0xFFFFu));
-            const __half mh = __hneg(__ushort_as_half((unsigned short)(hd.x >> 16)));
-            const __half eight = __ushort_as_half((unsigned short)0x4800);
+            const __half dh = __ushort_as_half((unsigned short)(hd[i].x & 0xFFFFu));
+            const __half mh = __hneg(__ushort_as_half((unsigned short)(hd[i].x >> 16)));
             unsigned short o[8];
             #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                int sc, mn; scale_min_k4(j, hd.y, hd.z, hd.w, sc, mn);
+                int sc, mn; scale_min_k4(j, hd[i].y, hd[i].z, hd[i].w, sc, mn);
                 o[j] = __half_as_ushort(centre ? __hmul(eight, __hmul(dh, __int2half_rn(sc))) : __hmul(mh, __int2half_rn(mn)));
             }
             v = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
@@ -211,7 +229,7 @@ __device__ __forceinline__ void tc_dequant_q6k(uint8_t* a_tile, int rl, const Ra
                 const uint32_t L = (__funnelshift_r(r.ql[qq][wi], r.ql[qq][wi + 1], sh) >> (4 * kp)) & 0x0F0F0F0Fu;
                 const uint32_t H = __funnelshift_r(r.qh[wi], r.qh[wi + 1], sh) >> (4 * kp + 2 * qq);
                 const uint32_t q6 = L | ((H & 0x03030303u) << 4);
-                const uint32_t a = __byte_perm(q6, 0, 0x4140) | 0x64006400u, bb = __byte_perm(q6, 0, 0x4342) | 0x64006400u;
+                const uint32_t a = __byte_perm(q6, 0x64646464u, 0x4140), bb = __byte_perm(q6, 0x64646464u, 0x4342);
                 const __half2 qa = __hsub2(*reinterpret_cast<const __half2*>(&a), k1056);
                 const __half2 qb = __hsub2(*reinterpret_cast<const __half2*>(&bb), k1056);
                 const __half2 ra = __hfma2(qa, shi, __hmul2(qa, slo));
@@ -273,15 +291,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
     uint8_t* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (a.N + n_tile - 1) / n_tile, tiles_m = (a.M + TC_M - 1) / TC_M;
-    const int n_work = tiles_n * tiles_m * a.ksplit;
+    const int n_tail = tiles_n * tiles_m - a.n_full;
+    const int n_work = a.n_full + n_tail * a.ksplit;
     const int n_tiles = a.n_main + a.n_min;
-    // work item w = (output tile, K range): main K tiles [t0, t1) (whole fetch groups), and the extra tiles on the last range
+    // Work item w = (output tile, K range).  The first n_full items are whole output tiles, a multiple of the grid, so every
+    // CTA gets the same number of them; the tiles left over would occupy a fraction of the SMs for a whole tile time, so
+    // each is cut into ksplit K ranges that together fill one more, short, round.  A range holds main K tiles [t0, t1)
+    // (whole fetch groups), and the last range of a tile the extra tiles.
     constexpr int GTILES = TYPE == T_Q4K ? 4 : 2;
-    auto k_range = [&](int w, int& t0, int& t1, bool& extra) {
-        const int sp = w % a.ksplit, ng = a.n_main / GTILES;
-        t0 = (int)((long long)ng * sp / a.ksplit) * GTILES;
-        t1 = (int)((long long)ng * (sp + 1) / a.ksplit) * GTILES;
-        extra = sp == a.ksplit - 1;
+    auto k_range = [&](int w, int& tile, int& sp, int& t0, int& t1, bool& extra) {
+        int ks = 1;
+        tile = w; sp = 0;
+        if (w >= a.n_full) { const int v = w - a.n_full; ks = a.ksplit; tile = a.n_full + v / ks; sp = v - (v / ks) * ks; }
+        const int ng = a.n_main / GTILES;
+        t0 = (int)((long long)ng * sp / ks) * GTILES;
+        t1 = (int)((long long)ng * (sp + 1) / ks) * GTILES;
+        extra = sp == ks - 1;
     };
     const uint32_t b_bytes = (uint32_t)n_tile * TC_K * 2;
 
@@ -307,9 +332,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             for (int w = blockIdx.x; w < n_work && !fail; w += gridDim.x) {
-                const int n0 = ((w / a.ksplit) % tiles_n) * n_tile;
-                int t0, t1; bool extra;
-                k_range(w, t0, t1, extra);
+                int tile, sp, t0, t1; bool extra;
+                k_range(w, tile, sp, t0, t1, extra);
+                const int n0 = (tile % tiles_n) * n_tile;
                 for (int t = t0; t < n_tiles; ++t, ++it) {
                     if (t == t1) { if (!extra) break; t = a.n_main; if (t >= n_tiles) break; }
                     const int s = it % TC_STAGES;
@@ -330,8 +355,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                 const uint32_t d_tmem = tmem + (j & 1) * 256u;
                 if (!tc_wait(&acc_empty[j & 1], ((j >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
-                int t0, t1; bool extra;
-                k_range(w, t0, t1, extra);
+                int tile, sp, t0, t1; bool extra;
+                k_range(w, tile, sp, t0, t1, extra);
                 const int count = (t1 - t0) + (extra ? a.n_min : 0);
                 for (int t = 0; t < count; ++t, ++it) {
                     const uint32_t s = it % TC_STAGES;
@@ -371,10 +396,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&full[it_ % TC_STAGES]);
         };
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-            const int row = ((w / a.ksplit) / tiles_n) * TC_M + rl;
+            int tile, sp, kt0, kt1; bool extra;
+            k_range(w, tile, sp, kt0, kt1, extra);
+            const int row = (tile / tiles_n) * TC_M + rl;
             const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
-            int kt0, kt1; bool extra;
-            k_range(w, kt0, kt1, extra);
             const int g_first = kt0 / GT, g_last = kt1 / GT;
             auto fetch = [&](decltype(cur)& r, int g) {
                 if (!rowp || g >= g_last) return;
@@ -401,10 +426,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                 }
                 cur = nxt;
             }
-            for (t = a.n_main; extra && t < n_tiles && ok; ++t, ++it) {   // Q4_K: the min-term and centring tiles
-                if (!stage_free(it)) { ok = false; break; }
-                tc_dequant_q4k_extra(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, rowp, nb, t - a.n_main, h);
-                stage_done(it);
+            if constexpr (TYPE == T_Q4K) {                               // the min-term and centring tiles
+                uint4 xh[4];
+                if (extra && a.n_main < n_tiles && ok) tc_extra_load(xh, rowp, nb, 0, h);
+                for (t = a.n_main; extra && t < n_tiles && ok; ++t, ++it) {
+                    if (!stage_free(it)) { ok = false; break; }
+                    tc_dequant_q4k_extra(smem + (it % TC_STAGES) * TC_STAGE_BYTES, rl, xh, rowp != nullptr, nb, t - a.n_main, h);
+                    if (t + 1 < n_tiles) tc_extra_load(xh, rowp, nb, t + 1 - a.n_main, h);      // the next one, in flight across the hand-over
+                    stage_done(it);
+                }
             }
         }
         if (!ok) tc_fail(&fail, a.status);
@@ -416,8 +446,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         uint32_t j = 0;
         for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++j) {
             const uint32_t acc = j & 1;
-            const int n0 = ((w / a.ksplit) % tiles_n) * n_tile, row = ((w / a.ksplit) / tiles_n) * TC_M + rl;
-            float* part = a.ksplit > 1 ? a.part + (size_t)(w % a.ksplit) * a.N * a.M : nullptr;
+            int tile, sp, t0_, t1_; bool extra_;
+            k_range(w, tile, sp, t0_, t1_, extra_);
+            const int n0 = (tile % tiles_n) * n_tile, row = (tile / tiles_n) * TC_M + rl;
+            float* part = w >= a.n_full ? a.part + ((size_t)sp * n_tail + (size_t)(tile - a.n_full)) * n_tile * TC_M : nullptr;
             if (dw == 0 && lane == 0) {
                 const bool good = tc_wait(&acc_full[acc], (j >> 1) & 1) && !fail;
                 if (!good) tc_fail(&fail, a.status);
@@ -434,7 +466,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
                     for (int c = 0; c < 32; ++c) {
                         const int tok = n0 + cb + c;
                         if (tok < a.N) {
-                            if (part) part[(size_t)tok * a.M + row] = __uint_as_float(r[c]);
+                            if (part) part[(size_t)(cb + c) * TC_M + rl] = __uint_as_float(r[c]);
                             else a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[c]));
                         }
                     }
@@ -454,14 +486,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
     }
 }
 
-// sum of the K-range partials in a fixed order, rounded once to fp16
-__global__ void mmq_tc_reduce_kernel(__half* y, const float* part, long long n, int ksplit) {
+// sum of the K-range partials of the tail tiles in a fixed order, rounded once to fp16
+__global__ void mmq_tc_reduce_kernel(__half* y, const float* part, int M, int N, int n_tile, int tiles_n, int n_full, int n_tail, int ksplit) {
     pdl_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float s = part[i];
-    for (int k = 1; k < ksplit; ++k) s += part[(long long)k * n + i];
-    y[i] = __float2half_rn(s);
+    const long long total = (long long)n_tail * n_tile * TC_M;
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const int rl = (int)(e % TC_M), tl = (int)((e / TC_M) % n_tile), tile = n_full + (int)(e / ((long long)TC_M * n_tile));
+    const int row = (tile / tiles_n) * TC_M + rl, tok = (tile % tiles_n) * n_tile + tl;
+    if (row >= M || tok >= N) return;
+    float sum = part[e];
+    for (int k = 1; k < ksplit; ++k) sum += part[(long long)k * total + e];
+    y[(size_t)tok * M + row] = __float2half_rn(sum);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -483,24 +519,29 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Token-tile width and K ranges per output tile, chosen together.  Cost of a choice = rounds of the persistent grid x
-// (tile width / 256, floored at 0.65 for the MMA-issue and dequantisation floor of a K tile) / K ranges.  K is split
-// only when the output tiles alone leave SMs idle (the partial sums cost N x M x 8 bytes of traffic per range) and
-// every range keeps at least four fetch groups.
-static void tc_pick(int M, int N, int n_main_groups, int sm_count, int& n_tile, int& ksplit) {
+// Token-tile width, the number of whole output tiles and the K ranges of each remaining ("tail") tile, chosen together.
+// The whole tiles are the largest multiple of the grid; the tail is cut into as many K ranges as fill the grid once more
+// (every range keeps at least eight K tiles, and its partial sums cost a tile of fp32 traffic each way).  Cost of a
+// choice, in tile times of the full width = (whole rounds + 1 / ranges + a little per range) x (tile width / 256,
+// floored at 0.65 for the MMA-issue and dequantisation floor of a K tile).
+static void tc_pick(int M, int N, int n_main_tiles, int sm_count, int& n_tile, int& ksplit, int& n_full) {
     const int tiles_m = (M + TC_M - 1) / TC_M;
     float best = 1e30f;
-    n_tile = 256; ksplit = 1;
+    n_tile = 256; ksplit = 1; n_full = tiles_m * ((N + 255) / 256);
     for (int cand = 256; cand >= 32; cand >>= 1) {
         if (cand < 256 && cand >= 2 * N) continue;
         const int tiles = tiles_m * ((N + cand - 1) / cand);
         const float w = cand / 256.f, wt = w > 0.65f ? w : 0.65f;
-        for (int ks = 1; ks <= 8; ++ks) {
-            if (ks > 1 && (tiles * ks > sm_count || n_main_groups / ks < 4)) break;
-            const int rounds = (tiles * ks + sm_count - 1) / sm_count;
-            const float cost = rounds * wt / ks + 0.03f * (ks - 1);
-            if (cost < best - 1e-6f) { best = cost; n_tile = cand; ksplit = ks; }
+        const int rounds = tiles / sm_count, tail = tiles - rounds * sm_count;
+        int ks = 1;
+        if (tail > 0) {
+            ks = sm_count / tail;
+            if (ks > n_main_tiles / 8) ks = n_main_tiles / 8;
+            if (ks > 16) ks = 16;
+            if (ks < 1) ks = 1;
         }
+        const float cost = tail == 0 ? rounds * wt : (rounds + 1.0f / ks + (ks > 1 ? 0.04f + 0.01f * ks : 0.f)) * wt;
+        if (cost < best - 1e-6f) { best = cost; n_tile = cand; ksplit = ks; n_full = ks > 1 ? rounds * sm_count : tiles; }
     }
 }
 size_t mmq_tc_scratch_bytes(int type, int M, int N, int K) {
@@ -508,9 +549,10 @@ size_t mmq_tc_scratch_bytes(int type, int M, int N, int K) {
     const int sm = c ? c->sm_count : 148;
     const int n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     size_t b = (((size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half)) + 255) & ~(size_t)255;
-    int n_tile, ks;
-    tc_pick(M, N, (K / TC_K) / (type == T_Q4K ? 4 : 2), sm, n_tile, ks);
-    if (ks > 1) b += (size_t)ks * N * M * sizeof(float);
+    int n_tile, ks, n_full;
+    tc_pick(M, N, K / TC_K, sm, n_tile, ks, n_full);
+    const int tiles = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    if (ks > 1) b += (size_t)ks * (size_t)(tiles - n_full) * n_tile * TC_M * sizeof(float);
     return b + 256;
 }
 
@@ -531,8 +573,8 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     a.status = c->d_status;
     const int Kp = (a.n_main + a.n_min) * TC_K;
     int n_tile;
-    tc_pick(M, N, a.n_main / (type == T_Q4K ? 4 : 2), c->sm_count, n_tile, a.ksplit);
-    const int tiles = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    tc_pick(M, N, a.n_main, c->sm_count, n_tile, a.ksplit, a.n_full);
+    const int tiles_n = (N + n_tile - 1) / n_tile, tiles = tiles_n * ((M + TC_M - 1) / TC_M);
     a.part = a.ksplit > 1 ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xq) + ((((size_t)N * Kp * sizeof(__half)) + 255) & ~(size_t)255)) : nullptr;
 
     CUtensorMap map;
@@ -554,14 +596,15 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     const long long groups = (long long)N * (K / 32);
     JB_CUDA(launch_k(mmq_tc_quantize_kernel, dim3((unsigned)((groups + 3) / 4)), dim3(32, 4), 0, st, pdl_enabled(), x, xq, N, K, Kp, (int)(type == T_Q4K)));
     count_launch();
-    const int n_work = tiles * a.ksplit;
+    const int n_work = a.n_full + (tiles - a.n_full) * a.ksplit;
     const dim3 grid(n_work < c->sm_count ? n_work : c->sm_count);
     if (ti == 0) JB_CUDA(launch_k(mmq_tc_kernel<T_Q4K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     else         JB_CUDA(launch_k(mmq_tc_kernel<T_Q6K>, grid, dim3(TC_THREADS), TC_SMEM, st, pdl_enabled(), map, a, n_tile));
     count_launch();
     if (a.ksplit > 1) {
-        const long long n = (long long)N * M;
-        JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)a.part, n, a.ksplit));
+        const int n_tail = tiles - a.n_full;
+        const long long n = (long long)n_tail * n_tile * TC_M;
+        JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)a.part, M, N, n_tile, tiles_n, a.n_full, n_tail, a.ksplit));
         count_launch();
     }
     return JB_OK;
