@@ -49,6 +49,7 @@ struct DeviceCtx {
     bool mms_attr[8] = {};
     // the activation operand the few-token GEMM quantised last (see launch_mmq_stream: reuse_operand)
     const void* mms_op_x = nullptr; void* mms_op_scratch = nullptr; void* mms_op_stream = nullptr; int mms_op_n = 0, mms_op_k = 0, mms_op_ds4 = -1;
+    const void* tc_op_x = nullptr; void* tc_op_xq = nullptr; void* tc_op_stream = nullptr; int tc_op_n = 0, tc_op_k = 0, tc_op_ds4 = -1;   // the same for the tensor-core GEMM's operand
     bool gemv_chain_attr = false;
     bool attn_tma_attr[6] = { false, false, false, false, false, false };
     bool attn_prefill_attr[3] = { false, false, false };

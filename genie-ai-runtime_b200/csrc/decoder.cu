@@ -389,8 +389,8 @@ static int dec_prefill_chunk(jllm_b200_decoder* d, const int* dev_tokens, int N,
         float* ks = d->kv.kv_scale_ptr(l, 0, false); float* vs = d->kv.kv_scale_ptr(l, 0, true);
         DCHK(launch_rmsnorm(d->pf_normed, d->pf_x, nullptr, w.rms_attn, true, N, H, m.rms_eps, st));
         DCHK(launch_mmq(d->pf_q, resolve_weight(w.wq), w.type_wq, d->pf_normed, QD, N, H, nullptr, st));
-        DCHK(launch_mmq(d->pf_k, resolve_weight(w.wk), w.type_wk, d->pf_normed, KVD, N, H, nullptr, st));
-        DCHK(launch_mmq(d->pf_v, resolve_weight(w.wv), w.type_wv, d->pf_normed, KVD, N, H, nullptr, st));
+        DCHK(launch_mmq_ex(d->pf_k, resolve_weight(w.wk), w.type_wk, d->pf_normed, KVD, N, H, nullptr, true, st));      // the operand of the product before
+        DCHK(launch_mmq_ex(d->pf_v, resolve_weight(w.wv), w.type_wv, d->pf_normed, KVD, N, H, nullptr, true, st));      // the operand of the product before
         DCHK(launch_qkv_prep_tokens(d->pf_q, d->pf_k, d->pf_v, w.q_norm, w.k_norm, m.rms_eps, kc, vc, ks, vs, N, m.n_heads, m.n_kv_heads,
                                     m.head_dim, start, m.rope_theta, m.rope_neox != 0, st));
         AttnCall c;
@@ -401,7 +401,7 @@ static int dec_prefill_chunk(jllm_b200_decoder* d, const int* dev_tokens, int N,
         DCHK(launch_add_half(d->pf_x2, d->pf_x, d->pf_y, (long long)N * H, st));
         DCHK(launch_rmsnorm(d->pf_normed, d->pf_x2, nullptr, w.rms_ffn, true, N, H, m.rms_eps, st));
         DCHK(launch_mmq(d->pf_gate, resolve_weight(w.w_gate), w.type_w_gate, d->pf_normed, I, N, H, nullptr, st));
-        DCHK(launch_mmq(d->pf_up, resolve_weight(w.w_up), w.type_w_up, d->pf_normed, I, N, H, nullptr, st));
+        DCHK(launch_mmq_ex(d->pf_up, resolve_weight(w.w_up), w.type_w_up, d->pf_normed, I, N, H, nullptr, true, st));      // the operand of the product before
         DCHK(launch_glu(d->pf_sw, d->pf_gate, d->pf_up, N, I, false, st));
         DCHK(launch_mmq(d->pf_y, resolve_weight(w.w_down), w.type_w_down, d->pf_sw, H, N, I, nullptr, st));
         DCHK(launch_add_half(d->pf_x, d->pf_x2, d->pf_y, (long long)N * H, st));

@@ -127,6 +127,7 @@ static int launch_mmq_impl(__half* y, const void* W, int type, const __half* x, 
         const size_t need_s = mmq_stream_scratch_bytes(type, M, N, K);
         void* sc = mmq_scratch(need_s, !capturing(st));
         if (!sc) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_s);
+        if (DeviceCtx* c = ctx()) c->tc_op_x = nullptr;          // the scratch is shared: the other path's operand is gone
         return launch_mmq_stream(y, W, type, x, sc, M, N, K, residual, same_x, st);
     }
     if (residual) {          // the other kernels have no fused exit: product, then the add (in place)
@@ -137,8 +138,10 @@ static int launch_mmq_impl(__half* y, const void* W, int type, const __half* x, 
         const size_t need_tc = mmq_tc_scratch_bytes(type, M, N, K);
         __half* xq = (__half*)mmq_scratch(need_tc, !capturing(st));
         if (!xq) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need_tc);
-        return launch_mmq_tc(y, W, type, x, xq, M, N, K, st);
+        if (DeviceCtx* c = ctx()) c->mms_op_x = nullptr;
+        return launch_mmq_tc(y, W, type, x, xq, M, N, K, same_x, st);
     }
+    if (DeviceCtx* c = ctx()) { c->tc_op_x = nullptr; c->mms_op_x = nullptr; }
     const size_t need = mmq_scratch_bytes(N, K);
     uint8_t* base = (uint8_t*)mmq_scratch(need, !capturing(st));
     if (!base) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need);

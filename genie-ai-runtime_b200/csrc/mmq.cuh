@@ -17,7 +17,7 @@ size_t mmq_scratch_bytes(int N, int K);
 // tensor-core path (mmq_tc.cu): tcgen05.mma over fp16 operands built from the same quantised values
 bool   mmq_tc_applies(const void* W, int type, int M, int N, int K);
 size_t mmq_tc_scratch_bytes(int type, int M, int N, int K);
-int    launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* xq, int M, int N, int K, cudaStream_t st);
+int    launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* xq, int M, int N, int K, bool same_x_as_last, cudaStream_t st);
 void*  mmq_scratch(size_t bytes, bool may_alloc);
 // few tokens (2..64): weights streamed once, mma.sync on fp16 operands with the tensor-core path's arithmetic (mmq_stream.cu)
 bool   mmq_stream_applies(const void* W, int type, int M, int N, int K);

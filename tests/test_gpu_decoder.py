@@ -131,6 +131,35 @@ def test_batched_prefill_matches_oracle_prefill(small_model):
         assert 0 <= margin <= NOISE * rms, (s, margin, rms)
 
 
+def test_batched_prefill_of_a_long_prompt(small_model):
+    """A 100-token prompt: more than 64 tokens go through the tensor-core GEMM, where the K, V and up products reuse the
+    quantised operand of the product before them.  The stream must be the oracle's (or part from it within the noise)."""
+    jb = pkg()
+    m, w = small_model
+    rng = np.random.Generator(np.random.PCG64(1005))
+    prompt = rng.integers(0, SMALL["vocab"], 100)
+    n_new, ctx = 8, 128
+    od = orc.Decoder(m, ctx)
+    want = od.generate_prefilled(prompt, n_new)
+    d = jb.decoder.Decoder(m["cfg"], w, ctx, jb.decoder.FUSED | jb.decoder.GRAPH | jb.decoder.PREFILL)
+    got = list(d.generate(prompt, n_new))
+    got2 = list(d.generate(prompt, n_new))
+    d.close()
+    assert jb.device_status() == 0
+    assert got == got2, (got, got2)
+    if got != want:
+        s = next(i for i in range(n_new) if got[i] != want[i])
+        od2 = orc.Decoder(m, ctx)
+        tok = od2.prefill(prompt)
+        for i in range(s):
+            tok = od2.step(want[i], len(prompt) + i)
+        lg = od2.logits
+        rms = float(np.sqrt(np.mean(lg.astype(np.float64) ** 2)))
+        margin = float(lg[want[s]] - lg[got[s]])
+        print(f"long-prompt stream parts at step {s}: oracle margin {margin:.4f} (logit RMS {rms:.3f})")
+        assert 0 <= margin <= NOISE * rms, (s, margin, rms)
+
+
 def test_decoder_argument_errors(small_model):
     jb = pkg()
     m, w = small_model
