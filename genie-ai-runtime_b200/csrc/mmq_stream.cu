@@ -337,6 +337,9 @@ __global__ void mms_reduce_kernel(__half* y, const float* part, const __half* re
 bool mmq_stream_applies(const void* W, int type, int M, int N, int K) {
     static const bool off = [] { const char* e = getenv("JLLM_B200_MMQ_STREAM"); return e && e[0] == '0'; }();
     if (off || N < 2 || N > 64 || M < 16 || K % QK_K) return false;
+    // the largest matrices at more than 48 tokens: the tensor-core kernel is faster (64 tokens, Q4_K 9728 x 2560: 29.5 against
+    // 36.6 us; Q6_K 2560 x 9728: 30.7 against 35.7 us; equal at 32 tokens, and the smaller matrices stay faster here)
+    if (N > 48 && (long long)M * K >= (1ll << 24) && mmq_tc_applies(W, type, M, N, K)) return false;
     if (type == T_Q4K) return ((uintptr_t)W & 15) == 0;
     return type == T_Q6K && ((uintptr_t)W & 1) == 0;
 }

@@ -57,11 +57,12 @@ def test_reference_golden_vectors(golden_dir, name, t):
     assert np.max(np.abs(y.float().cpu().numpy() - ref)) <= 0.5
 
 
-@pytest.mark.parametrize("t,M,N,K", [(12, 9728, 64, 2560), (14, 2560, 64, 9728), (12, 4096, 8, 2560), (14, 1024, 24, 2560), (12, 2560, 2, 4096),
-                                      (14, 151, 57, 768)])
+@pytest.mark.parametrize("t,M,N,K", [(12, 9728, 48, 2560), (14, 2560, 48, 9728), (12, 9728, 64, 2560), (14, 2560, 64, 9728), (12, 4096, 64, 2560),
+                                      (12, 4096, 8, 2560), (14, 1024, 24, 2560), (12, 2560, 2, 4096), (14, 151, 57, 768)])
 def test_few_tokens_stream_the_weights_once(t, M, N, K):
-    """2..64 tokens go through the weight-streaming kernel (csrc/mmq_stream.cu): the decoder's own shapes at 64 streams, every
-    token-tile count, ragged row and token edges, and K ranges split over CTAs (few rows, long K)."""
+    """2..64 tokens go through the weight-streaming kernel (csrc/mmq_stream.cu): the decoder's own shapes at 48 and 64 streams
+    (the two largest matrices at 64 streams are handed to the tensor-core kernel, which is faster there), every token-tile
+    count, ragged row and token edges, and K ranges split over CTAs (few rows, long K)."""
     import torch
     jb = pkg()
     rng = np.random.Generator(np.random.PCG64(1007 + M + N))
