@@ -538,18 +538,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
     }
 }
 
-// sum of the K-range partials of the tail tiles in a fixed order, rounded once to fp16
+// sum of the K-range partials of the tail tiles in a fixed order, rounded once to fp16; a thread takes four consecutive rows
+// of one token (16-byte loads; the rows of a tile start at a multiple of 128, so with M a multiple of 4 a group of four
+// is inside the tensor or outside it as a whole)
 __global__ void mmq_tc_reduce_kernel(__half* y, const float* part, int M, int N, int n_tile, int tiles_n, int n_full, int n_tail, int ksplit) {
     pdl_wait();
     const long long total = (long long)n_tail * n_tile * TC_M;
-    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long e = 4 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
     if (e >= total) return;
     const int rl = (int)(e % TC_M), tl = (int)((e / TC_M) % n_tile), tile = n_full + (int)(e / ((long long)TC_M * n_tile));
     const int row = (tile / tiles_n) * TC_M + rl, tok = (tile % tiles_n) * n_tile + tl;
     if (row >= M || tok >= N) return;
-    float sum = part[e];
-    for (int k = 1; k < ksplit; ++k) sum += part[(long long)k * total + e];
-    y[(size_t)tok * M + row] = __float2half_rn(sum);
+    float4 sum = *reinterpret_cast<const float4*>(part + e);
+    for (int k = 1; k < ksplit; ++k) {
+        const float4 v = *reinterpret_cast<const float4*>(part + (long long)k * total + e);
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    __half* dst = y + (size_t)tok * M + row;
+    if ((M & 3) == 0 && ((uintptr_t)y & 7) == 0) {
+        const __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+        const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+        for (int i = 0; i < 4 && row + i < M; ++i) dst[i] = __float2half_rn(v[i]);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -667,7 +679,7 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     count_launch();
     if (a.ksplit > 1) {
         const int n_tail = tiles - a.n_full;
-        const long long n = (long long)n_tail * n_tile * TC_M;
+        const long long n = (long long)n_tail * n_tile * TC_M / 4;
         JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)a.part, M, N, n_tile, tiles_n, a.n_full, n_tail, a.ksplit));
         count_launch();
     }
