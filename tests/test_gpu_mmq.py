@@ -15,7 +15,9 @@ pytestmark = pytest.mark.gpu
                                       (14, 20, 3, 9728), (13, 16, 3, 512),
                                       # several output tiles per persistent CTA, ragged last row / token tile, every token-tile width
                                       (12, 300, 300, 2560), (14, 260, 270, 1024), (12, 1, 2, 256), (14, 129, 33, 256), (12, 257, 129, 768),
-                                      (12, 40000, 40, 256), (14, 19000, 70, 512)])
+                                      (12, 40000, 40, 256), (14, 19000, 70, 512),
+                                      # more output tiles than SMs: whole rounds, then the leftover tiles cut into K ranges (ragged edges)
+                                      (12, 2500, 2000, 2048), (14, 2500, 1999, 1024)])
 def test_gemm_quant_batched_matches_oracle(t, M, N, K):
     import torch
     jb = pkg()
