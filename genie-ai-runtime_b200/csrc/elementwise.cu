@@ -198,10 +198,43 @@ __global__ void glu_kernel(__half* out, const __half* gate, const __half* up, lo
     out[i2] = __float2half_rn(r[0]);
     if (two) out[i2 + 1] = __float2half_rn(r[1]);
 }
+// the same arithmetic, eight elements per thread with 16-byte accesses (batched layers: millions of elements)
+__global__ void glu8_kernel(__half* out, const __half* gate, const __half* up, long long total8, int gelu) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const uint4 gv = reinterpret_cast<const uint4*>(gate)[i], uv = reinterpret_cast<const uint4*>(up)[i];
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t ow[4];
+    #pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(&gw[k])), u = __half22float2(*reinterpret_cast<const __half2*>(&uw[k]));
+        const float gs[2] = {g.x, g.y}, us[2] = {u.x, u.y};
+        float r[2];
+        #pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (gelu) {
+                const float x = gs[e];
+                const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(x, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, x), x), x)));
+                r[e] = __fmul_rn(__fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, tanhf(inner))), us[e]);
+            } else {
+                r[e] = __fmul_rn(__fdiv_rn(gs[e], __fadd_rn(1.0f, expf(-gs[e]))), us[e]);
+            }
+        }
+        const __half2 h = __halves2half2(__float2half_rn(r[0]), __float2half_rn(r[1]));
+        ow[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
 int launch_glu(__half* out, const __half* gate, const __half* up, int rows, int dim, bool gelu, cudaStream_t st) {
     const long long total = (long long)rows * dim;
     if (total <= 0) return JB_OK;
     if (!out || !gate || !up) return set_error(JB_ERR_PTR, "glu: null pointer");
+    if (total >= 4096 && total % 8 == 0 && (((uintptr_t)out | (uintptr_t)gate | (uintptr_t)up) & 15) == 0) {
+        JB_CUDA(launch_k(glu8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, st, pdl_enabled(), out, gate, up, total / 8, (int)gelu));
+        count_launch();
+        return JB_OK;
+    }
     const long long t2 = (total + 1) / 2;
     JB_CUDA(launch_k(glu_kernel, dim3((unsigned)((t2 + 255) / 256)), dim3(256), 0, st, pdl_enabled(), out, gate, up, total, (int)gelu));
     count_launch();
@@ -475,8 +508,28 @@ __global__ void add_half_kernel(__half* out, const __half* a, const __half* b, l
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2half_rn(__fadd_rn(__half2float(a[i]), __half2float(b[i])));
 }
+__global__ void add_half8_kernel(__half* out, const __half* a, const __half* b, long long n8) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 av = reinterpret_cast<const uint4*>(a)[i], bv = reinterpret_cast<const uint4*>(b)[i];
+    const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    uint32_t ow[4];
+    #pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&aw[k])), y = __half22float2(*reinterpret_cast<const __half2*>(&bw[k]));
+        const __half2 h = __halves2half2(__float2half_rn(__fadd_rn(x.x, y.x)), __float2half_rn(__fadd_rn(x.y, y.y)));
+        ow[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
 int launch_add_half(__half* out, const __half* a, const __half* b, long long n, cudaStream_t st) {
     if (n <= 0) return JB_OK;
+    if (n >= 4096 && n % 8 == 0 && (((uintptr_t)out | (uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+        JB_CUDA(launch_k(add_half8_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, pdl_enabled(), out, a, b, n / 8));
+        count_launch();
+        return JB_OK;
+    }
     JB_CUDA(launch_k(add_half_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), out, a, b, n));
     count_launch();
     return JB_OK;

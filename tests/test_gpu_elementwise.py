@@ -116,6 +116,16 @@ def test_swiglu_geglu_scale_softcap_softmax():
     assert _ulp_close(out.cpu().numpy(), orc.swiglu(g, u), 1)[0]
     jb.fused_geglu(out, dev(g), dev(u), 1, n)
     assert _ulp_close(out.cpu().numpy(), orc.geglu(g, u), 1)[0]
+    # a multiple of eight elements takes the 16-byte form of the kernel: the same bits as the two-element form on a copy
+    # whose length is not a multiple of eight
+    n8 = 16 * 9728
+    g8 = (rng.standard_normal(n8 + 1) * 3).astype(np.float16); u8 = orc.gen_act(rng, n8 + 1)
+    for fn in (jb.fused_swiglu, jb.fused_geglu):
+        wide = torch.zeros(n8, dtype=torch.float16, device="cuda"); narrow = torch.zeros(n8 + 1, dtype=torch.float16, device="cuda")
+        fn(wide, dev(g8[:n8].copy()), dev(u8[:n8].copy()), 16, 9728)
+        fn(narrow, dev(g8), dev(u8), 1, n8 + 1)
+        assert torch.equal(wide, narrow[:n8])
+    assert _ulp_close(wide.cpu().numpy()[:9728], orc.geglu(g8[:9728], u8[:9728]), 1)[0]
     one = torch.tensor([1.0], dtype=torch.float16, device="cuda"); two = torch.tensor([2.0], dtype=torch.float16, device="cuda")
     o1 = torch.zeros(1, dtype=torch.float16, device="cuda")
     jb.fused_swiglu(o1, one, two, 1, 1)
