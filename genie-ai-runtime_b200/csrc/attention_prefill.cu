@@ -22,7 +22,8 @@ constexpr int AP_TILE   = 32;
 constexpr int AP_STAGES = 2;
 constexpr int AP_HD     = 128;
 constexpr int AP_PQ     = 2;                          // query tokens per CTA: with 4 the accumulators took 232 registers (two CTAs per SM) and the
-                                                      // kernel, bound by instruction latency, ran 10 % slower (2048 tokens: 474 against 427 us)
+                                                      // kernel, bound by instruction latency, ran 10 % slower (2048 tokens: 474 against 427 us); the 69 KB of shared
+                                                      // memory allow three CTAs per SM, so the register bound is the one for three (412 us)
 constexpr int AP_TILE_BYTES  = AP_TILE * AP_HD;
 constexpr int AP_STAGE_BYTES = 2 * AP_TILE_BYTES;
 constexpr int AP_RING_BYTES  = AP_WARPS * AP_STAGES * AP_STAGE_BYTES;          // 64 KB
@@ -57,7 +58,7 @@ __device__ __forceinline__ uint32_t ap_swz(uint32_t tile, int row, int b) {
 }
 
 template <int G>
-__global__ void __launch_bounds__(AP_WARPS * 32, 4) attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+__global__ void __launch_bounds__(AP_WARPS * 32, 3) attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                                                                         const ApArgs a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full[AP_WARPS][AP_STAGES];
