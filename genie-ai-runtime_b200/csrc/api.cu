@@ -306,6 +306,15 @@ int jllm_b200_gemv_quant_int_dots(void* y, int32_t* dots, const void* W, int t, 
     if (t != T_Q4K && t != T_Q6K) return set_error(JB_ERR_TYPE, "int dots: ggml type %d has no integer path", t);
     return gemv_one(y, W, t, CH(x), nullptr, M, K, 0, dots, ST(s));
 }
+int jllm_b200_gemm_quant_batched_pair(void* y0, const void* W0, int t0, int M0, void* y1, const void* W1, int t1, int M1, const void* x, int N, int K,
+                                      void* s) {
+    if (N < 2 || M0 <= 0 || M1 <= 0 || K <= 0 || K % QK_K) return set_error(JB_ERR_ARG, "gemm_quant_batched_pair: M0=%d M1=%d N=%d K=%d", M0, M1, N, K);
+    if (!y0 || !y1 || !x) return set_error(JB_ERR_PTR, "gemm_quant_batched_pair: null pointer");
+    if ((t0 != T_Q4K && t0 != T_Q6K) || (t1 != T_Q4K && t1 != T_Q6K)) return set_error(JB_ERR_TYPE, "gemm_quant_batched_pair: ggml types %d, %d", t0, t1);
+    const void* Wd0 = resolve_weight(W0); const void* Wd1 = resolve_weight(W1);
+    if (!Wd0 || !Wd1) return set_error(JB_ERR_PTR, "gemm_quant_batched_pair: weight pointer is not device-visible");
+    return launch_mmq_pair(H(y0), H(y1), Wd0, t0, Wd1, t1, CH(x), M0, M1, N, K, ST(s));
+}
 int jllm_b200_gemm_quant_batched_int_dots(void* y, int32_t* dots, const void* W, int t, const void* x, int M, int N, int K, void* s) {
     if (t != T_Q4K && t != T_Q6K) return set_error(JB_ERR_TYPE, "int dots: ggml type %d has no integer path", t);
     return gemm_batched(H(y), W, t, CH(x), M, N, K, dots, ST(s));

@@ -114,8 +114,7 @@ static int bdec_enqueue_step(jllm_b200_batch_decoder* d, const int* prompt, int 
         BCHK(launch_attention(c, st));
         BCHK(launch_mmq_ex(d->x2, resolve_weight(w.wo), w.type_wo, d->att, H, B, QD, d->x, false, st));           // + residual
         BCHK(launch_rmsnorm(d->normed, d->x2, nullptr, w.rms_ffn, true, B, H, m.rms_eps, st));
-        BCHK(launch_mmq(d->gate, resolve_weight(w.w_gate), w.type_w_gate, d->normed, I, B, H, nullptr, st));
-        BCHK(launch_mmq_ex(d->up, resolve_weight(w.w_up), w.type_w_up, d->normed, I, B, H, nullptr, true, st));    // same activations as gate
+        BCHK(launch_mmq_pair(d->gate, d->up, resolve_weight(w.w_gate), w.type_w_gate, resolve_weight(w.w_up), w.type_w_up, d->normed, I, I, B, H, st));   // one launch where the tensor-core kernel serves both
         BCHK(launch_glu(d->sw, d->gate, d->up, B, I, false, st));
         BCHK(launch_mmq_ex(d->x, resolve_weight(w.w_down), w.type_w_down, d->sw, H, B, I, d->x2, false, st));     // + residual
     }
@@ -192,6 +191,7 @@ jllm_b200_batch_decoder* jllm_b200_batch_decoder_create(const jllm_b200_model_de
         need = a > need ? a : need; need = b2 > need ? b2 : need; need = c2 > need ? c2 : need;
     }
     { const size_t a = mmq_tc_scratch_bytes(T_Q6K, (int)H, B, (int)QD), b2 = mmq_tc_scratch_bytes(T_Q4K, (int)H, B, (int)QD); need = a > need ? a : need; need = b2 > need ? b2 : need; }
+    { const size_t a = mmq_tc_scratch_bytes_pair(T_Q6K, (int)I, (int)I, B, (int)H), b2 = mmq_tc_scratch_bytes_pair(T_Q4K, (int)I, (int)I, B, (int)H); need = a > need ? a : need; need = b2 > need ? b2 : need; }
     mmq_scratch(need, true);
     splitk_buffer((size_t)B * model->n_heads * 64 * (model->head_dim + 4), true);
     return d;

@@ -400,8 +400,7 @@ static int dec_prefill_chunk(jllm_b200_decoder* d, const int* dev_tokens, int N,
         DCHK(launch_mmq(d->pf_y, resolve_weight(w.wo), w.type_wo, d->pf_att, H, N, QD, nullptr, st));
         DCHK(launch_add_half(d->pf_x2, d->pf_x, d->pf_y, (long long)N * H, st));
         DCHK(launch_rmsnorm(d->pf_normed, d->pf_x2, nullptr, w.rms_ffn, true, N, H, m.rms_eps, st));
-        DCHK(launch_mmq(d->pf_gate, resolve_weight(w.w_gate), w.type_w_gate, d->pf_normed, I, N, H, nullptr, st));
-        DCHK(launch_mmq_ex(d->pf_up, resolve_weight(w.w_up), w.type_w_up, d->pf_normed, I, N, H, nullptr, true, st));      // the operand of the product before
+        DCHK(launch_mmq_pair(d->pf_gate, d->pf_up, resolve_weight(w.w_gate), w.type_w_gate, resolve_weight(w.w_up), w.type_w_up, d->pf_normed, I, I, N, H, st));
         DCHK(launch_glu(d->pf_sw, d->pf_gate, d->pf_up, N, I, false, st));
         DCHK(launch_mmq(d->pf_y, resolve_weight(w.w_down), w.type_w_down, d->pf_sw, H, N, I, nullptr, st));
         DCHK(launch_add_half(d->pf_x, d->pf_x2, d->pf_y, (long long)N * H, st));

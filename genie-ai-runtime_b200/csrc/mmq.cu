@@ -114,6 +114,27 @@ int launch_mmq_ex(__half* y, const void* W, int type, const __half* x, int M, in
     return launch_mmq_impl(y, W, type, x, M, N, K, nullptr, residual, same_x, st);
 }
 
+// Two products over the same activations (gate and up): one launch of the tensor-core kernel when both matrices are of one
+// type and that kernel is the one each would get on its own; else one product after the other, the second reusing the
+// quantised operand of the first.
+int launch_mmq_pair(__half* y1, __half* y2, const void* W1, int type1, const void* W2, int type2, const __half* x, int M1, int M2, int N, int K,
+                    cudaStream_t st) {
+    static const bool tc_off = [] { const char* e = getenv("JLLM_B200_MMQ"); return e && !strcmp(e, "cuda"); }();
+    static const bool pair_off = [] { const char* e = getenv("JLLM_B200_MMQ_PAIR"); return e && e[0] == '0'; }();
+    const bool ok = !tc_off && !pair_off && type1 == type2 && M1 > 0 && M2 > 0 && N > 0 && K > 0 && K % QK_K == 0 && y1 && y2 && W1 && W2 && x &&
+                    (type1 == T_Q4K || type1 == T_Q6K) && !mmq_stream_applies(W1, type1, M1, N, K) && !mmq_stream_applies(W2, type2, M2, N, K) &&
+                    mmq_tc_applies(W1, type1, M1, N, K) && mmq_tc_applies(W2, type2, M2, N, K);
+    if (!ok) {
+        const int rc = launch_mmq_impl(y1, W1, type1, x, M1, N, K, nullptr, nullptr, false, st);
+        return rc ? rc : launch_mmq_impl(y2, W2, type2, x, M2, N, K, nullptr, nullptr, true, st);
+    }
+    const size_t need = mmq_tc_scratch_bytes_pair(type1, M1, M2, N, K);
+    __half* xq = (__half*)mmq_scratch(need, !capturing(st));
+    if (!xq) return set_error(JB_ERR_NOMEM, "batched gemm: %zu B of activation scratch unavailable", need);
+    if (DeviceCtx* c = ctx()) c->mms_op_x = nullptr;
+    return launch_mmq_tc_pair(y1, y2, W1, W2, type1, x, xq, M1, M2, N, K, false, st);
+}
+
 static int launch_mmq_impl(__half* y, const void* W, int type, const __half* x, int M, int N, int K, int32_t* dbg, const __half* residual,
                            bool same_x, cudaStream_t st) {
     if (M <= 0 || N <= 0) return JB_OK;

@@ -42,6 +42,7 @@ constexpr uint32_t TC_WAIT_LIMIT = 1u << 24;
 
 struct TcArgs {
     __half* y; const uint8_t* W; int type; int M, N, K;
+    __half* y2; const uint8_t* W2; int M2;   // optional second weight matrix of the same type and K over the same activations (its own output): row tiles after the first's
     int n_main, n_min;        // K tiles of weights, K tiles of the min and centring terms (Q4_K)
     int* status;
     int n_full, ksplit;       // output tiles [0, n_full) are computed whole; each later one ("tail" tile) as `ksplit` K ranges whose
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
     __shared__ volatile int drain_go[2];     // verdict of the draining role's polling lane, double-buffered across tiles
     uint8_t* smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = (a.N + n_tile - 1) / n_tile, tiles_m = (a.M + TC_M - 1) / TC_M;
+    const int tiles_n = (a.N + n_tile - 1) / n_tile, tiles_m1 = (a.M + TC_M - 1) / TC_M, tiles_m = tiles_m1 + (a.M2 + TC_M - 1) / TC_M;
     const int n_tail = tiles_n * tiles_m - a.n_full;
     const int n_work = a.n_full + n_tail * a.ksplit;
     const int n_tiles = a.n_main + a.n_min;
@@ -450,8 +451,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
             int tile, sp, kt0, kt1; bool extra;
             k_range(w, tile, sp, kt0, kt1, extra);
-            const int row = (tile / tiles_n) * TC_M + rl;
-            const uint8_t* rowp = row < a.M ? a.W + (size_t)row * nb * BB : nullptr;
+            const int rt = tile / tiles_n;
+            const bool second = rt >= tiles_m1;
+            const int row = (second ? rt - tiles_m1 : rt) * TC_M + rl;
+            const uint8_t* rowp = row < (second ? a.M2 : a.M) ? (second ? a.W2 : a.W) + (size_t)row * nb * BB : nullptr;
             const int g_first = kt0 / GT, g_last = kt1 / GT;
             auto fetch = [&](decltype(cur)& r, int g) {
                 if (!rowp || g >= g_last) return;
@@ -500,7 +503,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
             const uint32_t acc = j & 1;
             int tile, sp, t0_, t1_; bool extra_;
             k_range(w, tile, sp, t0_, t1_, extra_);
-            const int n0 = (tile % tiles_n) * n_tile, row = (tile / tiles_n) * TC_M + rl;
+            const int rt = tile / tiles_n;
+            const bool second = rt >= tiles_m1;
+            const int n0 = (tile % tiles_n) * n_tile, row = (second ? rt - tiles_m1 : rt) * TC_M + rl, m_out = second ? a.M2 : a.M;
+            __half* y_out = second ? a.y2 : a.y;
             float* part = w >= a.n_full ? a.part + ((size_t)sp * n_tail + (size_t)(tile - a.n_full)) * n_tile * TC_M : nullptr;
             if (dw == 0 && lane == 0) {
                 const bool good = tc_wait(&acc_full[acc], (j >> 1) & 1) && !fail;
@@ -513,13 +519,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
             for (int cb = 0; cb < n_tile; cb += 32) {
                 uint32_t r[32];
                 tc_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + acc * 256u + (uint32_t)cb, r);
-                if (row < a.M) {
+                if (row < m_out) {
                     #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int tok = n0 + cb + c;
                         if (tok < a.N) {
                             if (part) part[(size_t)(cb + c) * TC_M + rl] = __uint_as_float(r[c]);
-                            else a.y[(size_t)tok * a.M + row] = __float2half_rn(__uint_as_float(r[c]));
+                            else y_out[(size_t)tok * m_out + row] = __float2half_rn(__uint_as_float(r[c]));
                         }
                     }
                 }
@@ -541,13 +547,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_kernel(const __grid_cons
 // sum of the K-range partials of the tail tiles in a fixed order, rounded once to fp16; a thread takes four consecutive rows
 // of one token (16-byte loads; the rows of a tile start at a multiple of 128, so with M a multiple of 4 a group of four
 // is inside the tensor or outside it as a whole)
-__global__ void mmq_tc_reduce_kernel(__half* y, const float* part, int M, int N, int n_tile, int tiles_n, int n_full, int n_tail, int ksplit) {
+__global__ void mmq_tc_reduce_kernel(__half* y, __half* y2, const float* part, int M, int M2, int N, int n_tile, int tiles_n, int n_full, int n_tail, int ksplit) {
     pdl_wait();
     const long long total = (long long)n_tail * n_tile * TC_M;
     const long long e = 4 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
     if (e >= total) return;
     const int rl = (int)(e % TC_M), tl = (int)((e / TC_M) % n_tile), tile = n_full + (int)(e / ((long long)TC_M * n_tile));
-    const int row = (tile / tiles_n) * TC_M + rl, tok = (tile % tiles_n) * n_tile + tl;
+    int rt = tile / tiles_n;
+    const int tiles_m1 = (M + TC_M - 1) / TC_M, tok = (tile % tiles_n) * n_tile + tl;
+    if (rt >= tiles_m1) { rt -= tiles_m1; y = y2; M = M2; }          // a tile of the second matrix
+    const int row = rt * TC_M + rl;
     if (row >= M || tok >= N) return;
     float4 sum = *reinterpret_cast<const float4*>(part + e);
     for (int k = 1; k < ksplit; ++k) {
@@ -588,8 +597,7 @@ static EncodeTiledFn encode_tiled_fn() {
 // (every range keeps at least eight K tiles, and its partial sums cost a tile of fp32 traffic each way).  Cost of a
 // choice, in tile times of the full width = (whole rounds + 1 / ranges + a little per range) x (tile width / 256,
 // floored at 0.65 for the MMA-issue and dequantisation floor of a K tile).
-static void tc_pick(int M, int N, int n_main_tiles, int sm_count, int& n_tile, int& ksplit, int& n_full) {
-    const int tiles_m = (M + TC_M - 1) / TC_M;
+static void tc_pick(int tiles_m, int N, int n_main_tiles, int sm_count, int& n_tile, int& ksplit, int& n_full) {
     float best = 1e30f;
     n_tile = 256; ksplit = 1; n_full = tiles_m * ((N + 255) / 256);
     for (int cand = 256; cand >= 32; cand >>= 1) {
@@ -608,14 +616,16 @@ static void tc_pick(int M, int N, int n_main_tiles, int sm_count, int& n_tile, i
         if (cost < best - 1e-6f) { best = cost; n_tile = cand; ksplit = ks; n_full = ks > 1 ? rounds * sm_count : tiles; }
     }
 }
-size_t mmq_tc_scratch_bytes(int type, int M, int N, int K) {
+size_t mmq_tc_scratch_bytes(int type, int M, int N, int K) { return mmq_tc_scratch_bytes_pair(type, M, 0, N, K); }
+size_t mmq_tc_scratch_bytes_pair(int type, int M, int M2, int N, int K) {
     DeviceCtx* c = ctx();
     const int sm = c ? c->sm_count : 148;
     const int n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     size_t b = (((size_t)N * (size_t)(K + n_min * TC_K) * sizeof(__half)) + 255) & ~(size_t)255;
     int n_tile, ks, n_full;
-    tc_pick(M, N, K / TC_K, sm, n_tile, ks, n_full);
-    const int tiles = ((N + n_tile - 1) / n_tile) * ((M + TC_M - 1) / TC_M);
+    const int tiles_m = (M + TC_M - 1) / TC_M + (M2 + TC_M - 1) / TC_M;
+    tc_pick(tiles_m, N, K / TC_K, sm, n_tile, ks, n_full);
+    const int tiles = ((N + n_tile - 1) / n_tile) * tiles_m;
     if (ks > 1) b += (size_t)ks * (size_t)(tiles - n_full) * n_tile * TC_M * sizeof(float);
     return b + 256;
 }
@@ -628,17 +638,25 @@ bool mmq_tc_applies(const void* W, int type, int M, int N, int K) {
 }
 
 int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* xq, int M, int N, int K, bool same_x, cudaStream_t st) {
+    return launch_mmq_tc_pair(y, nullptr, W, nullptr, type, x, xq, M, 0, N, K, same_x, st);
+}
+// y = x . W^T and, when W2 is given, y2 = x . W2^T in the same launch: the row tiles of both matrices are one list of work, so
+// two products that share their activations (gate and up) fill the grid together instead of one after the other.
+int launch_mmq_tc_pair(__half* y, __half* y2, const void* W, const void* W2, int type, const __half* x, __half* xq, int M, int M2, int N, int K,
+                       bool same_x, cudaStream_t st) {
     DeviceCtx* c = ctx();
     if (!c) return set_error(JB_ERR_STATE, "batched gemm: library not initialised");
     TcArgs a;
     a.y = y; a.W = (const uint8_t*)W; a.type = type; a.M = M; a.N = N; a.K = K;
+    a.y2 = y2; a.W2 = (const uint8_t*)W2; a.M2 = W2 ? M2 : 0;
     a.n_main = K / TC_K;
     a.n_min = type == T_Q4K ? (2 * (K / 32) + TC_K - 1) / TC_K : 0;
     a.status = c->d_status;
     const int Kp = (a.n_main + a.n_min) * TC_K;
     int n_tile;
-    tc_pick(M, N, a.n_main, c->sm_count, n_tile, a.ksplit, a.n_full);
-    const int tiles_n = (N + n_tile - 1) / n_tile, tiles = tiles_n * ((M + TC_M - 1) / TC_M);
+    const int tiles_m = (M + TC_M - 1) / TC_M + (a.M2 + TC_M - 1) / TC_M;
+    tc_pick(tiles_m, N, a.n_main, c->sm_count, n_tile, a.ksplit, a.n_full);
+    const int tiles_n = (N + n_tile - 1) / n_tile, tiles = tiles_n * tiles_m;
     a.part = a.ksplit > 1 ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xq) + ((((size_t)N * Kp * sizeof(__half)) + 255) & ~(size_t)255)) : nullptr;
 
     CUtensorMap map;
@@ -680,7 +698,7 @@ int launch_mmq_tc(__half* y, const void* W, int type, const __half* x, __half* x
     if (a.ksplit > 1) {
         const int n_tail = tiles - a.n_full;
         const long long n = (long long)n_tail * n_tile * TC_M / 4;
-        JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, (const float*)a.part, M, N, n_tile, tiles_n, a.n_full, n_tail, a.ksplit));
+        JB_CUDA(launch_k(mmq_tc_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, pdl_enabled(), y, y2, (const float*)a.part, M, a.M2, N, n_tile, tiles_n, a.n_full, n_tail, a.ksplit));
         count_launch();
     }
     return JB_OK;

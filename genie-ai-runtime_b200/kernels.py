@@ -159,6 +159,11 @@ def gemm_quant_batched_int_dots(y, dots, W, ggml_type, x, M, N, K, stream=None):
                                                     _stream(stream)))
 
 
+def gemm_quant_batched_pair(y0, W0, t0, M0, y1, W1, t1, M1, x, N, K, stream=None):
+    check(lib.jllm_b200_gemm_quant_batched_pair(_ptr(y0), _ptr(W0), i32(t0), i32(M0), _ptr(y1), _ptr(W1), i32(t1), i32(M1), _ptr(x), i32(N), i32(K),
+                                                _stream(stream)))
+
+
 def norm_gemv_quant_pair(y0, W0, t0, M0, y1, W1, t1, M1, x, norm_weight, weight_fp32, eps, K, stream=None):
     check(lib.jllm_b200_norm_gemv_quant_pair(_ptr(y0), _ptr(W0), i32(t0), i32(M0), _ptr(y1), _ptr(W1), i32(t1), i32(M1), _ptr(x),
                                              _ptr(norm_weight), i32(1 if weight_fp32 else 0), f32(eps), i32(K), _stream(stream)))

@@ -168,6 +168,12 @@ int64_t  jllm_b200_scratch_capacity(jllm_b200_scratch* s);
 int jllm_b200_gemv_quant_int_dots(void* y, int32_t* dots, const void* W, int ggml_type, const void* x, int M, int K, void* stream);
 /* Same for the batched GEMM: dots[N][M][K/32] or [N][M][K/16]. */
 int jllm_b200_gemm_quant_batched_int_dots(void* y, int32_t* dots, const void* W, int ggml_type, const void* x, int M, int N, int K, void* stream);
+/* Two batched products over the same activations (the gate and up projections of a layer): y0[N x M0] = x . W0^T and
+ * y1[N x M1] = x . W1^T, equal to two jllm_b200_gemm_quant_batched calls.  With more than 64 tokens (or the large matrices
+ * from 49) and both matrices Q4_K or both Q6_K the row tiles of the two share one launch; otherwise two launches, the
+ * second reusing the quantised activations.  N >= 2. */
+int jllm_b200_gemm_quant_batched_pair(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,
+                                      const void* x, int N, int K, void* stream);
 /* RMSNorm fused into the shared-activation GEMVs: x := half(x * rrms * w) is formed in shared
  * memory and quantised there, equal to fused_rmsnorm_residual -> gemv_quant_pair / _triple. */
 int jllm_b200_norm_gemv_quant_pair(void* y0, const void* W0, int type0, int M0, void* y1, const void* W1, int type1, int M1,

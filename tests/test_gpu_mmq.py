@@ -78,6 +78,28 @@ def test_few_tokens_stream_the_weights_once(t, M, N, K):
     assert jb.device_status() == 0
 
 
+@pytest.mark.parametrize("t,M0,M1,N,K", [(12, 300, 200, 100, 1024), (14, 130, 257, 70, 512), (12, 2500, 2300, 1000, 1024), (12, 9728, 9728, 64, 2560),
+                                          (12, 96, 64, 8, 512)])
+def test_two_products_over_the_same_activations(t, M0, M1, N, K):
+    """gemm_quant_batched_pair (the gate and up projections of a batched layer): both outputs against the oracle.  The shapes
+    cover the shared launch of the tensor-core kernel with ragged row tiles of both matrices, more tiles than SMs (whole
+    rounds plus split tail tiles that belong to either matrix), the decoder's own pair at 64 streams, and the few-token
+    path (two launches)."""
+    import torch
+    jb = pkg()
+    rng = np.random.Generator(np.random.PCG64(1010 + M0 + N))
+    W0 = orc.gen_weight(rng, t, M0, K); W1 = orc.gen_weight(rng, t, M1, K)
+    X = orc.gen_act(rng, N * K)
+    y0 = torch.full((N * M0,), float("nan"), dtype=torch.float16, device="cuda")
+    y1 = torch.full((N * M1,), float("nan"), dtype=torch.float16, device="cuda")
+    jb.gemm_quant_batched_pair(y0, dev(W0), t, M0, y1, dev(W1), t, M1, dev(X), N, K)
+    for y, W, M in ((y0, W0, M0), (y1, W1, M1)):
+        want = orc.entry_gemm_quant_batched(W, t, X, M, N, K).astype(np.float32).reshape(-1)
+        ok, md = close_gemm(y.float().cpu().numpy(), want, N, M)
+        assert ok, md
+    assert jb.device_status() == 0
+
+
 @pytest.mark.parametrize("t", [12, 14])
 def test_tensor_core_and_cuda_core_paths_agree(t):
     """The tcgen05 kernel and the CUDA-core kernel (the one that exports the integer accumulators) compute the same
