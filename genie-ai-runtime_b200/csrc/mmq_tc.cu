@@ -22,6 +22,9 @@
 //   warps 2-9   dequantise the weight tile (two threads per row) into the 128-byte-swizzled K-major layout
 //   warps 10-13 drain the finished accumulator (tcgen05.ld) and store fp16 results token-major while the
 //               other accumulator is being filled.
+// The grid walks a list of work: whole output tiles first (a multiple of the grid), then the leftover tiles cut into K
+// ranges that fill one more short round (fp32 partials, summed by a second kernel); the row tiles of a second weight
+// matrix over the same activations (gate and up) can follow the first's in the same list.
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word, the kernel still frees
 // its tensor memory and returns.
 #include "mmq.cuh"
